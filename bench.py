@@ -1,0 +1,341 @@
+#!/usr/bin/env python
+"""Benchmark of the E1 Elman-cell hot path (forward + BPTT backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward + backward pass of the E1 cell over one batch of seeded
+synthetic input at the benchmark's configs[1]: bf16, d=1280, B=32 sequences per
+GPU, T=512 (16 384 tokens per GPU and step).  For N > 1 the launcher starts one
+process per GPU (torchrun); the batch is sharded by rank with no data-path
+collective (each sequence's recurrence is independent): weak scaling.
+
+Prints ONE JSON line (rank 0).  `value` is whole-job tokens/s with inputs
+resident in HBM; `e2e` is the same pass through the public API with pinned host
+buffers copied in and results copied out inside the timed region.
+`--impl reference` times the reference's own CPU algorithm (the Python time loop
+with autograd, restated in oracle/) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "E1 layer fwd+bwd tokens/s @ d1280 B32 T512"
+UNIT = "tokens/s"
+T, B, D = 512, 32, 1280
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes per launch of the dominant kernel from the committed ncu capture
+# (profiles/), or None while no capture of the current kernel exists.
+NCU_TRAFFIC_BYTES = {"rec_tc_kernel<fwd>": None, "rec_tc_kernel<bwd>": None}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-steps", type=int, default=128,
+                    help="time steps of the workload the CPU baseline runs")
+    return ap.parse_args()
+
+
+def make_inputs(seed: int):
+    """configs[1] recipe: x~N(0,1); W_x,W_h~N(0,1/d), W_h rescaled to spectral radius 0.9;
+    b=0; z = x W_gx^T with W_gx~N(0,1/(2d)); h0=0; d_output~N(0,1)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, B, D, generator=g)
+    W_x = torch.randn(D, D, generator=g) / math.sqrt(D)
+    W_h = torch.randn(D, D, generator=g) / math.sqrt(D)
+    rho = float(torch.linalg.eigvals(W_h.double()).abs().max())
+    W_h = W_h * (0.9 / rho)
+    b = torch.zeros(D)
+    W_gx = torch.randn(D, D, generator=g) / math.sqrt(2 * D)
+    z = (x.reshape(T * B, D) @ W_gx.T).reshape(T, B, D)
+    r = torch.randn(T, B, D, generator=g)
+    return {"x": x, "z": z, "h0": torch.zeros(B, D), "W_x": W_x, "W_h": W_h, "b": b, "d_output": r}
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1])); mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for nm, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def cpu_reference_pass(inp, steps):
+    """The reference's CPU path for this workload: the Python time loop of its E1 cell
+    with autograd for BPTT, fp32, on the first `steps` time steps.  Returns seconds."""
+    from oracle import elman_oracle as orc
+    sub = {k: (v[:steps].contiguous() if v.dim() == 3 else v) for k, v in inp.items()}
+    t0 = time.perf_counter()
+    orc.e1_autograd(sub["x"], sub["z"], sub["h0"], sub["W_x"], sub["W_h"], sub["b"],
+                    sub["d_output"])
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    inp = make_inputs(1234)
+    sample = min(T, 32)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_pass(inp, sample)
+    times = [cpu_reference_pass(inp, sample) for _ in range(args.steps)]
+    sec = sum(times) / len(times)
+    value = B * sample / sec
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * (T / sample),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "configs[1]: E1 cell fwd+bwd, d=1280, B=32, T=512 (fp32 on CPU)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"first {sample} of {T} time steps per step, full B and d; "
+                                   "ms_per_step is scaled to T=512"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    from elman_b200 import _lib
+    from elman_b200 import hasty_pytorch_lib as H
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group(backend="nccl", device_id=dev)
+
+    inp = make_inputs(1234 + rank)
+    host = {k: v.to(torch.bfloat16).contiguous().pin_memory() for k, v in inp.items()}
+    d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+    torch.cuda.synchronize()
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def step_device():
+        h, out, v = H.mamba_gated_elman_forward(True, d["x"], d["z"], d["h0"], d["W_x"],
+                                                d["W_h"], d["b"])
+        return H.mamba_gated_elman_backward(d["W_x"], d["W_h"], d["x"], d["z"], h, v,
+                                            d["d_output"]), out
+
+    out_host = {k: torch.empty_like(host["x"]).pin_memory() for k in ("y", "dx", "dz")}
+    dw_host = {k: torch.empty(D, D, dtype=torch.bfloat16).pin_memory() for k in ("dW_x", "dW_h")}
+
+    def step_e2e():
+        x = host["x"].to(dev, non_blocking=True)
+        z = host["z"].to(dev, non_blocking=True)
+        r = host["d_output"].to(dev, non_blocking=True)
+        h, out, v = H.mamba_gated_elman_forward(True, x, z, d["h0"], d["W_x"], d["W_h"], d["b"])
+        dx, dz, dWx, dWh, db = H.mamba_gated_elman_backward(d["W_x"], d["W_h"], x, z, h, v, r)
+        out_host["y"].copy_(out, non_blocking=True)
+        out_host["dx"].copy_(dx, non_blocking=True)
+        out_host["dz"].copy_(dz, non_blocking=True)
+        dw_host["dW_x"].copy_(dWx, non_blocking=True)
+        dw_host["dW_h"].copy_(dWh, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, phases=False):
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(steps)]
+        phase_ms = [[], [], [], []]
+        barrier()
+        wall0 = time.perf_counter()
+        for s, e in ev:
+            flush_buf.zero_()          # evict L2 between timed iterations (not timed)
+            s.record()
+            fn()
+            e.record()
+            if phases:
+                e.synchronize()
+                for ph in range(4):
+                    phase_ms[ph].append(_lib.last_timing_ms(ph))
+        barrier()
+        wall = time.perf_counter() - wall0
+        total_ms = sum(s.elapsed_time(e) for s, e in ev)
+        return total_ms, wall, phase_ms
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    torch.cuda.synchronize()
+    if _lib.device_status()[0] != 0:
+        raise SystemExit("a device-side wait timed out during warm-up: " + str(_lib.device_status()))
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    _lib.set_option("time_kernels", 1)
+    launches0, tc0 = _lib.launch_count(), _lib.tc_launch_count()
+    total_ms, wall, phase_ms = timed(step_device, args.steps, phases=True)
+    launches = _lib.launch_count() - launches0
+    tc_launches = _lib.tc_launch_count() - tc0
+    _lib.set_option("time_kernels", 0)
+    clocks = sampler.stop() if rank == 0 else None
+
+    for _ in range(3):
+        step_e2e()
+    torch.cuda.synchronize()
+    e2e_ms, _, _ = timed(step_e2e, args.steps)
+    if _lib.device_status()[0] != 0:
+        raise SystemExit("a device-side wait timed out: " + str(_lib.device_status()))
+
+    t_all = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = (float(v) for v in t_all.cpu())
+
+    if rank == 0:
+        tokens = B * T * world * args.steps
+        value = tokens / (total_ms / 1e3)
+        e2e_value = tokens / (e2e_ms / 1e3)
+        peaks, peaks_kind = read_peaks()
+        mean = lambda xs: sum(xs) / max(len(xs), 1)
+        rec_fwd_ms, rec_bwd_ms, proj_ms, bgemm_ms = (mean(p) for p in phase_ms)
+        dom = "fwd" if rec_fwd_ms >= rec_bwd_ms else "bwd"
+        dom_ms = max(rec_fwd_ms, rec_bwd_ms)
+        rec_flops = 2.0 * T * B * D * D               # per launch of either recurrence kernel
+        rec_bytes = 5.0 * B * D * 2 * T               # algorithmic HBM bytes per launch
+        achieved_tf = rec_flops / (dom_ms / 1e3) / 1e12 if dom_ms > 0 else 0.0
+        peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+        roofline = {
+            "kernel": f"rec_tc_kernel<{dom}>", "bound": "tensor",
+            "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s",
+            "frac": achieved_tf / peak_tf if peak_tf else None,
+            "traffic": NCU_TRAFFIC_BYTES.get(f"rec_tc_kernel<{dom}>"),
+            "peak_source": f"{peaks_kind} (bf16_tflops burst; sustained "
+                           f"{peaks.get('bf16_tflops_sustained')})",
+            "note": "per-step recurrence at B=32 is latency-bound (grid-wide dependency every "
+                    "step); us_per_step is the figure of merit",
+            "hbm_view": {"achieved_gbs": rec_bytes / (dom_ms / 1e3) / 1e9 if dom_ms > 0 else 0.0,
+                         "peak_gbs": peaks.get("hbm_gbs")},
+        }
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "configs[1]: E1 cell fwd+bwd, bf16, d=1280, B=32 per GPU, T=512",
+                       "tokens_per_step_per_gpu": B * T, "sharding": "batch (no collective)",
+                       "l2": "256 MiB buffer written between timed iterations",
+                       "seed": "1234+rank"},
+            "e2e": {"value": e2e_value, "unit": UNIT,
+                    "h2d_bytes_per_step": 3 * T * B * D * 2,
+                    "d2h_bytes_per_step": 3 * T * B * D * 2 + 2 * D * D * 2,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches, "tensor_core_launches": tc_launches,
+            "clocks": clocks, "roofline": roofline,
+            "phases_ms": {"recurrence_fwd": rec_fwd_ms, "recurrence_bwd": rec_bwd_ms,
+                          "projection_fwd": proj_ms, "gemms_bwd": bgemm_ms,
+                          "recurrence_fwd_us_per_step": rec_fwd_ms * 1e3 / T,
+                          "recurrence_bwd_us_per_step": rec_bwd_ms * 1e3 / T},
+            "wall_s_timed_region": wall,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            fp32 = {k: v.float() for k, v in host.items()}
+            cpu_reference_pass(fp32, 8)
+            sec = cpu_reference_pass(fp32, args.cpu_sample_steps)
+            line["cpu_baseline"] = {
+                "value": B * args.cpu_sample_steps / sec, "unit": UNIT, "cores": cores,
+                "kind": "port",
+                "sample": f"first {args.cpu_sample_steps} of {T} time steps, full B and d, fp32, "
+                          f"one pass ({sec:.1f} s)"}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line), flush=True)
+
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,626 @@
+// C ABI of the library: argument checks, workspace carving and the sequence of
+// kernels behind each entry point declared in include/elman_b200.h.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+
+#include "common.cuh"
+
+namespace elman {
+
+// ---------------------------------------------------------------------------
+// errors, options, counters, status word
+// ---------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+Options& options() {
+  static Options o;
+  return o;
+}
+
+static std::atomic<long> g_launches{0};
+static std::atomic<long> g_tc_launches{0};
+void count_launch(bool tensor_core) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (tensor_core) g_tc_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// One host-mapped status word per device, created on first use.
+static constexpr int kMaxDevices = 64;
+static int* g_status_host[kMaxDevices] = {nullptr};
+static int* g_status_dev[kMaxDevices] = {nullptr};
+
+static int ensure_status(int dev) {
+  if (dev < 0 || dev >= kMaxDevices) return -1;
+  if (g_status_host[dev] != nullptr) return 0;
+  int* hp = nullptr;
+  if (cudaHostAlloc((void**)&hp, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  memset(hp, 0, 64);
+  int* dp = nullptr;
+  if (cudaHostGetDevicePointer((void**)&dp, hp, 0) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFreeHost(hp);
+    return -1;
+  }
+  g_status_host[dev] = hp;
+  g_status_dev[dev] = dp;
+  return 0;
+}
+
+int* device_status_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (ensure_status(dev) != 0) return nullptr;
+  return g_status_dev[dev];
+}
+
+static int check_status_on_entry() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return ELMAN_OK;
+  if (dev < 0 || dev >= kMaxDevices || g_status_host[dev] == nullptr) return ELMAN_OK;
+  int code = *(volatile int*)g_status_host[dev];
+  if (code != 0)
+    return set_error(ELMAN_ERR_TIMEOUT,
+                     "an earlier launch gave up a bounded device-side wait (kernel %d, step %d); "
+                     "results of that launch are invalid",
+                     (code >> 24) & 0xFF, code & 0xFFFFFF);
+  return ELMAN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// workspace carving
+// ---------------------------------------------------------------------------
+struct Carver {
+  char* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base((char*)p) {}
+  void* take(size_t bytes) {
+    off = (off + 255) & ~(size_t)255;
+    void* p = base ? base + off : nullptr;
+    off += bytes;
+    return p;
+  }
+  size_t total() const { return (off + 255) & ~(size_t)255; }
+};
+
+static inline size_t esize(int dtype) { return dtype == ELMAN_F32 ? 4 : 2; }
+
+static int check_common(int dtype, int T, int B, int d) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(T >= 0 && B >= 0 && d >= 0, "negative size (T=%d B=%d d=%d)", T, B, d);
+  ELMAN_ARG_CHECK((long)T * B * d < (1L << 40), "tensor too large");
+  return check_status_on_entry();
+}
+
+#define REQUIRE_PTR(p) ELMAN_ARG_CHECK((p) != nullptr, "argument %s is NULL", #p)
+
+static bool use_tc(int dtype) { return dtype == ELMAN_BF16 && options().force_generic == 0; }
+
+// C[M,N] = A[M,K] W[N,K]^T (+bias) (+C): tcgen05 when possible, CUDA cores otherwise.
+static int proj_nt(int dtype, int M, int N, int K, const void* A, int lda, const void* W, int ldw,
+                   const void* bias, void* C, int ldc, int accumulate, cudaStream_t st) {
+  if (M == 0 || N == 0) return ELMAN_OK;
+  if (use_tc(dtype) && gemm_tc_supported(M, N, K, A, lda, W, ldw, C, ldc, 0)) {
+    return gemm_tc_nt(M, N, K, (const bf16*)A, lda, (const bf16*)W, ldw, (const bf16*)bias, C, ldc,
+                      0, accumulate, st);
+  }
+  return gemm_generic(dtype, M, N, K, A, lda, 1, W, 1, ldw, bias, C, ldc, accumulate, st);
+}
+
+// C[M,N] = A[M,K] Bm[K,N] (+C).  Bt is scratch for Bm^T (K*N elements) used by the
+// tensor-core path, or NULL to force the strided CUDA-core kernel.
+static int gemm_nn(int dtype, int M, int N, int K, const void* A, int lda, const void* Bm, int ldb,
+                   void* Bt, void* C, int ldc, int accumulate, cudaStream_t st) {
+  if (M == 0 || N == 0) return ELMAN_OK;
+  if (use_tc(dtype) && Bt != nullptr && ldb == N &&
+      gemm_tc_supported(M, N, K, A, lda, Bt, K, C, ldc, 0)) {
+    ELMAN_RETURN_IF(transpose2d(dtype, K, N, Bm, Bt, st));
+    return gemm_tc_nt(M, N, K, (const bf16*)A, lda, (const bf16*)Bt, K, nullptr, C, ldc, 0,
+                      accumulate, st);
+  }
+  return gemm_generic(dtype, M, N, K, A, lda, 1, Bm, ldb, 1, nullptr, C, ldc, accumulate, st);
+}
+
+// C[M,N] = At^T Bt_ where the inputs are stored as Am[K,M] and Bm[K,N] (sum over
+// the leading "row" index, K = T*B).  AT / BT are the transposed copies [M,K] and
+// [N,K]; when `at_ready` / `bt_ready` they already hold the data.
+static int gemm_tn(int dtype, int M, int N, long K, const void* Am, const void* Bm, void* AT,
+                   bool at_ready, void* BT, bool bt_ready, void* C, cudaStream_t st) {
+  if (M == 0 || N == 0) return ELMAN_OK;
+  if (use_tc(dtype) && AT != nullptr && BT != nullptr && K < (1L << 31) &&
+      gemm_tc_supported(M, N, (int)K, AT, (int)K, BT, (int)K, C, N, 0)) {
+    if (!at_ready) ELMAN_RETURN_IF(transpose2d(dtype, (int)K, M, Am, AT, st));
+    if (!bt_ready) ELMAN_RETURN_IF(transpose2d(dtype, (int)K, N, Bm, BT, st));
+    return gemm_tc_nt(M, N, (int)K, (const bf16*)AT, (int)K, (const bf16*)BT, (int)K, nullptr, C,
+                      N, 0, 0, st);
+  }
+  return gemm_generic(dtype, M, N, (int)K, Am, 1, M, Bm, N, 1, nullptr, C, N, 0, st);
+}
+
+// Optional per-phase timing with CUDA events on the caller's stream (option
+// "time_kernels"): phase 0 = forward recurrence, 1 = backward recurrence,
+// 2 = forward projection GEMM(s), 3 = backward GEMMs and their transposes.
+static constexpr int kPhases = 4;
+static cudaEvent_t g_ev[kPhases][2];
+static bool g_ev_ready = false;
+static bool g_ev_recorded[kPhases] = {false, false, false, false};
+
+struct PhaseTimer {
+  int phase;
+  cudaStream_t st;
+  bool on;
+  PhaseTimer(int ph, cudaStream_t s) : phase(ph), st(s), on(options().time_kernels != 0) {
+    if (!on) return;
+    if (!g_ev_ready) {
+      for (int i = 0; i < kPhases; ++i)
+        for (int j = 0; j < 2; ++j) cudaEventCreate(&g_ev[i][j]);
+      g_ev_ready = true;
+    }
+    cudaEventRecord(g_ev[phase][0], st);
+  }
+  ~PhaseTimer() {
+    if (!on) return;
+    cudaEventRecord(g_ev[phase][1], st);
+    g_ev_recorded[phase] = true;
+  }
+};
+
+static bool dense_tc_ok(int dtype, int T, int B, int d) {
+  return use_tc(dtype) && rec_tc_supported(T, B, d);
+}
+
+// ---------------------------------------------------------------------------
+// E1
+// ---------------------------------------------------------------------------
+struct E1FwdWs { void* pre; int* sync; };
+static size_t carve_e1_fwd(int dtype, int T, int B, int d, void* ws, E1FwdWs* o) {
+  Carver c(ws);
+  o->pre = c.take((size_t)T * B * d * esize(dtype));
+  size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
+  o->sync = (int*)c.take(sb);
+  return c.total();
+}
+
+struct E1BwdWs { void* Wt; void* dv; float* db; int* sync; void* WxT; void* dvT; void* xT; };
+static size_t carve_e1_bwd(int dtype, int T, int B, int d, void* ws, E1BwdWs* o) {
+  Carver c(ws);
+  size_t es = esize(dtype);
+  o->Wt = c.take((size_t)d * d * es);
+  o->dv = c.take((size_t)(T + 1) * B * d * es);  // slot T: zero "gradient from the future"
+  o->db = (float*)c.take((size_t)d * sizeof(float));
+  size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
+  o->sync = (int*)c.take(sb);
+  if (dtype == ELMAN_BF16) {
+    o->WxT = c.take((size_t)d * d * es);
+    o->dvT = c.take((size_t)T * B * d * es);
+    o->xT = c.take((size_t)T * B * d * es);
+  } else {
+    o->WxT = o->dvT = o->xT = nullptr;
+  }
+  return c.total();
+}
+
+static int run_rec_fwd(int dtype, int T, int B, int d, const void* W, const void* pre,
+                       const void* g, void* h, void* y, void* v, int* sync, cudaStream_t st) {
+  PhaseTimer timer(0, st);
+  RecFwdArgs a{T, B, d, W, pre, g, h, y, v, sync};
+  if (dense_tc_ok(dtype, T, B, d)) return rec_fwd_tc(a, st);
+  return rec_fwd_generic(dtype, a, st);
+}
+
+static int run_rec_bwd(int dtype, int T, int B, int d, const void* Wt, const void* h,
+                       const void* v, const void* g, const void* dy, void* dv, void* dg, float* db,
+                       int* sync, cudaStream_t st) {
+  PhaseTimer timer(1, st);
+  RecBwdArgs a{T, B, d, Wt, h, v, g, dy, dv, dg, db, sync};
+  if (dense_tc_ok(dtype, T, B, d)) return rec_bwd_tc(a, st);
+  return rec_bwd_generic(dtype, a, st);
+}
+
+}  // namespace elman
+
+using namespace elman;
+
+extern "C" {
+
+int elman_b200_version(void) { return 100; }
+
+const char* elman_b200_last_error(void) { return g_err; }
+
+int elman_b200_device_status(int* detail, int clear) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return set_error(ELMAN_ERR_CUDA, "no current CUDA device");
+  }
+  if (detail) *detail = 0;
+  if (dev < 0 || dev >= kMaxDevices || g_status_host[dev] == nullptr) return ELMAN_OK;
+  int code = *(volatile int*)g_status_host[dev];
+  if (detail) *detail = code;
+  if (clear) *(volatile int*)g_status_host[dev] = 0;
+  return code == 0 ? ELMAN_OK : ELMAN_ERR_TIMEOUT;
+}
+
+int elman_b200_set_option(const char* name, long value) {
+  if (name == nullptr) return set_error(ELMAN_ERR_ARG, "option name is NULL");
+  Options& o = options();
+  if (!strcmp(name, "force_generic")) o.force_generic = value;
+  else if (!strcmp(name, "spin_limit")) o.spin_limit = value < 1 ? 1 : value;
+  else if (!strcmp(name, "rec_ksplit")) o.rec_ksplit = value;
+  else if (!strcmp(name, "rec_groups")) o.rec_groups = value;
+  else if (!strcmp(name, "time_kernels")) o.time_kernels = value;
+  else return set_error(ELMAN_ERR_ARG, "unknown option '%s'", name);
+  return ELMAN_OK;
+}
+
+long elman_b200_get_option(const char* name) {
+  if (name == nullptr) return -1;
+  Options& o = options();
+  if (!strcmp(name, "force_generic")) return o.force_generic;
+  if (!strcmp(name, "spin_limit")) return o.spin_limit;
+  if (!strcmp(name, "rec_ksplit")) return o.rec_ksplit;
+  if (!strcmp(name, "rec_groups")) return o.rec_groups;
+  if (!strcmp(name, "time_kernels")) return o.time_kernels;
+  return -1;
+}
+
+int elman_b200_last_timing(int phase, float* ms) {
+  ELMAN_ARG_CHECK(phase >= 0 && phase < kPhases && ms != nullptr, "bad phase %d", phase);
+  if (!g_ev_ready || !g_ev_recorded[phase])
+    return set_error(ELMAN_ERR_ARG, "phase %d was not timed (set option time_kernels)", phase);
+  ELMAN_CUDA_CHECK(cudaEventSynchronize(g_ev[phase][1]));
+  ELMAN_CUDA_CHECK(cudaEventElapsedTime(ms, g_ev[phase][0], g_ev[phase][1]));
+  return ELMAN_OK;
+}
+
+long elman_b200_launch_count(void) { return g_launches.load(); }
+long elman_b200_tc_launch_count(void) { return g_tc_launches.load(); }
+
+// ------------------------------- E1 ----------------------------------------
+
+size_t elman_e1_forward_workspace(int dtype, int T, int B, int d) {
+  E1FwdWs w;
+  return carve_e1_fwd(dtype, T, B, d, nullptr, &w);
+}
+
+int elman_e1_forward(int dtype, int training, int T, int B, int d, const void* x, const void* z,
+                     const void* h0, const void* W_x, const void* W_h, const void* b, void* h,
+                     void* output, void* v, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (B == 0 || d == 0) return ELMAN_OK;
+  REQUIRE_PTR(h0); REQUIRE_PTR(h);
+  cudaStream_t st = (cudaStream_t)stream;
+  ELMAN_RETURN_IF(copy_rows(dtype, h0, h, (long)B * d, st));
+  if (T == 0) return ELMAN_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(z); REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(b);
+  REQUIRE_PTR(output); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(!training || v != nullptr, "v must be provided when training");
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E1FwdWs w;
+  size_t need = carve_e1_fwd(dtype, T, B, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  // time-parallel input projection with the bias fused into the epilogue
+  {
+    PhaseTimer timer(2, st);
+    ELMAN_RETURN_IF(proj_nt(dtype, T * B, d, d, x, d, W_x, d, b, w.pre, d, 0, st));
+  }
+  return run_rec_fwd(dtype, T, B, d, W_h, w.pre, z, h, output, training ? v : nullptr, w.sync, st);
+}
+
+size_t elman_e1_backward_workspace(int dtype, int T, int B, int d) {
+  E1BwdWs w;
+  return carve_e1_bwd(dtype, T, B, d, nullptr, &w);
+}
+
+int elman_e1_backward(int dtype, int T, int B, int d, const void* W_x, const void* W_h,
+                      const void* x, const void* z, const void* h, const void* v,
+                      const void* d_output, void* dx, void* dz, void* dW_x, void* dW_h, void* db,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (d == 0) return ELMAN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  REQUIRE_PTR(dW_x); REQUIRE_PTR(dW_h); REQUIRE_PTR(db);
+  size_t es = esize(dtype);
+  if (T == 0 || B == 0) {
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_x, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_h, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    return ELMAN_OK;
+  }
+  REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(x); REQUIRE_PTR(z); REQUIRE_PTR(h);
+  REQUIRE_PTR(v); REQUIRE_PTR(d_output); REQUIRE_PTR(dx); REQUIRE_PTR(dz); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E1BwdWs w;
+  size_t need = carve_e1_bwd(dtype, T, B, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  const int TB = T * B;
+  ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
+  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, z, d_output, w.dv, dz, w.db, w.sync, st));
+  ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
+  // dx = dv W_x ; dW_x = dv^T x ; dW_h = dv^T h[0:T]
+  PhaseTimer timer(3, st);
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, w.WxT, dx, d, 0, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, w.dvT, false, w.xT, false, dW_x, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, w.dvT, true, w.xT, false, dW_h, st));
+  return ELMAN_OK;
+}
+
+// ------------------------------- E0 ----------------------------------------
+
+struct E0FwdWs { void* pre; void* gate; int* sync; };
+static size_t carve_e0_fwd(int dtype, int T, int B, int d, void* ws, E0FwdWs* o) {
+  Carver c(ws);
+  o->pre = c.take((size_t)T * B * d * esize(dtype));
+  o->gate = c.take((size_t)T * B * d * esize(dtype));
+  size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
+  o->sync = (int*)c.take(sb);
+  return c.total();
+}
+
+size_t elman_e0_forward_workspace(int dtype, int T, int B, int d) {
+  E0FwdWs w;
+  return carve_e0_fwd(dtype, T, B, d, nullptr, &w);
+}
+
+int elman_e0_forward(int dtype, int training, int T, int B, int d, const void* x, const void* h0,
+                     const void* W_x, const void* W_h, const void* W_gate, const void* b,
+                     const void* b_gate, void* h, void* output, void* v, void* gate_cache,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (B == 0 || d == 0) return ELMAN_OK;
+  REQUIRE_PTR(h0); REQUIRE_PTR(h);
+  cudaStream_t st = (cudaStream_t)stream;
+  ELMAN_RETURN_IF(copy_rows(dtype, h0, h, (long)B * d, st));
+  if (T == 0) return ELMAN_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(W_gate); REQUIRE_PTR(b);
+  REQUIRE_PTR(b_gate); REQUIRE_PTR(output); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(!training || (v != nullptr && gate_cache != nullptr),
+                  "v and gate_cache must be provided when training");
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E0FwdWs w;
+  size_t need = carve_e0_fwd(dtype, T, B, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  void* gate = (training && gate_cache != nullptr) ? gate_cache : w.gate;
+  ELMAN_RETURN_IF(proj_nt(dtype, T * B, d, d, x, d, W_x, d, b, w.pre, d, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, T * B, d, d, x, d, W_gate, d, b_gate, gate, d, 0, st));
+  return run_rec_fwd(dtype, T, B, d, W_h, w.pre, gate, h, output, training ? v : nullptr, w.sync,
+                     st);
+}
+
+struct E0BwdWs {
+  void* Wt; void* dv; void* dg; float* db; float* cs; int* sync;
+  void* WT2; void* dvT; void* xT;
+};
+static size_t carve_e0_bwd(int dtype, int T, int B, int d, void* ws, E0BwdWs* o) {
+  Carver c(ws);
+  size_t es = esize(dtype);
+  o->Wt = c.take((size_t)d * d * es);
+  o->dv = c.take((size_t)(T + 1) * B * d * es);  // slot T: zero "gradient from the future"
+  o->dg = c.take((size_t)T * B * d * es);
+  o->db = (float*)c.take((size_t)d * sizeof(float));
+  o->cs = (float*)c.take(column_sum_scratch_bytes(d));
+  size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
+  o->sync = (int*)c.take(sb);
+  if (dtype == ELMAN_BF16) {
+    o->WT2 = c.take((size_t)d * d * es);
+    o->dvT = c.take((size_t)T * B * d * es);
+    o->xT = c.take((size_t)T * B * d * es);
+  } else {
+    o->WT2 = o->dvT = o->xT = nullptr;
+  }
+  return c.total();
+}
+
+size_t elman_e0_backward_workspace(int dtype, int T, int B, int d) {
+  E0BwdWs w;
+  return carve_e0_bwd(dtype, T, B, d, nullptr, &w);
+}
+
+int elman_e0_backward(int dtype, int T, int B, int d, const void* W_x, const void* W_h,
+                      const void* W_gate, const void* x, const void* h, const void* v,
+                      const void* gate_cache, const void* d_output, void* dx, void* dW_x,
+                      void* dW_h, void* dW_gate, void* db, void* db_gate, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (d == 0) return ELMAN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  REQUIRE_PTR(dW_x); REQUIRE_PTR(dW_h); REQUIRE_PTR(dW_gate); REQUIRE_PTR(db); REQUIRE_PTR(db_gate);
+  size_t es = esize(dtype);
+  if (T == 0 || B == 0) {
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_x, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_h, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_gate, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(db_gate, 0, (size_t)d * es, st));
+    return ELMAN_OK;
+  }
+  REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(W_gate); REQUIRE_PTR(x); REQUIRE_PTR(h);
+  REQUIRE_PTR(v); REQUIRE_PTR(gate_cache); REQUIRE_PTR(d_output); REQUIRE_PTR(dx);
+  REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E0BwdWs w;
+  size_t need = carve_e0_bwd(dtype, T, B, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  const int TB = T * B;
+  ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
+  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, gate_cache, d_output, w.dv, w.dg, w.db,
+                              w.sync, st));
+  ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
+  ELMAN_RETURN_IF(column_sum(dtype, TB, d, w.dg, db_gate, w.cs, st));
+  // dx = dv W_x + dg W_gate
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, w.WT2, dx, d, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dg, d, W_gate, d, w.WT2, dx, d, 1, st));
+  // dW_x = dv^T x ; dW_h = dv^T h[0:T] ; dW_gate = dg^T x
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, w.dvT, false, w.xT, false, dW_x, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dg, x, w.dvT, false, w.xT, true, dW_gate, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, w.dvT, false, w.xT, false, dW_h, st));
+  return ELMAN_OK;
+}
+
+// ------------------------------- E5 ----------------------------------------
+
+struct E5FwdWs { void* Vx; void* pre; void* Vz; void* gate; float* tmp; int* sync; };
+static size_t carve_e5_fwd(int dtype, int T, int B, int d, int r, void* ws, E5FwdWs* o) {
+  Carver c(ws);
+  size_t es = esize(dtype);
+  o->Vx = c.take((size_t)T * B * r * es);
+  o->pre = c.take((size_t)T * B * d * es);
+  o->Vz = c.take((size_t)T * B * r * es);
+  o->gate = c.take((size_t)T * B * d * es);
+  o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
+  o->sync = (int*)c.take(rec_sync_bytes());
+  return c.total();
+}
+
+size_t elman_e5_forward_workspace(int dtype, int T, int B, int d, int r) {
+  E5FwdWs w;
+  return carve_e5_fwd(dtype, T, B, d, r, nullptr, &w);
+}
+
+int elman_e5_forward(int dtype, int training, int T, int B, int d, int r, const void* x,
+                     const void* h0, const void* U_h, const void* V_h, const void* U_x,
+                     const void* V_x, const void* U_z, const void* V_z, const void* b, void* h,
+                     void* output, void* v, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  ELMAN_ARG_CHECK(r >= 1, "rank must be positive (got %d)", r);
+  if (B == 0 || d == 0) return ELMAN_OK;
+  REQUIRE_PTR(h0); REQUIRE_PTR(h);
+  cudaStream_t st = (cudaStream_t)stream;
+  ELMAN_RETURN_IF(copy_rows(dtype, h0, h, (long)B * d, st));
+  if (T == 0) return ELMAN_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(U_h); REQUIRE_PTR(V_h); REQUIRE_PTR(U_x); REQUIRE_PTR(V_x);
+  REQUIRE_PTR(U_z); REQUIRE_PTR(V_z); REQUIRE_PTR(b); REQUIRE_PTR(output); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(!training || v != nullptr, "v must be provided when training");
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E5FwdWs w;
+  size_t need = carve_e5_fwd(dtype, T, B, d, r, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  const int TB = T * B;
+  // pre = (x V_x^T) U_x^T + b ; gate = (x V_z^T) U_z^T
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_x, d, nullptr, w.Vx, r, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vx, r, U_x, r, b, w.pre, d, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_z, d, nullptr, w.Vz, r, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vz, r, U_z, r, nullptr, w.gate, d, 0, st));
+  LowRankFwdArgs a{T, B, d, r, U_h, V_h, w.pre, w.gate, h, output, training ? v : nullptr, w.tmp,
+                   w.sync};
+  return lowrank_fwd_generic(dtype, a, st);
+}
+
+struct E5BwdWs {
+  void* Vz; void* gate; void* Ut; void* Vt; void* dv; void* dg; float* db; float* tmp; int* sync;
+  void* Vx; void* Vh; void* dVx; void* dVz; void* dVh;
+};
+static size_t carve_e5_bwd(int dtype, int T, int B, int d, int r, void* ws, E5BwdWs* o) {
+  Carver c(ws);
+  size_t es = esize(dtype);
+  size_t TBr = (size_t)T * B * r * es, TBd = (size_t)T * B * d * es;
+  o->Vz = c.take(TBr);
+  o->gate = c.take(TBd);
+  o->Ut = c.take((size_t)d * r * es);
+  o->Vt = c.take((size_t)d * r * es);
+  o->dv = c.take(TBd);
+  o->dg = c.take(TBd);
+  o->db = (float*)c.take((size_t)d * sizeof(float));
+  o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
+  o->sync = (int*)c.take(rec_sync_bytes());
+  o->Vx = c.take(TBr);
+  o->Vh = c.take(TBr);
+  o->dVx = c.take(TBr);
+  o->dVz = c.take(TBr);
+  o->dVh = c.take(TBr);
+  return c.total();
+}
+
+size_t elman_e5_backward_workspace(int dtype, int T, int B, int d, int r) {
+  E5BwdWs w;
+  return carve_e5_bwd(dtype, T, B, d, r, nullptr, &w);
+}
+
+int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, const void* V_h,
+                      const void* U_x, const void* V_x, const void* U_z, const void* V_z,
+                      const void* x, const void* h, const void* v, const void* d_output, void* dx,
+                      void* dU_h, void* dV_h, void* dU_x, void* dV_x, void* dU_z, void* dV_z,
+                      void* db, void* workspace, size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  ELMAN_ARG_CHECK(r >= 1, "rank must be positive (got %d)", r);
+  if (d == 0) return ELMAN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  REQUIRE_PTR(dU_h); REQUIRE_PTR(dV_h); REQUIRE_PTR(dU_x); REQUIRE_PTR(dV_x); REQUIRE_PTR(dU_z);
+  REQUIRE_PTR(dV_z); REQUIRE_PTR(db);
+  size_t es = esize(dtype);
+  if (T == 0 || B == 0) {
+    void* outs[6] = {dU_h, dV_h, dU_x, dV_x, dU_z, dV_z};
+    for (void* p : outs) ELMAN_CUDA_CHECK(cudaMemsetAsync(p, 0, (size_t)d * r * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    return ELMAN_OK;
+  }
+  REQUIRE_PTR(U_h); REQUIRE_PTR(V_h); REQUIRE_PTR(U_x); REQUIRE_PTR(V_x); REQUIRE_PTR(U_z);
+  REQUIRE_PTR(V_z); REQUIRE_PTR(x); REQUIRE_PTR(h); REQUIRE_PTR(v); REQUIRE_PTR(d_output);
+  REQUIRE_PTR(dx); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E5BwdWs w;
+  size_t need = carve_e5_bwd(dtype, T, B, d, r, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  const int TB = T * B;
+  // recompute the gate pre-activation (the reference does the same per step)
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_z, d, nullptr, w.Vz, r, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vz, r, U_z, r, nullptr, w.gate, d, 0, st));
+  ELMAN_RETURN_IF(transpose2d(dtype, d, r, U_h, w.Ut, st));  // [r,d]
+  ELMAN_RETURN_IF(transpose2d(dtype, r, d, V_h, w.Vt, st));  // [d,r]
+  LowRankBwdArgs a{T, B, d, r, w.Ut, w.Vt, h, v, w.gate, d_output, w.dv, w.dg, w.db, w.tmp, w.sync};
+  ELMAN_RETURN_IF(lowrank_bwd_generic(dtype, a, st));
+  ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
+  // rank-r activations and their gradients, all time steps at once
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_x, d, nullptr, w.Vx, r, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, h, d, V_h, d, nullptr, w.Vh, r, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, r, d, w.dv, d, U_x, r, nullptr, w.dVx, r, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, r, d, w.dg, d, U_z, r, nullptr, w.dVz, r, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, r, d, w.dv, d, U_h, r, nullptr, w.dVh, r, 0, st));
+  // dx = dVx V_x + dVz V_z
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, r, w.dVx, r, V_x, d, nullptr, dx, d, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, r, w.dVz, r, V_z, d, nullptr, dx, d, 1, st));
+  // weight gradients: sums over all T*B rows
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, r, TB, w.dv, w.Vh, nullptr, false, nullptr, false, dU_h, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, r, d, TB, w.dVh, h, nullptr, false, nullptr, false, dV_h, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, r, TB, w.dv, w.Vx, nullptr, false, nullptr, false, dU_x, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, r, d, TB, w.dVx, x, nullptr, false, nullptr, false, dV_x, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, r, TB, w.dg, w.Vz, nullptr, false, nullptr, false, dU_z, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, r, d, TB, w.dVz, x, nullptr, false, nullptr, false, dV_z, st));
+  return ELMAN_OK;
+}
+
+// --------------------------- projection GEMM --------------------------------
+
+int elman_projection(int dtype, int M, int N, int K, const void* A, int lda, const void* W,
+                     int ldw, const void* bias, void* C, int ldc, int accumulate, void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(M >= 0 && N >= 0 && K >= 0, "negative size");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (M == 0 || N == 0) return ELMAN_OK;
+  REQUIRE_PTR(A); REQUIRE_PTR(W); REQUIRE_PTR(C);
+  ELMAN_ARG_CHECK(lda >= K && ldw >= K && ldc >= N, "row stride smaller than the row");
+  return proj_nt(dtype, M, N, K, A, lda, W, ldw, bias, C, ldc, accumulate, (cudaStream_t)stream);
+}
+
+}  // extern "C"

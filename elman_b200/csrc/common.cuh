@@ -1,0 +1,184 @@
+// Shared declarations of the elman_b200 library: dtype helpers, error plumbing,
+// the bounded-wait status word, and the internal kernel-launcher prototypes.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/elman_b200.h"
+
+namespace elman {
+
+typedef __nv_bfloat16 bf16;
+
+// ---------------------------------------------------------------------------
+// host-side error handling
+// ---------------------------------------------------------------------------
+int set_error(int code, const char* fmt, ...);
+
+#define ELMAN_CUDA_CHECK(expr)                                                        \
+  do {                                                                                \
+    cudaError_t _e = (expr);                                                          \
+    if (_e != cudaSuccess)                                                            \
+      return ::elman::set_error(ELMAN_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,       \
+                                cudaGetErrorString(_e), __FILE__, __LINE__);          \
+  } while (0)
+
+#define ELMAN_RETURN_IF(expr)        \
+  do {                               \
+    int _rc = (expr);                \
+    if (_rc != ELMAN_OK) return _rc; \
+  } while (0)
+
+#define ELMAN_ARG_CHECK(cond, ...) \
+  do {                             \
+    if (!(cond)) return ::elman::set_error(ELMAN_ERR_ARG, __VA_ARGS__); \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// options / counters (api.cu)
+// ---------------------------------------------------------------------------
+struct Options {
+  long force_generic = 0;
+  long spin_limit = 4000000;   // iterations of a device-side poll loop
+  long rec_ksplit = 0;
+  long rec_groups = 0;
+  long time_kernels = 0;
+};
+Options& options();
+void count_launch(bool tensor_core);
+
+// Host-visible status word of the current device (mapped pinned memory).
+// Device code writes a non-zero code there when a bounded wait gives up.
+int* device_status_ptr();   // device-side alias, or nullptr if unavailable
+
+// kernel ids recorded in the status word
+enum KernelId { KID_REC_SIMT = 1, KID_REC_TC_FWD = 2, KID_REC_TC_BWD = 3, KID_GEMM_TC = 4,
+                KID_LOWRANK_SIMT = 5, KID_WAIT_PROBE = 6 };
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + __expf(-z)); }
+__device__ __forceinline__ float siluf_(float z) { return z * sigmoidf_(z); }
+__device__ __forceinline__ float dsiluf_(float z) {
+  float s = sigmoidf_(z);
+  return s * (1.0f + z * (1.0f - s));
+}
+
+__device__ __forceinline__ void report_timeout(int* status, int kernel_id, int step) {
+  if (status != nullptr) {
+    atomicCAS(status, 0, (kernel_id << 24) | (step & 0xFFFFFF));
+    __threadfence_system();
+  }
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// internal launchers (each returns ELMAN_OK or an error code)
+// ---------------------------------------------------------------------------
+
+// C[m,n] = sum_k A(m,k) * B(k,n) (+ bias[n]) (+ C[m,n]); arbitrary element strides.
+int gemm_generic(int dtype, int M, int N, int K, const void* A, long sAm, long sAk,
+                 const void* B, long sBk, long sBn, const void* bias, void* C, long ldc,
+                 int accumulate, cudaStream_t stream);
+
+// C[M,N] = A[M,K] * W[N,K]^T, bf16, TMA + tcgen05.  Returns ELMAN_ERR_UNSUPPORTED
+// (without setting an error message) when the shape or alignment rules it out.
+int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int ldw,
+               const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
+               cudaStream_t stream);
+bool gemm_tc_supported(int M, int N, int K, const void* A, int lda, const void* W, int ldw,
+                       const void* C, int ldc, int c_is_f32);
+
+// out[rows, cols] = in[cols, rows]^T for a dense row-major matrix.
+int transpose2d(int dtype, int rows_in, int cols_in, const void* in, void* out,
+                cudaStream_t stream);
+// out[n] = sum_m in[m, n]  (deterministic two-pass; scratch holds 64*N floats).
+int column_sum(int dtype, long M, int N, const void* in, void* out, float* scratch,
+               cudaStream_t stream);
+size_t column_sum_scratch_bytes(int N);
+int copy_rows(int dtype, const void* src, void* dst, long n, cudaStream_t stream);
+int float_to_dtype(int dtype, const float* src, void* dst, long n, cudaStream_t stream);
+
+// Dense recurrence, CUDA-core persistent kernel.
+//   forward : h[t+1] = tanh(pre[t] + h[t] W^T);  y[t] = h[t+1] * silu(g[t])
+//   backward: dv[t] = (dy[t]*silu(g[t]) + dv[t+1] Wt^T) * (1 - tanh(v[t])^2), dg[t] = dy*h*silu'(g)
+struct RecFwdArgs {
+  int T, B, d;
+  const void* W;      // [d,d] recurrent matrix ([out,in])
+  const void* pre;    // [T,B,d] W_x x_t + b
+  const void* g;      // [T,B,d] gate pre-activation
+  void* h;            // [T+1,B,d], h[0] already holds h0
+  void* y;            // [T,B,d]
+  void* v;            // [T,B,d] or null
+  int* sync;          // zeroed ints (barrier / step counters)
+};
+struct RecBwdArgs {
+  int T, B, d;
+  const void* Wt;     // [d,d] transpose of the recurrent matrix ([in,out])
+  const void* h;      // [T+1,B,d]
+  const void* v;      // [T,B,d]
+  const void* g;      // [T,B,d]
+  const void* dy;     // [T,B,d]
+  void* dv;           // [T,B,d]
+  void* dg;           // [T,B,d]
+  float* db;          // [d] fp32 sum over t,b of dv
+  int* sync;
+};
+size_t rec_sync_bytes();
+int rec_fwd_generic(int dtype, const RecFwdArgs& a, cudaStream_t stream);
+int rec_bwd_generic(int dtype, const RecBwdArgs& a, cudaStream_t stream);
+
+// Low-rank (E5) recurrence, CUDA-core persistent kernel: the recurrent term is
+// U (V state) with V:[r,d], U:[d,r]; tmp holds the rank-r intermediate [B,r] floats x2.
+struct LowRankFwdArgs {
+  int T, B, d, r;
+  const void* U;      // [d,r]
+  const void* V;      // [r,d]
+  const void* pre; const void* g; void* h; void* y; void* v;
+  float* tmp;         // 2*B*r floats
+  int* sync;
+};
+struct LowRankBwdArgs {
+  int T, B, d, r;
+  const void* Ut;     // [r,d] = U^T
+  const void* Vt;     // [d,r] = V^T
+  const void* h; const void* v; const void* g; const void* dy;
+  void* dv; void* dg; float* db;
+  float* tmp;
+  int* sync;
+};
+int lowrank_fwd_generic(int dtype, const LowRankFwdArgs& a, cudaStream_t stream);
+int lowrank_bwd_generic(int dtype, const LowRankBwdArgs& a, cudaStream_t stream);
+
+// Dense recurrence, bf16, tcgen05 + TMA persistent cluster kernel.
+bool rec_tc_supported(int T, int B, int d);
+size_t rec_tc_sync_bytes();
+int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream);
+int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream);
+
+}  // namespace elman

@@ -1,0 +1,287 @@
+// Time-parallel projection GEMM on the sm_100a tensor cores:
+//   C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) (+ C)
+// bf16 operands, fp32 accumulation in tensor memory, bias / accumulate / down-cast
+// fused into the epilogue.  This replaces the cuBLAS calls the reference makes for
+// W_x x_t over all t, the gate projection, dx, dW_x and dW_h
+// (elman/cuda/lib/mamba_gated_elman_gpu.cu.cc:440-448, :561-589; blas.h:51-72).
+//
+// One CTA computes one 128x128 tile.  Thread 0 of warp 0 streams 128x64 operand
+// tiles with TMA (128-byte swizzle) through a 3-stage mbarrier ring, thread 0 of
+// warp 1 issues tcgen05.mma (M=128, N=128, K=16) into a 128-column TMEM
+// accumulator, and all four warps drain it with tcgen05.ld.  Two CTAs fit on an
+// SM, so one tile's epilogue overlaps the other's main loop.  No multicast is used.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace elman {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int STAGES = 3;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+constexpr int B_TILE_BYTES = BN * BK * 2;
+constexpr int GEMM_SMEM = STAGES * (A_TILE_BYTES + B_TILE_BYTES) + 1024;  // + alignment slack
+constexpr uint32_t TMEM_COLS = 128;
+
+struct GemmParams {
+  int M, N, K;
+  const bf16* bias;
+  void* C;
+  long ldc;
+  int c_is_f32;
+  int accumulate;
+  long spin_limit;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(128)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_TILE_BYTES;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int nk = (p.K + BK - 1) / BK;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    ptx::mbar_init(&acc_bar, 1);
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmA);
+    ptx::prefetch_tmap(&tmB);
+  }
+  if (warp == 0) {
+    ptx::tmem_alloc(&tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nk; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+        if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, p.spin_limit, abortp)) {
+          abort_flag = 1;
+          report_timeout(p.status, KID_GEMM_TC, i);
+          break;
+        }
+        ptx::mbar_arrive_expect_tx(&full_bar[s], A_TILE_BYTES + B_TILE_BYTES);
+        ptx::tma_load_2d(sA + s * A_TILE_BYTES, &tmA, i * BK, m0, &full_bar[s]);
+        ptx::tma_load_2d(sB + s * B_TILE_BYTES, &tmB, i * BK, n0, &full_bar[s]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < nk && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+        if (!ptx::mbar_wait(&full_bar[s], ph, p.spin_limit, abortp)) {
+          abort_flag = 1;
+          report_timeout(p.status, KID_GEMM_TC, i);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(sA + s * A_TILE_BYTES));
+        const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(sB + s * B_TILE_BYTES));
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {
+          // 16 bf16 along K = 32 bytes = 2 descriptor address units
+          ptx::umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        ptx::umma_commit(&empty_bar[s]);  // frees the stage when these MMAs retire
+      }
+      if (ok) ptx::umma_commit(&acc_bar);
+    }
+    __syncwarp();
+  }
+
+  // ----- epilogue: all four warps, warp w owns TMEM lanes [32w, 32w+32) -----
+  bool ok = ptx::mbar_wait(&acc_bar, 0, p.spin_limit * 8, abortp);
+  if (!ok && abort_flag == 0) {
+    abort_flag = 1;
+    report_timeout(p.status, KID_GEMM_TC, 0xFFFF);
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  ptx::tc_fence_after();
+  if (ok) {
+    const int gm = m0 + warp * 32 + lane;
+    const bool vec_ok = ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0);
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
+      ptx::tmem_ld_wait();
+      const int gn0 = n0 + c * 32;
+      if (gm < p.M && gn0 < p.N) {
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+        const bool full = gn0 + 32 <= p.N;
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (full || gn0 + j < p.N) f[j] += __bfloat162float(p.bias[gn0 + j]);
+        }
+        if (p.c_is_f32) {
+          float* crow = (float*)p.C + (long)gm * p.ldc + gn0;
+          if (full && ((p.ldc & 3) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+              if (p.accumulate) {
+                float4 old = *reinterpret_cast<float4*>(crow + j);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(crow + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && gn0 + j < p.N; ++j)
+              crow[j] = p.accumulate ? crow[j] + f[j] : f[j];
+          }
+        } else {
+          bf16* crow = (bf16*)p.C + (long)gm * p.ldc + gn0;
+          if (full && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (p.accumulate) {
+                uint4 old = *reinterpret_cast<uint4*>(crow + j);
+                const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  float2 of = __bfloat1622float2(o2[q]);
+                  f[j + 2 * q] += of.x;
+                  f[j + 2 * q + 1] += of.y;
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16(f[j], f[j + 1]);
+              o.y = pack_bf16(f[j + 2], f[j + 3]);
+              o.z = pack_bf16(f[j + 4], f[j + 5]);
+              o.w = pack_bf16(f[j + 6], f[j + 7]);
+              *reinterpret_cast<uint4*>(crow + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && gn0 + j < p.N; ++j) {
+              float val = p.accumulate ? f[j] + __bfloat162float(crow[j]) : f[j];
+              crow[j] = __float2bfloat16_rn(val);
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // Give copies that may still be in flight time to land before the CTA's
+    // shared memory and tensor memory are released.
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = (EncodeTiledFn)ptr;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return fn;
+}
+
+}  // namespace
+
+int make_tmap_bf16_sw128(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                         uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr)
+    return set_error(ELMAN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return set_error(ELMAN_ERR_CUDA,
+                     "cuTensorMapEncodeTiled failed (%d) for [%llu x %llu] ld=%llu box_rows=%u",
+                     (int)rc, (unsigned long long)rows, (unsigned long long)cols,
+                     (unsigned long long)ld, box_rows);
+  return ELMAN_OK;
+}
+
+bool gemm_tc_supported(int M, int N, int K, const void* A, int lda, const void* W, int ldw,
+                       const void* C, int ldc, int c_is_f32) {
+  (void)C; (void)ldc; (void)c_is_f32;
+  if (M < 1 || N < 1 || K < 8) return false;
+  if ((K & 7) != 0 || (lda & 7) != 0 || (ldw & 7) != 0) return false;
+  if (((uintptr_t)A & 15) != 0 || ((uintptr_t)W & 15) != 0) return false;
+  return get_encode_fn() != nullptr;
+}
+
+int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int ldw,
+               const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
+               cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    ELMAN_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          GEMM_SMEM));
+    attr_set = true;
+  }
+  CUtensorMap tmA, tmB;
+  ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM));
+  ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN));
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.bias = bias; p.C = C; p.ldc = ldc; p.c_is_f32 = c_is_f32; p.accumulate = accumulate;
+  p.spin_limit = options().spin_limit;
+  p.status = device_status_ptr();
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, p);
+  count_launch(true);
+  ELMAN_CUDA_CHECK(cudaGetLastError());
+  return ELMAN_OK;
+}
+
+}  // namespace elman

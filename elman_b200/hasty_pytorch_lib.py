@@ -1,0 +1,244 @@
+"""Drop-in for the reference's `hasty_pytorch_lib` extension module (E0 / E1 / E5 only).
+
+Same function names, positional arguments and return lists as the pybind11
+functions of the reference (elman/cuda/pytorch/elman_ladder.cc:22-281 and
+:2802-3103, registered at :16539-16591).  Each function allocates its outputs
+and scratch with PyTorch's caching allocator, as the reference does with
+torch::empty, and enqueues the work of libelman_b200 on PyTorch's current CUDA
+stream.  Inputs must be CUDA and contiguous (the reference's CHECK_INPUT,
+support.h:21-23); shapes and dtypes are cross-checked as well, which the
+reference does not do.  fp32 and bf16 are accepted; fp16/fp64 raise.
+
+Use `elman_b200.install_as_hasty()` to make `import hasty_pytorch_lib` resolve
+to this module, so the reference's model files pick it up unchanged.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float32: _lib.ELMAN_F32, torch.bfloat16: _lib.ELMAN_BF16}
+
+
+def _check_inputs(fn, ref, **tensors):
+    for name, t in tensors.items():
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{fn}: {name} must be a Tensor")
+        if not t.is_cuda:
+            raise RuntimeError(f"{fn}: {name} must be a CUDA tensor")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{fn}: {name} must be contiguous")
+        if t.dtype != ref.dtype:
+            raise RuntimeError(f"{fn}: {name} has dtype {t.dtype}, expected {ref.dtype}")
+        if t.device != ref.device:
+            raise RuntimeError(f"{fn}: {name} is on {t.device}, expected {ref.device}")
+    if ref.dtype not in _DT:
+        raise RuntimeError(f"{fn}: dtype {ref.dtype} is not supported (float32 and bfloat16 are)")
+    return _DT[ref.dtype]
+
+
+def _shape(fn, t, shape, name):
+    if tuple(t.shape) != tuple(shape):
+        raise RuntimeError(f"{fn}: {name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+def _ptr(t):
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _stream(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# --------------------------------------------------------------------------- E1
+
+def mamba_gated_elman_forward(training, x, z, h0, W_x, W_h, b):
+    """-> [h[T+1,B,d], output[T,B,d], v[T,B,d] (empty if not training)]"""
+    fn = "mamba_gated_elman_forward"
+    dt = _check_inputs(fn, x, x=x, z=z, h0=h0, W_x=W_x, W_h=W_h, b=b)
+    if x.dim() != 3:
+        raise RuntimeError(f"{fn}: x must be [T, B, dim]")
+    T, B, d = x.shape
+    _shape(fn, z, (T, B, d), "z"); _shape(fn, h0, (B, d), "h0")
+    _shape(fn, W_x, (d, d), "W_x"); _shape(fn, W_h, (d, d), "W_h"); _shape(fn, b, (d,), "b")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        h = torch.empty(T + 1, B, d, dtype=x.dtype, device=x.device)
+        out = torch.empty(T, B, d, dtype=x.dtype, device=x.device)
+        v = torch.empty((T, B, d) if training else (0,), dtype=x.dtype, device=x.device)
+        nws = lib.elman_e1_forward_workspace(dt, T, B, d)
+        ws = _workspace(nws, x.device)
+        rc = lib.elman_e1_forward(dt, 1 if training else 0, T, B, d, _ptr(x), _ptr(z), _ptr(h0),
+                                  _ptr(W_x), _ptr(W_h), _ptr(b), _ptr(h), _ptr(out), _ptr(v),
+                                  ws.data_ptr(), ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [h, out, v]
+
+
+def mamba_gated_elman_backward(W_x, W_h, x, z, h, v, d_output):
+    """-> [dx, dz, dW_x, dW_h, db]"""
+    fn = "mamba_gated_elman_backward"
+    dt = _check_inputs(fn, x, W_x=W_x, W_h=W_h, x=x, z=z, h=h, v=v, d_output=d_output)
+    T, B, d = x.shape
+    _shape(fn, z, (T, B, d), "z"); _shape(fn, h, (T + 1, B, d), "h")
+    _shape(fn, v, (T, B, d), "v"); _shape(fn, d_output, (T, B, d), "d_output")
+    _shape(fn, W_x, (d, d), "W_x"); _shape(fn, W_h, (d, d), "W_h")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        dx = torch.empty_like(x)
+        dz = torch.empty_like(z)
+        dW_x = torch.empty(d, d, dtype=x.dtype, device=x.device)
+        dW_h = torch.empty(d, d, dtype=x.dtype, device=x.device)
+        db = torch.empty(d, dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e1_backward_workspace(dt, T, B, d), x.device)
+        rc = lib.elman_e1_backward(dt, T, B, d, _ptr(W_x), _ptr(W_h), _ptr(x), _ptr(z), _ptr(h),
+                                   _ptr(v), _ptr(d_output), _ptr(dx), _ptr(dz), _ptr(dW_x),
+                                   _ptr(dW_h), _ptr(db), ws.data_ptr(), ws.numel(),
+                                   _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [dx, dz, dW_x, dW_h, db]
+
+
+# --------------------------------------------------------------------------- E0
+
+def stock_elman_forward(training, x, h0, W_x, W_h, W_gate, b, b_gate):
+    """-> [h, output, v, gate_cache] (v, gate_cache empty if not training)"""
+    fn = "stock_elman_forward"
+    dt = _check_inputs(fn, x, x=x, h0=h0, W_x=W_x, W_h=W_h, W_gate=W_gate, b=b, b_gate=b_gate)
+    if x.dim() != 3:
+        raise RuntimeError(f"{fn}: x must be [T, B, dim]")
+    T, B, d = x.shape
+    _shape(fn, h0, (B, d), "h0")
+    for name, w in (("W_x", W_x), ("W_h", W_h), ("W_gate", W_gate)):
+        _shape(fn, w, (d, d), name)
+    _shape(fn, b, (d,), "b"); _shape(fn, b_gate, (d,), "b_gate")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        h = torch.empty(T + 1, B, d, dtype=x.dtype, device=x.device)
+        out = torch.empty(T, B, d, dtype=x.dtype, device=x.device)
+        v = torch.empty((T, B, d) if training else (0,), dtype=x.dtype, device=x.device)
+        gc = torch.empty((T, B, d) if training else (0,), dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e0_forward_workspace(dt, T, B, d), x.device)
+        rc = lib.elman_e0_forward(dt, 1 if training else 0, T, B, d, _ptr(x), _ptr(h0), _ptr(W_x),
+                                  _ptr(W_h), _ptr(W_gate), _ptr(b), _ptr(b_gate), _ptr(h),
+                                  _ptr(out), _ptr(v), _ptr(gc), ws.data_ptr(), ws.numel(),
+                                  _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [h, out, v, gc]
+
+
+def stock_elman_backward(W_x, W_h, W_gate, x, h, v, gate_cache, d_output):
+    """-> [dx, dW_x, dW_h, dW_gate, db, db_gate]"""
+    fn = "stock_elman_backward"
+    dt = _check_inputs(fn, x, W_x=W_x, W_h=W_h, W_gate=W_gate, x=x, h=h, v=v,
+                       gate_cache=gate_cache, d_output=d_output)
+    T, B, d = x.shape
+    _shape(fn, h, (T + 1, B, d), "h"); _shape(fn, v, (T, B, d), "v")
+    _shape(fn, gate_cache, (T, B, d), "gate_cache"); _shape(fn, d_output, (T, B, d), "d_output")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        dx = torch.empty_like(x)
+        dW_x, dW_h, dW_gate = (torch.empty(d, d, dtype=x.dtype, device=x.device) for _ in range(3))
+        db, db_gate = (torch.empty(d, dtype=x.dtype, device=x.device) for _ in range(2))
+        ws = _workspace(lib.elman_e0_backward_workspace(dt, T, B, d), x.device)
+        rc = lib.elman_e0_backward(dt, T, B, d, _ptr(W_x), _ptr(W_h), _ptr(W_gate), _ptr(x),
+                                   _ptr(h), _ptr(v), _ptr(gate_cache), _ptr(d_output), _ptr(dx),
+                                   _ptr(dW_x), _ptr(dW_h), _ptr(dW_gate), _ptr(db), _ptr(db_gate),
+                                   ws.data_ptr(), ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [dx, dW_x, dW_h, dW_gate, db, db_gate]
+
+
+# --------------------------------------------------------------------------- E5
+
+def pure_lowrank_elman_forward(training, x, h0, U_h, V_h, U_x, V_x, U_z, V_z, b):
+    """-> [h, output, v]"""
+    fn = "pure_lowrank_elman_forward"
+    dt = _check_inputs(fn, x, x=x, h0=h0, U_h=U_h, V_h=V_h, U_x=U_x, V_x=V_x, U_z=U_z, V_z=V_z,
+                       b=b)
+    if x.dim() != 3:
+        raise RuntimeError(f"{fn}: x must be [T, B, dim]")
+    T, B, d = x.shape
+    r = U_h.shape[1] if U_h.dim() == 2 else -1
+    for name, u in (("U_h", U_h), ("U_x", U_x), ("U_z", U_z)):
+        _shape(fn, u, (d, r), name)
+    for name, vv in (("V_h", V_h), ("V_x", V_x), ("V_z", V_z)):
+        _shape(fn, vv, (r, d), name)
+    _shape(fn, h0, (B, d), "h0"); _shape(fn, b, (d,), "b")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        h = torch.empty(T + 1, B, d, dtype=x.dtype, device=x.device)
+        out = torch.empty(T, B, d, dtype=x.dtype, device=x.device)
+        v = torch.empty((T, B, d) if training else (0,), dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e5_forward_workspace(dt, T, B, d, r), x.device)
+        rc = lib.elman_e5_forward(dt, 1 if training else 0, T, B, d, r, _ptr(x), _ptr(h0),
+                                  _ptr(U_h), _ptr(V_h), _ptr(U_x), _ptr(V_x), _ptr(U_z), _ptr(V_z),
+                                  _ptr(b), _ptr(h), _ptr(out), _ptr(v), ws.data_ptr(), ws.numel(),
+                                  _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [h, out, v]
+
+
+def pure_lowrank_elman_backward(U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, d_output):
+    """-> [dx, dU_h, dV_h, dU_x, dV_x, dU_z, dV_z, db]"""
+    fn = "pure_lowrank_elman_backward"
+    dt = _check_inputs(fn, x, U_h=U_h, V_h=V_h, U_x=U_x, V_x=V_x, U_z=U_z, V_z=V_z, x=x, h=h, v=v,
+                       d_output=d_output)
+    T, B, d = x.shape
+    r = U_h.shape[1]
+    _shape(fn, h, (T + 1, B, d), "h"); _shape(fn, v, (T, B, d), "v")
+    _shape(fn, d_output, (T, B, d), "d_output")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        dx = torch.empty_like(x)
+        dU = [torch.empty(d, r, dtype=x.dtype, device=x.device) for _ in range(3)]
+        dV = [torch.empty(r, d, dtype=x.dtype, device=x.device) for _ in range(3)]
+        db = torch.empty(d, dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e5_backward_workspace(dt, T, B, d, r), x.device)
+        rc = lib.elman_e5_backward(dt, T, B, d, r, _ptr(U_h), _ptr(V_h), _ptr(U_x), _ptr(V_x),
+                                   _ptr(U_z), _ptr(V_z), _ptr(x), _ptr(h), _ptr(v), _ptr(d_output),
+                                   _ptr(dx), _ptr(dU[0]), _ptr(dV[0]), _ptr(dU[1]), _ptr(dV[1]),
+                                   _ptr(dU[2]), _ptr(dV[2]), _ptr(db), ws.data_ptr(), ws.numel(),
+                                   _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [dx, dU[0], dV[0], dU[1], dV[1], dU[2], dV[2], db]
+
+
+# The reference exposes the fused E5 kernels under separate names; here both
+# names run the same (already fused) path.
+pure_lowrank_elman_forward_fused = pure_lowrank_elman_forward
+pure_lowrank_elman_backward_fused = pure_lowrank_elman_backward
+
+
+# ------------------------------------------------------------------ projection
+
+def projection(A, W, bias=None, out=None, accumulate=False):
+    """out[M,N] = A[M,K] @ W[N,K]^T (+ bias) (+ out) through elman_projection."""
+    fn = "projection"
+    tensors = dict(A=A, W=W)
+    if bias is not None:
+        tensors["bias"] = bias
+    dt = _check_inputs(fn, A, **tensors)
+    M, K = A.shape
+    N = W.shape[0]
+    _shape(fn, W, (N, K), "W")
+    if out is None:
+        out = torch.empty(M, N, dtype=A.dtype, device=A.device)
+        accumulate = False
+    lib = _lib.load()
+    with torch.cuda.device(A.device):
+        rc = lib.elman_projection(dt, M, N, K, _ptr(A), K, _ptr(W), K, _ptr(bias), _ptr(out), N,
+                                  1 if accumulate else 0, _stream(A.device))
+        _lib.check(rc, fn)
+    return out

@@ -1,0 +1,186 @@
+/*
+ * elman_b200 — C ABI of the B200 (sm_100a) Elman-layer recurrence library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, a cudaStream_t).  All tensors are dense, row-major and
+ * time-major: x[T,B,d] means element (t,b,i) lives at ((t*B)+b)*d+i.
+ * `dtype` selects the storage type of every tensor of a call:
+ *   ELMAN_F32  : float storage, float arithmetic (CUDA cores)
+ *   ELMAN_BF16 : __nv_bfloat16 storage, float accumulation (tcgen05 tensor
+ *                cores where the shape allows it, CUDA cores otherwise)
+ * The library never allocates device memory inside a compute call: the caller
+ * provides `workspace` of at least the size the matching *_workspace()
+ * function returns, 256-byte aligned.  Work is enqueued on `stream` and the
+ * call returns without synchronising.  Return value: ELMAN_OK or an error code;
+ * elman_b200_last_error() gives the message of the calling thread's last error.
+ *
+ * Each function names the entry point of the reference (ekg/elman) it
+ * replaces; the reference binds those through pybind11 in
+ * elman/cuda/pytorch/elman_ladder.cc and implements them in elman/cuda/lib/.
+ */
+#ifndef ELMAN_B200_H_
+#define ELMAN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ELMAN_OK 0
+#define ELMAN_ERR_ARG 1        /* bad shape, null pointer, misaligned buffer, unknown dtype */
+#define ELMAN_ERR_CUDA 2       /* a CUDA runtime/driver call failed */
+#define ELMAN_ERR_TIMEOUT 3    /* a bounded device-side wait gave up in an earlier launch */
+#define ELMAN_ERR_WORKSPACE 4  /* workspace too small */
+#define ELMAN_ERR_UNSUPPORTED 5
+
+#define ELMAN_F32 0
+#define ELMAN_BF16 1
+
+/* Library version (major*100 + minor). */
+int elman_b200_version(void);
+
+/* Message of the last error raised on the calling thread ("" if none). */
+const char* elman_b200_last_error(void);
+
+/*
+ * Device-side waits (grid barrier, mbarrier polls, step flags) are bounded.  A
+ * wait that gives up records a code in a host-visible status word and makes the
+ * kernel return early.  This call reads that word for the current device
+ * without synchronising: returns ELMAN_OK, or ELMAN_ERR_TIMEOUT with the
+ * recorded detail (kernel id << 24 | step) in *detail.  `clear` != 0 resets it.
+ * The compute entry points also check it on entry.
+ */
+int elman_b200_device_status(int* detail, int clear);
+
+/*
+ * Tuning and test knobs (process-wide):
+ *   "force_generic"  1 = always take the CUDA-core kernels, 0 = default
+ *   "spin_limit"     iteration cap of every device-side wait
+ *   "rec_ksplit"     K-split (cluster size) of the tensor-core recurrence, 0 = auto
+ *   "rec_groups"     independent batch groups pipelined by the recurrence, 0 = auto
+ *   "time_kernels"   1 = bracket the phases of E1/E0 calls with CUDA events
+ * Returns ELMAN_OK or ELMAN_ERR_ARG for an unknown name.
+ */
+int elman_b200_set_option(const char* name, long value);
+long elman_b200_get_option(const char* name);
+
+/*
+ * Failure-detection test hook (no counterpart in the reference): launches one
+ * tiny kernel that waits, for at most `spin_limit` polls, on a flag nothing
+ * sets, then records ELMAN_ERR_TIMEOUT in the status word and returns.
+ * `scratch` is 8 bytes of device memory; scratch[1] is set to 1 when the wait
+ * gave up.  The device and context stay usable.
+ */
+int elman_b200_wait_probe(long spin_limit, void* scratch, void* stream);
+
+/*
+ * Measurement hook (no counterpart in the reference).  With option
+ * "time_kernels" set, the dense-cell entry points record CUDA events on the
+ * caller's stream around their phases: 0 forward recurrence kernel, 1 backward
+ * recurrence kernel, 2 forward projection GEMM, 3 backward GEMMs.  This call
+ * waits for the phase's stop event and returns the elapsed milliseconds of the
+ * most recent call.
+ */
+int elman_b200_last_timing(int phase, float* ms);
+
+/* Number of this library's kernel launches since load (for launch accounting). */
+long elman_b200_launch_count(void);
+/* Of those, launches that took a tcgen05 tensor-core kernel. */
+long elman_b200_tc_launch_count(void);
+
+/* ---------------------------------------------------------------------------
+ * E1 — gated Elman cell.
+ *   h_t = tanh(W_x x_t + W_h h_{t-1} + b),  y_t = h_t * silu(z_t)
+ * Replaces mamba_gated_elman_forward / mamba_gated_elman_backward
+ * (elman/cuda/pytorch/elman_ladder.cc:161-217, :219-281), i.e.
+ * MambaGatedElmanForward<T>::Run / MambaGatedElmanBackward<T>::Run
+ * (elman/cuda/lib/mamba_gated_elman_gpu.cu.cc:417-474, :492-593).
+ *   x,z,output,v : [T,B,d]   h : [T+1,B,d] (h[0] is written from h0)
+ *   W_x,W_h : [d,d] ([out,in])   b : [d]   h0 : [B,d]
+ * `v` (pre-activations) may be NULL when training == 0.
+ * Backward ignores the gradient of h, as the reference does, and returns
+ * dx,dz : [T,B,d], dW_x,dW_h : [d,d], db : [d] (all overwritten).
+ * ------------------------------------------------------------------------- */
+size_t elman_e1_forward_workspace(int dtype, int T, int B, int d);
+int elman_e1_forward(int dtype, int training, int T, int B, int d,
+                     const void* x, const void* z, const void* h0,
+                     const void* W_x, const void* W_h, const void* b,
+                     void* h, void* output, void* v,
+                     void* workspace, size_t workspace_bytes, void* stream);
+size_t elman_e1_backward_workspace(int dtype, int T, int B, int d);
+int elman_e1_backward(int dtype, int T, int B, int d,
+                      const void* W_x, const void* W_h, const void* x, const void* z,
+                      const void* h, const void* v, const void* d_output,
+                      void* dx, void* dz, void* dW_x, void* dW_h, void* db,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * E0 — stock Elman cell with a learned, x-only output gate.
+ *   h_t as E1,  y_t = h_t * silu(W_gate x_t + b_gate)
+ * Replaces stock_elman_forward / stock_elman_backward
+ * (elman/cuda/pytorch/elman_ladder.cc:22-84, :86-155), i.e.
+ * StockElmanForward<T>::Run / StockElmanBackward<T>::Run
+ * (elman/cuda/lib/stock_elman_gpu.cu.cc:214-296, :322-472).
+ * gate_cache[T,B,d] holds W_gate x_t + b_gate; it and v are required when
+ * training != 0 and may be NULL otherwise.
+ * ------------------------------------------------------------------------- */
+size_t elman_e0_forward_workspace(int dtype, int T, int B, int d);
+int elman_e0_forward(int dtype, int training, int T, int B, int d,
+                     const void* x, const void* h0,
+                     const void* W_x, const void* W_h, const void* W_gate,
+                     const void* b, const void* b_gate,
+                     void* h, void* output, void* v, void* gate_cache,
+                     void* workspace, size_t workspace_bytes, void* stream);
+size_t elman_e0_backward_workspace(int dtype, int T, int B, int d);
+int elman_e0_backward(int dtype, int T, int B, int d,
+                      const void* W_x, const void* W_h, const void* W_gate,
+                      const void* x, const void* h, const void* v,
+                      const void* gate_cache, const void* d_output,
+                      void* dx, void* dW_x, void* dW_h, void* dW_gate,
+                      void* db, void* db_gate,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * E5 — pure low-rank Elman cell (no dense matrix anywhere).
+ *   h_t = tanh(U_h (V_h h_{t-1}) + U_x (V_x x_t) + b),  y_t = h_t * silu(U_z (V_z x_t))
+ * Replaces pure_lowrank_elman_forward[_fused] / pure_lowrank_elman_backward[_fused]
+ * (elman/cuda/pytorch/elman_ladder.cc:2802-2948, :2956-3103), i.e.
+ * PureLowRankElmanForwardFused<T>::Run / PureLowRankElmanBackwardFused<T>::Run
+ * (elman/cuda/lib/pure_lowrank_elman_fused_gpu.cu.cc:170-271, :295-505).
+ *   U_* : [d,r]   V_* : [r,d]
+ * ------------------------------------------------------------------------- */
+size_t elman_e5_forward_workspace(int dtype, int T, int B, int d, int r);
+int elman_e5_forward(int dtype, int training, int T, int B, int d, int r,
+                     const void* x, const void* h0,
+                     const void* U_h, const void* V_h, const void* U_x, const void* V_x,
+                     const void* U_z, const void* V_z, const void* b,
+                     void* h, void* output, void* v,
+                     void* workspace, size_t workspace_bytes, void* stream);
+size_t elman_e5_backward_workspace(int dtype, int T, int B, int d, int r);
+int elman_e5_backward(int dtype, int T, int B, int d, int r,
+                      const void* U_h, const void* V_h, const void* U_x, const void* V_x,
+                      const void* U_z, const void* V_z,
+                      const void* x, const void* h, const void* v, const void* d_output,
+                      void* dx, void* dU_h, void* dV_h, void* dU_x, void* dV_x,
+                      void* dU_z, void* dV_z, void* db,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Time-parallel projection  C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) (+ C).
+ * This is the GEMM the reference issues through cuBLAS for W_x x_t over all t
+ * and for the gate projection (blas<T>::gemm, elman/cuda/lib/blas.h:20-173;
+ * call sites mamba_gated_elman_gpu.cu.cc:440-448, stock_elman_gpu.cu.cc:245-264).
+ * Row strides lda/ldw/ldc are in elements.  bias may be NULL.  accumulate != 0
+ * adds into the existing C.  bf16 calls take the TMA + tcgen05 kernel when
+ * K % 64 == 0 and the pointers/strides are 16-byte aligned.
+ * ------------------------------------------------------------------------- */
+int elman_projection(int dtype, int M, int N, int K,
+                     const void* A, int lda, const void* W, int ldw,
+                     const void* bias, void* C, int ldc, int accumulate, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ELMAN_B200_H_ */

@@ -1,0 +1,166 @@
+"""E1 parity on the GPU: CUDA library (through the C ABI) vs the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from elman_b200 import _lib
+from elman_b200 import hasty_pytorch_lib as H
+from oracle import elman_oracle as orc
+from tests._gpu_cases import TOL, assert_close, errors, option, oracle_e1, run_e1
+
+pytestmark = pytest.mark.gpu
+
+FWD_BWD_KEYS = ["h", "output", "v", "dx", "dz", "dW_x", "dW_h", "db"]
+
+
+@pytest.mark.parametrize("T,B,d", [(1, 1, 8), (5, 3, 33), (16, 4, 64), (12, 9, 130), (40, 2, 256)])
+def test_fp32_matches_oracle(T, B, d):
+    inp = orc.make_e1_inputs(T, B, d, seed=100 + d)
+    got, ref = run_e1(inp, torch.float32)
+    assert_close(errors(got, oracle_e1(ref)), TOL[torch.float32], f"fp32 T{T} B{B} d{d}")
+
+
+def test_fp32_config0_matches_reference_fixture(golden_dir):
+    """configs[0]: fp32, B=4, T=128, d=256 against the reference's own outputs."""
+    d = np.load(os.path.join(golden_dir, "e1_c0.npz"))
+    T, B, dim, seed = (int(v) for v in d["meta"])
+    inp = orc.make_e1_inputs(T, B, dim, seed=seed)
+    got, _ = run_e1(inp, torch.float32)
+    want = {k[4:]: torch.from_numpy(d[k]) for k in d.files if k.startswith("out_")}
+    assert_close(errors(got, want), TOL[torch.float32], "config0 vs reference fixture")
+
+
+@pytest.mark.parametrize("name", ["e1_small", "e1_h0"])
+def test_fp32_small_reference_fixtures(golden_dir, name):
+    d = np.load(os.path.join(golden_dir, name + ".npz"))
+    inp = {k[3:]: torch.from_numpy(d[k]) for k in d.files if k.startswith("in_")}
+    want = {k[4:]: torch.from_numpy(d[k]) for k in d.files if k.startswith("out_")}
+    got, _ = run_e1(inp, torch.float32)
+    assert_close(errors(got, want), TOL[torch.float32], name)
+
+
+@pytest.mark.parametrize("T,B,d", [(7, 3, 40), (24, 16, 128), (16, 32, 256)])
+def test_bf16_cuda_core_path_matches_oracle(T, B, d):
+    inp = orc.make_e1_inputs(T, B, d, seed=200 + d)
+    with option("force_generic", 1):
+        got, ref = run_e1(inp, torch.bfloat16)
+    assert_close(errors(got, oracle_e1(ref)), TOL[torch.bfloat16], f"bf16 generic T{T} B{B} d{d}")
+
+
+@pytest.mark.parametrize("T,B,d,ksplit", [(6, 16, 128, 1), (6, 16, 128, 2), (20, 32, 256, 4),
+                                          (20, 32, 256, 2), (9, 16, 384, 2), (33, 32, 512, 8),
+                                          (12, 64, 256, 4), (10, 48, 256, 4), (8, 8, 128, 2)])
+def test_bf16_tensor_core_path_matches_oracle(T, B, d, ksplit):
+    inp = orc.make_e1_inputs(T, B, d, seed=300 + d + ksplit)
+    before = _lib.tc_launch_count()
+    with option("rec_ksplit", ksplit):
+        got, ref = run_e1(inp, torch.bfloat16)
+    assert _lib.tc_launch_count() > before, "tensor-core kernels were not used"
+    assert _lib.device_status()[0] == 0
+    assert_close(errors(got, oracle_e1(ref)), TOL[torch.bfloat16],
+                 f"bf16 tcgen05 T{T} B{B} d{d} S{ksplit}")
+
+
+def test_bf16_batch_groups_pipeline_matches_oracle():
+    inp = orc.make_e1_inputs(16, 64, 256, seed=77)
+    for groups in (1, 2, 4):
+        with option("rec_groups", groups), option("rec_ksplit", 4):
+            got, ref = run_e1(inp, torch.bfloat16)
+        assert_close(errors(got, oracle_e1(ref)), TOL[torch.bfloat16], f"groups={groups}")
+
+
+def test_inference_mode_returns_empty_v_and_same_output():
+    inp = orc.make_e1_inputs(10, 16, 128, seed=5)
+    got_t, _ = run_e1(inp, torch.bfloat16, training=True)
+    got_i, _ = run_e1(inp, torch.bfloat16, training=False)
+    assert got_i["v"].numel() == 0
+    assert torch.equal(got_t["output"], got_i["output"])
+    assert torch.equal(got_t["h"], got_i["h"])
+
+
+def test_nonzero_h0_and_bias():
+    inp = orc.make_e1_inputs(9, 16, 128, seed=6)
+    g = torch.Generator().manual_seed(1)
+    inp["h0"] = 0.5 * torch.randn(16, 128, generator=g)
+    inp["b"] = 0.2 * torch.randn(128, generator=g)
+    for dtype in (torch.float32, torch.bfloat16):
+        got, ref = run_e1(inp, dtype)
+        assert_close(errors(got, oracle_e1(ref)), TOL[dtype], f"h0/bias {dtype}")
+
+
+def test_results_are_bit_reproducible():
+    """No float atomics anywhere: two runs give identical bits (the reference's db is not)."""
+    inp = orc.make_e1_inputs(32, 32, 256, seed=8)
+    a, _ = run_e1(inp, torch.bfloat16)
+    b, _ = run_e1(inp, torch.bfloat16)
+    for k in FWD_BWD_KEYS:
+        assert torch.equal(a[k], b[k]), k
+
+
+def test_config1_full_size_properties():
+    """configs[1] (bf16, d=1280, B=32, T=512): size-independent properties at full size,
+    plus the CPU oracle on a prefix of the sequence."""
+    T, B, d = 512, 32, 1280
+    inp = orc.make_e1_inputs(T, B, d, seed=1235)
+    got, ref = run_e1(inp, torch.bfloat16)
+    assert _lib.device_status()[0] == 0
+    for k in FWD_BWD_KEYS:
+        assert torch.isfinite(got[k].float()).all(), k
+    # (1) tensor-core path agrees with the CUDA-core path of the same library
+    with option("force_generic", 1):
+        gen, _ = run_e1(inp, torch.bfloat16)
+    assert_close({k: orc.rel_err(got[k].float().cpu(), gen[k].float().cpu()) for k in FWD_BWD_KEYS},
+                 TOL[torch.bfloat16], "tcgen05 vs CUDA-core at config1")
+    # (2) batch independence: rows 0..15 alone give the same forward result
+    sub = {k: (v[:, :16].contiguous() if v.dim() == 3 else v) for k, v in inp.items()}
+    sub["h0"] = inp["h0"][:16].contiguous()
+    gsub, _ = run_e1(sub, torch.bfloat16, training=False)
+    assert orc.rel_err(gsub["output"].float().cpu(), got["output"][:, :16].float().cpu()) < 1e-2
+    # (3) causality + oracle: the first 24 steps match the CPU oracle on the same prefix
+    Tp = 24
+    pref = {k: (v[:Tp].contiguous() if v.dim() == 3 else v) for k, v in ref.items()}
+    o = orc.e1_forward(pref["x"], pref["z"], pref["h0"], pref["W_x"], pref["W_h"], pref["b"])
+    assert orc.rel_err(got["output"][:Tp].float().cpu(), o["output"]) < TOL[torch.bfloat16]
+    assert orc.rel_err(got["h"][:Tp + 1].float().cpu(), o["h"]) < TOL[torch.bfloat16]
+    # (4) backward is linear in d_output: grads(2r) = 2 grads(r)
+    dev = {k: v.to(torch.bfloat16).cuda() for k, v in inp.items()}
+    r2 = (dev["d_output"].float() * 2).to(torch.bfloat16)
+    dx2, dz2, dWx2, dWh2, db2 = H.mamba_gated_elman_backward(
+        dev["W_x"], dev["W_h"], dev["x"], dev["z"], got["h"], got["v"], r2)
+    assert orc.rel_err(dx2.float().cpu(), 2 * got["dx"].float().cpu()) < 1e-2
+    assert orc.rel_err(dWh2.float().cpu(), 2 * got["dW_h"].float().cpu()) < 1e-2
+
+
+def test_argument_checks_raise():
+    x = torch.zeros(4, 2, 8, device="cuda")
+    W = torch.zeros(8, 8, device="cuda")
+    b = torch.zeros(8, device="cuda")
+    h0 = torch.zeros(2, 8, device="cuda")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        H.mamba_gated_elman_forward(True, x.cpu(), x, h0, W, W, b)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        H.mamba_gated_elman_forward(True, x.transpose(0, 1), x, h0, W, W, b)
+    with pytest.raises(RuntimeError, match="shape"):
+        H.mamba_gated_elman_forward(True, x, x, h0, W[:4], W, b)
+    with pytest.raises(RuntimeError, match="dtype"):
+        H.mamba_gated_elman_forward(True, x, x.half(), h0, W, W, b)
+    with pytest.raises(RuntimeError, match="not supported"):
+        H.mamba_gated_elman_forward(True, x.double(), x.double(), h0.double(), W.double(),
+                                    W.double(), b.double())
+
+
+def test_empty_sequence_and_empty_batch():
+    W = torch.randn(8, 8, device="cuda")
+    b = torch.zeros(8, device="cuda")
+    h0 = torch.randn(2, 8, device="cuda")
+    x = torch.zeros(0, 2, 8, device="cuda")
+    h, out, v = H.mamba_gated_elman_forward(True, x, x, h0, W, W, b)
+    assert h.shape == (1, 2, 8) and out.shape == (0, 2, 8)
+    assert torch.equal(h[0], h0)
+    dx, dz, dWx, dWh, db = H.mamba_gated_elman_backward(W, W, x, x, h, v, out)
+    assert float(dWx.abs().sum()) == 0 and float(db.abs().sum()) == 0
+    x0 = torch.zeros(3, 0, 8, device="cuda")
+    h, out, v = H.mamba_gated_elman_forward(True, x0, x0, torch.zeros(0, 8, device="cuda"), W, W, b)
+    assert out.shape == (3, 0, 8)

@@ -1,0 +1,80 @@
+"""The projection GEMM (TMA + tcgen05 for bf16, CUDA cores for fp32) vs a torch fp32 matmul."""
+import pytest
+import torch
+
+from elman_b200 import _lib
+from elman_b200 import hasty_pytorch_lib as H
+from oracle.elman_oracle import rel_err
+from tests._gpu_cases import option
+
+pytestmark = pytest.mark.gpu
+
+
+def ref_proj(A, W, bias, C0):
+    r = A.float().cpu() @ W.float().cpu().T
+    if bias is not None:
+        r = r + bias.float().cpu()
+    if C0 is not None:
+        r = r + C0.float().cpu()
+    return r
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 128, 128), (100, 72, 40), (1, 8, 8),
+                                   (384, 1280, 1280), (130, 250, 72), (2048, 256, 1024)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_bf16_tensor_core_gemm(M, N, K, with_bias):
+    g = torch.Generator().manual_seed(M + N + K)
+    A = torch.randn(M, K, generator=g).bfloat16().cuda()
+    W = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16().cuda()
+    bias = torch.randn(N, generator=g).bfloat16().cuda() if with_bias else None
+    before = _lib.tc_launch_count()
+    out = H.projection(A, W, bias)
+    torch.cuda.synchronize()
+    assert _lib.tc_launch_count() == before + 1, "tcgen05 GEMM was not used"
+    assert _lib.device_status()[0] == 0
+    # bf16 output: one rounding of an fp32-accumulated result
+    assert rel_err(out, ref_proj(A, W, bias, None)) < 4e-3
+
+
+def test_bf16_accumulate_into_existing_output():
+    g = torch.Generator().manual_seed(3)
+    A = torch.randn(256, 128, generator=g).bfloat16().cuda()
+    W = (torch.randn(192, 128, generator=g) / 11).bfloat16().cuda()
+    C0 = torch.randn(256, 192, generator=g).bfloat16().cuda()
+    out = C0.clone()
+    H.projection(A, W, None, out=out, accumulate=True)
+    torch.cuda.synchronize()
+    assert rel_err(out, ref_proj(A, W, None, C0)) < 4e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 64, 16), (100, 72, 41), (5, 3, 7)])
+def test_fp32_cuda_core_gemm(M, N, K):
+    g = torch.Generator().manual_seed(M * N)
+    A = torch.randn(M, K, generator=g).cuda()
+    W = torch.randn(N, K, generator=g).cuda()
+    bias = torch.randn(N, generator=g).cuda()
+    out = H.projection(A, W, bias)
+    torch.cuda.synchronize()
+    assert rel_err(out, ref_proj(A, W, bias, None)) < 1e-5
+
+
+def test_bf16_odd_k_falls_back_to_cuda_cores_and_matches():
+    g = torch.Generator().manual_seed(9)
+    A = torch.randn(64, 270, generator=g).bfloat16().cuda()
+    W = (torch.randn(96, 270, generator=g) / 16).bfloat16().cuda()
+    before = _lib.tc_launch_count()
+    out = H.projection(A, W)
+    torch.cuda.synchronize()
+    assert _lib.tc_launch_count() == before
+    assert rel_err(out, ref_proj(A, W, None, None)) < 4e-3
+
+
+def test_tensor_core_and_cuda_core_paths_agree():
+    g = torch.Generator().manual_seed(10)
+    A = torch.randn(512, 256, generator=g).bfloat16().cuda()
+    W = (torch.randn(384, 256, generator=g) / 16).bfloat16().cuda()
+    a = H.projection(A, W)
+    with option("force_generic", 1):
+        b = H.projection(A, W)
+    torch.cuda.synchronize()
+    assert rel_err(a, b.float().cpu()) < 4e-3

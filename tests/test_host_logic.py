@@ -1,0 +1,166 @@
+"""Host-side mirror classes (autograd Functions, cells, layers) on the CPU.
+
+The CUDA library is replaced, in these tests only, by stand-ins built from the
+CPU oracle, so that the Python plumbing (argument order, saved tensors, spectral
+normalisation, the layer's projections and permutes) is checked against the
+fixtures the reference produced.  The shipped classes themselves refuse CPU
+tensors; the stand-ins lift that by patching `is_cuda` away from the call path.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from elman_b200 import mamba_gated_elman as e1mod
+from elman_b200 import pure_lowrank_elman as e5mod
+from elman_b200 import stock_elman as e0mod
+from oracle import elman_oracle as orc
+
+
+class OracleBackend:
+    """Oracle-backed stand-in with the extension module's function names."""
+
+    @staticmethod
+    def mamba_gated_elman_forward(training, x, z, h0, W_x, W_h, b):
+        o = orc.e1_forward(x, z, h0, W_x, W_h, b)
+        return [o["h"], o["output"], o["v"] if training else x.new_empty(0)]
+
+    @staticmethod
+    def mamba_gated_elman_backward(W_x, W_h, x, z, h, v, d_output):
+        g = orc.e1_backward(W_x, W_h, x, z, h, v, d_output)
+        return [g["dx"], g["dz"], g["dW_x"], g["dW_h"], g["db"]]
+
+    @staticmethod
+    def stock_elman_forward(training, x, h0, W_x, W_h, W_gate, b, b_gate):
+        o = orc.e0_forward(x, h0, W_x, W_h, W_gate, b, b_gate)
+        e = x.new_empty(0)
+        return [o["h"], o["output"], o["v"] if training else e, o["gate_cache"] if training else e]
+
+    @staticmethod
+    def stock_elman_backward(W_x, W_h, W_gate, x, h, v, gate_cache, d_output):
+        g = orc.e0_backward(W_x, W_h, W_gate, x, h, v, gate_cache, d_output)
+        return [g[k] for k in ("dx", "dW_x", "dW_h", "dW_gate", "db", "db_gate")]
+
+    @staticmethod
+    def pure_lowrank_elman_forward(training, x, h0, U_h, V_h, U_x, V_x, U_z, V_z, b):
+        o = orc.e5_forward(x, h0, U_h, V_h, U_x, V_x, U_z, V_z, b)
+        return [o["h"], o["output"], o["v"] if training else x.new_empty(0)]
+
+    @staticmethod
+    def pure_lowrank_elman_backward(U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, d_output):
+        g = orc.e5_backward(U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, d_output)
+        return [g[k] for k in ("dx", "dU_h", "dV_h", "dU_x", "dV_x", "dU_z", "dV_z", "db")]
+
+
+class _CpuAsCuda(torch.Tensor):
+    """A CPU tensor that answers is_cuda=True so the cells' device check passes."""
+
+    @property
+    def is_cuda(self):
+        return True
+
+
+def as_fake_cuda(t):
+    return t.as_subclass(_CpuAsCuda)
+
+
+@pytest.fixture()
+def oracle_backend(monkeypatch):
+    for mod in (e1mod, e0mod, e5mod):
+        monkeypatch.setattr(mod, "hasty_pytorch_lib", OracleBackend)
+
+
+def load(golden_dir, name):
+    d = np.load(os.path.join(golden_dir, name + ".npz"))
+    inp = {k[3:]: torch.from_numpy(d[k]) for k in d.files if k.startswith("in_")}
+    out = {k[4:]: torch.from_numpy(d[k]) for k in d.files if k.startswith("out_")}
+    return inp, out
+
+
+def test_cells_refuse_cpu_tensors():
+    cell = e1mod.MambaGatedElmanCell(8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        cell(torch.zeros(2, 1, 8), torch.zeros(2, 1, 8))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        e0mod.StockElmanCell(8)(torch.zeros(2, 1, 8))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        e5mod.PureLowRankElmanCell(8, rank=2)(torch.zeros(2, 1, 8))
+
+
+@pytest.mark.parametrize("name,spectral", [("e1_small", False), ("e1_h0", False),
+                                           ("e1_spectral", True)])
+def test_e1_cell_against_reference_fixture(golden_dir, oracle_backend, name, spectral):
+    inp, want = load(golden_dir, name)
+    d = inp["W_x"].shape[0]
+    cell = e1mod.MambaGatedElmanCell(d, w_h_mode="spectral_norm" if spectral else "none")
+    with torch.no_grad():
+        cell.W_x.copy_(inp["W_x"]); cell.W_h.copy_(inp["W_h"]); cell.b.copy_(inp["b"])
+    if spectral:
+        cell._spectral_u = inp["spectral_u"].clone()
+    x = as_fake_cuda(inp["x"].clone()).requires_grad_(True)
+    z = as_fake_cuda(inp["z"].clone()).requires_grad_(True)
+    out, h = cell(x, z, inp["h0"])
+    (out * inp["d_output"]).sum().backward()
+    got = {"output": out, "h": h, "dx": x.grad, "dz": z.grad, "dW_x": cell.W_x.grad,
+           "dW_h": cell.W_h.grad, "db": cell.b.grad}
+    for k, vref in want.items():
+        assert orc.rel_err(got[k], vref) < 2e-5, k
+
+
+def test_e1_layer_against_reference_fixture(golden_dir, oracle_backend):
+    inp, want = load(golden_dir, "e1_layer")
+    dim = inp["x"].shape[-1]
+    layer = e1mod.MambaGatedElman(dim, expansion=1.0)
+    sd = {k[2:]: v for k, v in inp.items() if k.startswith("p_")}
+    assert set(sd) == set(layer.state_dict()), "parameter names differ from the reference's"
+    layer.load_state_dict(sd)
+    x = as_fake_cuda(inp["x"].clone()).requires_grad_(True)
+    out, h_final = layer(x)
+    (out * inp["d_output"]).sum().backward()
+    assert orc.rel_err(out, want["output"]) < 2e-5
+    assert orc.rel_err(h_final, want["h_final"]) < 2e-5
+    assert orc.rel_err(x.grad, want["dx"]) < 2e-5
+    for k, p in layer.named_parameters():
+        assert orc.rel_err(p.grad, want["g_" + k]) < 5e-5, k
+
+
+def test_e0_cell_against_reference_fixture(golden_dir, oracle_backend):
+    inp, want = load(golden_dir, "e0_small")
+    d = inp["W_x"].shape[0]
+    cell = e0mod.StockElmanCell(d, w_h_mode="free")
+    with torch.no_grad():
+        for k in ("W_x", "W_h", "W_gate", "b", "b_gate"):
+            getattr(cell, k).copy_(inp[k])
+    x = as_fake_cuda(inp["x"].clone()).requires_grad_(True)
+    out, h = cell(x, inp["h0"])
+    (out * inp["d_output"]).sum().backward()
+    got = {"output": out, "h": h, "dx": x.grad, "dW_x": cell.W_x.grad, "dW_h": cell.W_h.grad,
+           "dW_gate": cell.W_gate.grad, "db": cell.b.grad, "db_gate": cell.b_gate.grad}
+    for k, vref in want.items():
+        assert orc.rel_err(got[k], vref) < 2e-5, k
+
+
+def test_e5_cell_against_reference_fixture(golden_dir, oracle_backend):
+    inp, want = load(golden_dir, "e5_small")
+    d, r = inp["U_h"].shape
+    cell = e5mod.PureLowRankElmanCell(d, rank=r)
+    with torch.no_grad():
+        for k in ("U_h", "V_h", "U_x", "V_x", "U_z", "V_z", "b"):
+            getattr(cell, k).copy_(inp[k])
+    x = as_fake_cuda(inp["x"].clone()).requires_grad_(True)
+    out, h = cell(x, inp["h0"])
+    (out * inp["d_output"]).sum().backward()
+    got = {"output": out, "h": h, "dx": x.grad, "db": cell.b.grad}
+    for k in ("U_h", "V_h", "U_x", "V_x", "U_z", "V_z"):
+        got["d" + k] = getattr(cell, k).grad
+    for k, vref in want.items():
+        assert orc.rel_err(got[k], vref) < 2e-5, k
+
+
+def test_state_dict_names_match_reference_layout():
+    assert set(e0mod.StockElman(16).state_dict()) == {
+        "in_proj.weight", "cell.W_x", "cell.b", "cell.W_gate", "cell.b_gate", "cell.W_h",
+        "out_proj.weight"}
+    assert set(e5mod.PureLowRankElman(16, rank=4).state_dict()) == {
+        "cell.U_h", "cell.V_h", "cell.U_x", "cell.V_x", "cell.U_z", "cell.V_z", "cell.b"}
