@@ -33,6 +33,7 @@ SIGNATURES = {
     "elman_b200_get_option": (_L, [_c.c_char_p]),
     "elman_b200_wait_probe": (_I, [_L, _P, _P]),
     "elman_b200_last_timing": (_I, [_I, _c.POINTER(_c.c_float)]),
+    "elman_b200_recurrence_trace": (_I, [_c.POINTER(_c.c_longlong), _I]),
     "elman_b200_launch_count": (_L, []),
     "elman_b200_tc_launch_count": (_L, []),
     "elman_e1_forward_workspace": (_Z, [_I, _I, _I, _I]),

@@ -262,6 +262,8 @@ int elman_b200_set_option(const char* name, long value) {
   else if (!strcmp(name, "rec_ksplit")) o.rec_ksplit = value;
   else if (!strcmp(name, "rec_groups")) o.rec_groups = value;
   else if (!strcmp(name, "time_kernels")) o.time_kernels = value;
+  else if (!strcmp(name, "rec_trace")) o.rec_trace = value;
+  else if (!strcmp(name, "rec_mma_warps")) o.rec_mma_warps = value;
   else return set_error(ELMAN_ERR_ARG, "unknown option '%s'", name);
   return ELMAN_OK;
 }
@@ -274,6 +276,8 @@ long elman_b200_get_option(const char* name) {
   if (!strcmp(name, "rec_ksplit")) return o.rec_ksplit;
   if (!strcmp(name, "rec_groups")) return o.rec_groups;
   if (!strcmp(name, "time_kernels")) return o.time_kernels;
+  if (!strcmp(name, "rec_trace")) return o.rec_trace;
+  if (!strcmp(name, "rec_mma_warps")) return o.rec_mma_warps;
   return -1;
 }
 
@@ -284,6 +288,11 @@ int elman_b200_last_timing(int phase, float* ms) {
   ELMAN_CUDA_CHECK(cudaEventSynchronize(g_ev[phase][1]));
   ELMAN_CUDA_CHECK(cudaEventElapsedTime(ms, g_ev[phase][0], g_ev[phase][1]));
   return ELMAN_OK;
+}
+
+int elman_b200_recurrence_trace(long long* dst, int max_entries) {
+  ELMAN_ARG_CHECK(dst != nullptr && max_entries > 0, "bad trace buffer");
+  return rec_tc_copy_trace(dst, max_entries);
 }
 
 long elman_b200_launch_count(void) { return g_launches.load(); }

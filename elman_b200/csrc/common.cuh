@@ -46,6 +46,8 @@ struct Options {
   long rec_ksplit = 0;
   long rec_groups = 0;
   long time_kernels = 0;
+  long rec_trace = 0;
+  long rec_mma_warps = 0;
 };
 Options& options();
 void count_launch(bool tensor_core);
@@ -180,5 +182,7 @@ bool rec_tc_supported(int T, int B, int d);
 size_t rec_tc_sync_bytes();
 int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream);
 int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream);
+// Copies the cycle stamps of the last traced launch (option rec_trace) to the host.
+int rec_tc_copy_trace(long long* dst, int max_entries);
 
 }  // namespace elman

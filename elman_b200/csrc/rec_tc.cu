@@ -38,11 +38,14 @@ namespace {
 
 constexpr int TILE_M = 128;
 constexpr int NUM_EPI_THREADS = 128;
-constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;
+constexpr int NUM_MMA_WARPS = 4;
+constexpr int NUM_THREADS = 32 + NUM_MMA_WARPS * 32 + NUM_EPI_THREADS + 32;  // + publisher warp
 constexpr int MAX_S = 8;
 constexpr int MAX_GROUPS = 16;
-constexpr int MAX_E = 16;          // epilogue elements per thread and step
+constexpr int MAX_QUADS = 2;       // batch quads (4 rows) per epilogue thread and step
 constexpr int COUNTER_STRIDE = 32; // ints; one 128-byte line per counter
+constexpr int TRACE_STEPS = 64;
+constexpr int TRACE_SLOTS = 16;
 
 struct RecTcParams {
   int T, B, d;
@@ -53,6 +56,8 @@ struct RecTcParams {
   int Npad;     // Ng rounded up to 16 (MMA N)
   int nstages;  // state ring depth
   int R;        // d / 128: producers per K slice and step
+  int nmw;      // MMA-issuing warps (independent accumulator chains)
+  uint32_t tmem_cols;
   // forward
   const bf16* pre; const bf16* g; bf16* h; bf16* y; bf16* v;
   // backward
@@ -61,6 +66,7 @@ struct RecTcParams {
   int* abort_word;  // global abort flag
   int* status;
   long spin_limit;
+  long long* trace;   // optional [TRACE_STEPS][TRACE_SLOTS] cycle stamps of CTA 0, or null
 };
 
 // ------------------------- cluster / DSMEM helpers -------------------------
@@ -76,6 +82,37 @@ __device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t rank) {
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Store to a peer's shared memory that also credits `bytes` to an mbarrier in the
+// same peer when the data has landed: data and signal travel together, so the
+// sender needs neither a fence nor a separate arrive.
+__device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(remote_addr), "r"(__float_as_uint(v)), "r"(remote_bar)
+               : "memory");
+}
+__device__ __forceinline__ void st_async_v4(uint32_t remote_addr, uint32_t a, uint32_t b, uint32_t c,
+                                            uint32_t d, uint32_t remote_bar) {
+  asm volatile(
+      "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+      ::"r"(remote_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(remote_bar)
+      : "memory");
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint32_t remote_bar_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr)
+               : "memory");
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ void fence_acq_rel_cluster() {
   asm volatile("fence.acq_rel.cluster;" ::: "memory");
@@ -102,6 +139,20 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_THREADS) : "memory");
 }
+// Barrier over the epilogue threads that also ORs a predicate: every thread gets
+// the same answer, so they can leave a loop together.
+__device__ __forceinline__ bool epi_bar_or(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, %2, p;\n\t"
+      "selp.b32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred), "n"(NUM_EPI_THREADS)
+      : "memory");
+  return r != 0;
+}
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, int c0, int c1,
                                             int c2, uint64_t* bar) {
   asm volatile(
@@ -109,6 +160,25 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       "[%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(ptx::smem_u32(smem_dst)), "l"(m), "r"(ptx::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+
+// Cycle stamps of CTA 0 for the first TRACE_STEPS virtual steps (diagnostics only).
+__device__ __forceinline__ void stamp(long long* trace, int q, int slot) {
+  if (trace != nullptr && blockIdx.x == 0 && q < TRACE_STEPS)
+    trace[q * TRACE_SLOTS + slot] = clock64();
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, int c0, int c1,
+                                            int c2, int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(ptx::smem_u32(smem_dst)), "l"(m), "r"(ptx::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
 }
 
 struct Waiter {
@@ -132,7 +202,7 @@ struct Waiter {
   __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) const {
     long spins = 0;
     unsigned long long t0 = 0;
-    while (!ptx::mbar_try_wait(bar, parity))
+    while (!ptx::mbar_try_wait_suspend(bar, parity))
       if (give_up(spins, t0, 255)) return false;
     return true;
   }
@@ -165,6 +235,32 @@ __device__ __forceinline__ unsigned short f_to_bf16_bits(float f) {
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sigmoid_fast(float z) { return __fdividef(1.f, 1.f + __expf(-z)); }
+// 1 - tanh(v)^2 without cancellation: 4u/(1+u)^2 with u = exp(-2|v|)
+__device__ __forceinline__ float dtanh_from_v(float v) {
+  const float u = __expf(-2.f * fabsf(v));
+  const float r = __fdividef(1.f, 1.f + u);
+  return 4.f * u * r * r;
+}
+__device__ __forceinline__ float2 bf16x2_to_f2(uint32_t u) {
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t ldg_u32(const bf16* p) {
+  return __ldg(reinterpret_cast<const unsigned int*>(p));
+}
+__device__ __forceinline__ void stg_u32(bf16* p, uint32_t v) {
+  *reinterpret_cast<unsigned int*>(p) = v;
+}
+
 template <bool BWD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmState,
@@ -177,12 +273,13 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   __shared__ __align__(8) uint64_t acc_empty_bar[2];  // epilogue -> MMA
   __shared__ __align__(8) uint64_t red_full_bar[2];   // peers' partials landed (owner side)
   __shared__ __align__(8) uint64_t red_empty_bar[2];  // owners consumed my partials (source side)
+  __shared__ __align__(8) uint64_t stored_bar[2];     // epilogue warps stored the new state
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ float db_part[NUM_EPI_THREADS];
+  __shared__ float db_part[2][NUM_EPI_THREADS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int S = p.S, Kc = p.Kc, Npad = p.Npad, Ng = p.Ng, G = p.G;
+  const int S = p.S, Kc = p.Kc, Npad = p.Npad, Ng = p.Ng, G = p.G, nmw = p.nmw;
   const int rows_own = TILE_M / S;
   const uint32_t j = cluster_ctarank();   // K slice index == rank in cluster
   const int i = blockIdx.x / S;           // row block index
@@ -196,9 +293,11 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   uint8_t* sState = sW + w_bytes;                        // nstages x nkt tiles of [Npad x 64]
   const int state_tile_bytes = Npad * 64 * 2;
   const int state_stage_bytes = nkt * state_tile_bytes;
-  float* sStage = (float*)(sState + p.nstages * state_stage_bytes);  // [2][S][rows_own][Npad+1]
-  const int stg_row = Npad + 1;
-  const int stg_buf_floats = S * rows_own * stg_row;
+  // partial sums from the S cluster peers: [2 buffers][S sources][Npad batch][rows_own]
+  float* sStage = (float*)(sState + p.nstages * state_stage_bytes);
+  const int stg_src_floats = Npad * rows_own;
+  const int stg_buf_floats = S * stg_src_floats;
+  const uint32_t tmem_cols = p.tmem_cols;
 
   Waiter waiter{p.spin_limit, &abort_flag, p.abort_word};
 
@@ -207,33 +306,31 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     ptx::mbar_init(&w_bar, 1);
     for (int s = 0; s < 4; ++s) {
       ptx::mbar_init(&full_bar[s], 1);
-      ptx::mbar_init(&empty_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], nmw);
     }
-    const int red_arrivals = S > 4 ? S : 4;
     for (int a = 0; a < 2; ++a) {
-      ptx::mbar_init(&acc_full_bar[a], 1);
+      ptx::mbar_init(&acc_full_bar[a], nmw);
       ptx::mbar_init(&acc_empty_bar[a], 4);
-      ptx::mbar_init(&red_full_bar[a], red_arrivals);
+      ptx::mbar_init(&red_full_bar[a], 1);  // the owner's expect_tx arrive; data credits bytes
       ptx::mbar_init(&red_empty_bar[a], S);
+      ptx::mbar_init(&stored_bar[a], NUM_EPI_THREADS / 32);
     }
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmW);
     ptx::prefetch_tmap(&tmState);
   }
   if (warp == 1) {
-    uint32_t cols = 2 * Npad < 32 ? 32 : 2 * Npad;
-    uint32_t pow2 = 32;
-    while (pow2 < cols) pow2 <<= 1;
-    ptx::tmem_alloc(&tmem_slot, pow2);
+    ptx::tmem_alloc(&tmem_slot, tmem_cols);
     ptx::tmem_relinquish();
   }
-  if (tid >= 64) db_part[tid - 64] = 0.f;
+  if (tid < NUM_EPI_THREADS) { db_part[0][tid] = 0.f; db_part[1][tid] = 0.f; }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   // peers must have initialised their barriers before any remote arrive / store
   cluster_sync_all();
   const uint32_t tmem_base = tmem_slot;
+  const int kid = BWD ? KID_REC_TC_BWD : KID_REC_TC_FWD;
 
   if (warp == 0) {
     // =========================== TMA producer ===============================
@@ -250,24 +347,32 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         if (ok && step > 0)
           ok = waiter.wait_counter(p.ready + (grp * MAX_S + (int)j) * COUNTER_STRIDE, step * p.R);
         if (!ok) {
-          if (atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, BWD ? KID_REC_TC_BWD : KID_REC_TC_FWD, step);
+          if (atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, kid, step);
           abort_flag = 1;
           break;
         }
+        stamp(p.trace, q, 0);  // dependency satisfied
         // data written by other SMs through the generic proxy -> read by TMA
-        ptx::fence_proxy_async();
+        fence_proxy_async_global();
+        stamp(p.trace, q, 11);  // proxy fence done
         const int slot = BWD ? (p.T - step) : step;  // time index of the input state
         ptx::mbar_arrive_expect_tx(&full_bar[s], (uint32_t)state_stage_bytes);
-        for (int kk = 0; kk < nkt; ++kk)
-          tma_load_3d(sState + s * state_stage_bytes + kk * state_tile_bytes, &tmState,
-                      (int)j * Kc + kk * 64, grp * Ng, slot, &full_bar[s]);
+        // one 4-D box: all nkt 64-column tiles of my K slice for this batch group
+        tma_load_4d(sState + s * state_stage_bytes, &tmState, 0, grp * Ng, (int)j * nkt, slot,
+                    &full_bar[s]);
+        stamp(p.trace, q, 1);  // loads issued
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
-    // =========================== MMA issuer =================================
-    if (lane == 0) {
+  } else if (warp <= NUM_MMA_WARPS) {
+    // ====================== MMA issuers (warps 1..nmw) =======================
+    // MMA number m of a step (tile m/4, 16-wide K chunk m%4) is issued by MMA warp
+    // m % nmw into that warp's own accumulator: nmw short dependent chains run
+    // concurrently instead of one long one; the epilogue adds the nmw accumulators.
+    const int mw = warp - 1;
+    if (lane == 0 && mw < nmw) {
       const uint32_t idesc = ptx::umma_idesc_bf16(TILE_M, Npad);
+      const int nmma = nkt * 4;
       bool ok = waiter.wait(&w_bar, 0);
       for (int q = 0; q < total_q && ok; ++q) {
         const int s = q % p.nstages;
@@ -276,65 +381,107 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const uint32_t aph = (uint32_t)(q >> 1) & 1u;
         ok = waiter.wait(&acc_empty_bar[a], aph ^ 1u) && waiter.wait(&full_bar[s], ph);
         if (!ok) break;
+        if (mw == 0) stamp(p.trace, q, 2);  // state tile landed
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(a * Npad);
-        for (int kk = 0; kk < nkt; ++kk) {
-          const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(sW + kk * (TILE_M * 128)));
-          const uint64_t db = ptx::umma_desc_k_sw128(
-              ptx::smem_u32(sState + s * state_stage_bytes + kk * state_tile_bytes));
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            ptx::umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kk > 0 || k > 0) ? 1u : 0u);
+        const uint32_t d_tmem = tmem_base + (uint32_t)((a * nmw + mw) * Npad);
+        const uint32_t w0 = ptx::smem_u32(sW);
+        const uint32_t s0 = ptx::smem_u32(sState + s * state_stage_bytes);
+        for (int m = mw; m < nmma; m += nmw) {
+          const int kk = m >> 2, k = m & 3;
+          const uint64_t da = ptx::umma_desc_k_sw128(w0 + kk * (TILE_M * 128)) + 2 * k;
+          const uint64_t db = ptx::umma_desc_k_sw128(s0 + kk * state_tile_bytes) + 2 * k;
+          ptx::umma_bf16(d_tmem, da, db, idesc, m >= nmw ? 1u : 0u);
         }
         ptx::umma_commit(&empty_bar[s]);
         ptx::umma_commit(&acc_full_bar[a]);
+        if (mw == 0) stamp(p.trace, q, 3);  // MMAs issued
       }
       if (!ok) {
-        if (abort_flag == 0 && atomicExch(p.abort_word, 1) == 0)
-          report_timeout(p.status, BWD ? KID_REC_TC_BWD : KID_REC_TC_FWD, 0xFFFFF1);
+        if (abort_flag == 0 && atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, kid, 0xFFFFF1);
         abort_flag = 1;
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp <= NUM_MMA_WARPS + NUM_EPI_THREADS / 32) {
     // =========================== epilogue ===================================
-    const int et = tid - 64;                 // 0..127
+    const int et = tid - (1 + NUM_MMA_WARPS) * 32;   // 0..127
     const int quarter = warp & 3;            // TMEM lane quarter this warp may read
     const int m = quarter * 32 + lane;       // accumulator row held by this thread
     const int owner = m / rows_own;          // cluster rank that finalises row m
     const int m_local = m - owner * rows_own;
-    const int rows_in_warp = rows_own < 32 ? rows_own : 32;
-    // finalise mapping: feature fl of my chunk, batch rows bq, bq+S, ...
-    const int fl = et % rows_own;
-    const int bq = et / rows_own;
-    const int f = i * TILE_M + (int)j * rows_own + fl;  // global feature index
-    const int my_kslice = f / Kc;
+    // finalise mapping: this thread owns the feature pair fp of my chunk for the
+    // batch quads qd0, qd0 + nbq, ... (a quad = 4 consecutive batch rows)
+    const int pairs = rows_own / 2;
+    const int nbq = NUM_EPI_THREADS / pairs;
+    const int fp = et % pairs;
+    const int qd0 = et / pairs;
+    const int nquads = (Ng + 3) / 4;
+    const int f = i * TILE_M + (int)j * rows_own + 2 * fp;  // first feature of the pair
     const uint32_t stage_local = ptx::smem_u32(sStage);
     const long BD = (long)p.B * p.d;
-    float db_acc = 0.f;
-    bool ok = true;
+    float db0 = 0.f, db1 = 0.f;
 
-    // element registers: forward (pre, z) / backward (a = dy*silu(g), dtanh)
-    float e0[MAX_E], e1[MAX_E];
-    auto prefetch = [&](int q) {
+    // raw prefetched inputs of the next step, and the values derived from them
+    uint32_t r0[MAX_QUADS][4], r1[MAX_QUADS][4], r2[MAX_QUADS][4], r3[MAX_QUADS][4];
+    float2 e0[MAX_QUADS][4], e1[MAX_QUADS][4];
+    uint32_t late0[MAX_QUADS][4], late1[MAX_QUADS][4];  // outputs nobody waits for
+    // element offsets inside one (time step, batch group) block; -1 marks padding
+    int eoff[MAX_QUADS][4];
+#pragma unroll
+    for (int e = 0; e < MAX_QUADS; ++e)
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int b = 4 * (qd0 + e * nbq) + u;
+        eoff[e][u] = b < Ng ? b * p.d + f : -1;
+      }
+    auto block_base = [&](int q) -> long {
       const int step = q / G, grp = q - step * G;
       const int t = BWD ? (p.T - 1 - step) : step;
+      return ((long)t * p.B + (long)grp * Ng) * p.d;
+    };
+    auto prefetch = [&](int q) {
+      const long base = block_base(q);
 #pragma unroll
-      for (int e = 0; e < MAX_E; ++e) {
-        const int b = bq + e * S;
-        if (b < Ng) {
-          const long idx = ((long)t * p.B + grp * Ng + b) * p.d + f;
-          if (!BWD) {
-            e0[e] = bf16_bits_to_f(ldg_bf16_bits(p.pre + idx));
-            e1[e] = bf16_bits_to_f(ldg_bf16_bits(p.g + idx));
-          } else {
-            const float gz = bf16_bits_to_f(ldg_bf16_bits(p.g + idx));
-            const float dyv = bf16_bits_to_f(ldg_bf16_bits(p.dy + idx));
-            const float hv = bf16_bits_to_f(ldg_bf16_bits(p.h_in + idx + BD));
-            const float th = tanhf(bf16_bits_to_f(ldg_bf16_bits(p.v_in + idx)));
-            p.dg[idx] = __float2bfloat16_rn(dyv * hv * dsiluf_(gz));
-            e0[e] = dyv * siluf_(gz);
-            e1[e] = 1.f - th * th;
+      for (int e = 0; e < MAX_QUADS; ++e) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (eoff[e][u] >= 0) {
+            const long idx = base + eoff[e][u];
+            if (!BWD) {
+              r0[e][u] = ldg_u32(p.pre + idx);
+              r1[e][u] = ldg_u32(p.g + idx);
+            } else {
+              r0[e][u] = ldg_u32(p.g + idx);
+              r1[e][u] = ldg_u32(p.dy + idx);
+              r2[e][u] = ldg_u32(p.h_in + idx + BD);
+              r3[e][u] = ldg_u32(p.v_in + idx);
+            }
+          }
+        }
+      }
+    };
+    // everything that does not depend on the recurrent term
+    auto premath = [&]() {
+#pragma unroll
+      for (int e = 0; e < MAX_QUADS; ++e) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (eoff[e][u] >= 0) {
+            if (!BWD) {
+              e0[e][u] = bf16x2_to_f2(r0[e][u]);
+              const float2 gz = bf16x2_to_f2(r1[e][u]);
+              e1[e][u] = make_float2(gz.x * sigmoid_fast(gz.x), gz.y * sigmoid_fast(gz.y));
+            } else {
+              const float2 gz = bf16x2_to_f2(r0[e][u]);
+              const float2 dy = bf16x2_to_f2(r1[e][u]);
+              const float2 hv = bf16x2_to_f2(r2[e][u]);
+              const float2 vv = bf16x2_to_f2(r3[e][u]);
+              const float sx = sigmoid_fast(gz.x), sy = sigmoid_fast(gz.y);
+              late0[e][u] = f2_to_bf16x2(dy.x * hv.x * sx * (1.f + gz.x * (1.f - sx)),
+                                         dy.y * hv.y * sy * (1.f + gz.y * (1.f - sy)));
+              e0[e][u] = make_float2(dy.x * gz.x * sx, dy.y * gz.y * sy);
+              e1[e][u] = make_float2(dtanh_from_v(vv.x), dtanh_from_v(vv.y));
+            }
           }
         }
       }
@@ -342,76 +489,158 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     if (total_q > 0) prefetch(0);
 
     for (int q = 0; q < total_q; ++q) {
-      const int step = q / G, grp = q - step * G;
-      const int t = BWD ? (p.T - 1 - step) : step;
+      const int step = q / G;
+      const long base_q = block_base(q);
       const int a = q & 1;
       const uint32_t aph = (uint32_t)(q >> 1) & 1u;
+      if (et == 0)  // arm this step's reduction barrier with the bytes all S sources will send me
+        ptx::mbar_arrive_expect_tx(&red_full_bar[a], (uint32_t)(S * rows_own * nquads * 16));
+      // everything that does not need the recurrent term, while the MMAs are in flight
+      premath();
+      if (et == 0) stamp(p.trace, q, 12);  // step-local math done
+      // A failed (timed-out / aborted) wait never skips the named barrier below:
+      // the thread marks the CTA aborted, skips the data movement, and everybody
+      // leaves the loop together after the barrier.
       // ---- drain my accumulator row and scatter it to the owning peer ----
-      ok = waiter.wait(&acc_full_bar[a], aph) && waiter.wait_cluster(&red_empty_bar[a], aph ^ 1u);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      ptx::tc_fence_after();
-      {
+      bool good = waiter.wait(&acc_full_bar[a], aph) &&
+                  waiter.wait_cluster(&red_empty_bar[a], aph ^ 1u);
+      good = __all_sync(0xffffffffu, good);
+      if (et == 0) stamp(p.trace, q, 4);  // accumulator complete
+      if (good) {
+        ptx::tc_fence_after();
+        // staging layout at the owner: [source][batch quad][row][4 batch values];
+        // a warp's 16-byte stores for one quad cover 32 consecutive rows = 512 bytes
         const uint32_t remote =
-            mapa(stage_local + (uint32_t)(((a * S + (int)j) * rows_own + m_local) * stg_row) * 4u,
+            mapa(stage_local + (uint32_t)((a * S + (int)j) * stg_src_floats + m_local * 4) * 4u,
                  (uint32_t)owner);
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * Npad);
+        const uint32_t remote_bar = mapa(ptx::smem_u32(&red_full_bar[a]), (uint32_t)owner);
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                               (uint32_t)(a * nmw * Npad);
         for (int c = 0; c < Npad; c += 16) {
           uint32_t r[16];
           ptx::tmem_ld16(taddr + (uint32_t)c, r);
+          for (int w = 1; w < nmw; ++w) {
+            uint32_t r_[16];
+            ptx::tmem_ld16(taddr + (uint32_t)(w * Npad + c), r_);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+              r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(r_[k]));
+          }
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int k = 0; k < 16; ++k)
-            if (c + k < Ng) st_cluster_f32(remote + (uint32_t)(c + k) * 4u, __uint_as_float(r[k]));
+          for (int k = 0; k < 16; k += 4)
+            if (c + k < Ng)
+              st_async_v4(remote + (uint32_t)(((c + k) >> 2) * rows_own * 4) * 4u, r[k], r[k + 1],
+                          r[k + 2], r[k + 3], remote_bar);
         }
         ptx::tc_fence_before();
-        fence_acq_rel_cluster();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&acc_empty_bar[a]);
-        if ((lane % rows_in_warp) == 0)
-          mbar_arrive_remote(mapa(ptx::smem_u32(&red_full_bar[a]), (uint32_t)owner));
+        if (et == 0) stamp(p.trace, q, 5);  // partials scattered
+        // ---- owner: add the S partials, fused epilogue, write the new state ----
+        good = waiter.wait_cluster(&red_full_bar[a], aph);
+        good = __all_sync(0xffffffffu, good);
+        if (et == 0) stamp(p.trace, q, 6);  // all partials landed
       }
-      // ---- owner: add the S partials, fused epilogue, publish the new state ----
-      ok = waiter.wait_cluster(&red_full_bar[a], aph);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      const float* stg = sStage + a * stg_buf_floats + fl * stg_row;
+      if (good) {
+        const uint32_t stg = stage_local + (uint32_t)(a * stg_buf_floats + 2 * fp * 4) * 4u;
+        float4 s0[MAX_QUADS], s1[MAX_QUADS];  // sums for feature 2fp and 2fp+1, 4 batch rows
 #pragma unroll
-      for (int e = 0; e < MAX_E; ++e) {
-        const int b = bq + e * S;
-        if (b < Ng) {
-          float acc = 0.f;
-          for (int src = 0; src < S; ++src) acc += stg[src * rows_own * stg_row + b];
-          const long idx = ((long)t * p.B + grp * Ng + b) * p.d + f;
-          if (!BWD) {
-            const float val = acc + e0[e];
-            const float hv = tanhf(val);
-            p.h[idx + BD] = __float2bfloat16_rn(hv);
-            if (p.v != nullptr) p.v[idx] = __float2bfloat16_rn(val);
-            p.y[idx] = __float2bfloat16_rn(hv * siluf_(e1[e]));
-          } else {
-            const float dvv = (e0[e] + acc) * e1[e];
-            p.dv[idx] = __float2bfloat16_rn(dvv);
-            db_acc += dvv;
+        for (int e = 0; e < MAX_QUADS; ++e) {
+          const int qd = qd0 + e * nbq;
+          s0[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+          s1[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (qd < nquads) {
+            for (int src = 0; src < S; ++src) {
+              const uint32_t ad = stg + (uint32_t)(src * stg_src_floats + qd * rows_own * 4) * 4u;
+              const float4 x0 = lds_f4(ad), x1 = lds_f4(ad + 16);
+              s0[e].x += x0.x; s0[e].y += x0.y; s0[e].z += x0.z; s0[e].w += x0.w;
+              s1[e].x += x1.x; s1[e].y += x1.y; s1[e].z += x1.z; s1[e].w += x1.w;
+            }
+          }
+        }
+        if (et == 0) stamp(p.trace, q, 14);  // partial sums read
+#pragma unroll
+        for (int e = 0; e < MAX_QUADS; ++e) {
+          const float a0[4] = {s0[e].x, s0[e].y, s0[e].z, s0[e].w};
+          const float a1[4] = {s1[e].x, s1[e].y, s1[e].z, s1[e].w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (eoff[e][u] >= 0) {
+              const long idx = base_q + eoff[e][u];
+              if (!BWD) {
+                const float v0 = a0[u] + e0[e][u].x, v1 = a1[u] + e0[e][u].y;
+                const float h0 = tanh_fast(v0), h1 = tanh_fast(v1);
+                stg_u32(p.h + idx + BD, f2_to_bf16x2(h0, h1));
+                late0[e][u] = f2_to_bf16x2(v0, v1);
+                late1[e][u] = f2_to_bf16x2(h0 * e1[e][u].x, h1 * e1[e][u].y);
+              } else {
+                const float d0 = (e0[e][u].x + a0[u]) * e1[e][u].x;
+                const float d1 = (e0[e][u].y + a1[u]) * e1[e][u].y;
+                stg_u32(p.dv + idx, f2_to_bf16x2(d0, d1));
+                db0 += d0;
+                db1 += d1;
+              }
+            }
+          }
+        }
+      } else {
+        if (abort_flag == 0 && atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, kid, step);
+        abort_flag = 1;
+      }
+      // hand the publication of this chunk to the publisher warp: its gpu-scope
+      // release would otherwise stall this warp's next loads and stores
+      __syncwarp();
+      if (lane == 0 && good) ptx::mbar_arrive(&stored_bar[a]);
+      if (et == 0) stamp(p.trace, q, 7);  // new state stored
+      // all 128 epilogue threads meet here, whether their waits succeeded or not,
+      // and agree on whether to stop
+      if (epi_bar_or(!good || abort_flag != 0)) {
+        abort_flag = 1;
+        break;
+      }
+      if (et == 0) stamp(p.trace, q, 8);  // epilogue threads met
+      // tell every source that its slot in my staging buffer `a` is free again
+      // (my reads of it completed before the barrier above; no data is published here)
+      if (et < S) mbar_arrive_remote_relaxed(mapa(ptx::smem_u32(&red_empty_bar[a]), (uint32_t)et));
+      // outputs that no other CTA waits for
+#pragma unroll
+      for (int e = 0; e < MAX_QUADS; ++e) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (eoff[e][u] >= 0) {
+            const long idx = base_q + eoff[e][u];
+            if (!BWD) {
+              if (p.v != nullptr) stg_u32(p.v + idx, late0[e][u]);
+              stg_u32(p.y + idx, late1[e][u]);
+            } else {
+              stg_u32(p.dg + idx, late0[e][u]);
+            }
           }
         }
       }
-      // all 128 epilogue threads have written their part of the chunk
-      epi_bar_sync();
-      if (et == 0) {
-        __threadfence();
-        red_release_gpu_add(p.ready + (grp * MAX_S + my_kslice) * COUNTER_STRIDE, 1);
-      }
-      // tell every source that its slot in my staging buffer `a` is free again
-      if (et < S) mbar_arrive_remote(mapa(ptx::smem_u32(&red_empty_bar[a]), (uint32_t)et));
       if (q + 1 < total_q) prefetch(q + 1);
+      if (et == 0) stamp(p.trace, q, 10);  // next step's inputs requested
     }
-    if (!ok) {
-      if (abort_flag == 0 && atomicExch(p.abort_word, 1) == 0)
-        report_timeout(p.status, BWD ? KID_REC_TC_BWD : KID_REC_TC_FWD, 0xFFFFF2);
-      abort_flag = 1;
+    if (BWD) { db_part[0][et] = db0; db_part[1][et] = db1; }
+  } else {
+    // =========================== publisher ==================================
+    // Waits until the four epilogue warps have stored their part of the new state
+    // (mbarrier, CTA scope), then bumps the step counter with a gpu-scope release:
+    // the stores are ordered before the counter for every CTA that acquires it.
+    if (lane == 0) {
+      const int my_kslice = (i * TILE_M + (int)j * rows_own) / Kc;
+      for (int q = 0; q < total_q; ++q) {
+        const int step = q / G, grp = q - step * G;
+        const int a = q & 1;
+        const uint32_t aph = (uint32_t)(q >> 1) & 1u;
+        if (!waiter.wait(&stored_bar[a], aph)) break;   // the failing role reports the abort
+        red_release_gpu_add(p.ready + (grp * MAX_S + my_kslice) * COUNTER_STRIDE, 1);
+        stamp(p.trace, q, 9);  // published
+      }
     }
-    if (BWD) db_part[et] = db_acc;
+    __syncwarp();
   }
 
   // ------------------------------ teardown ---------------------------------
@@ -421,22 +650,16 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // let copies that may still be in flight land before memory is released
     for (int k = 0; k < 2000; ++k) __nanosleep(100);
   }
-  if (BWD && abort_flag == 0 && tid >= 64) {
-    const int et = tid - 64;
-    if (et < rows_own) {
-      float ssum = 0.f;
-      for (int k = et; k < NUM_EPI_THREADS; k += rows_own) ssum += db_part[k];
-      p.db[i * TILE_M + (int)j * rows_own + et] = ssum;
-    }
+  if (BWD && abort_flag == 0 && tid < rows_own) {
+    // feature tid of my chunk = pair tid/2, element tid%2, summed over the batch slots
+    const int pairs = rows_own / 2;
+    float ssum = 0.f;
+    for (int k = tid / 2; k < NUM_EPI_THREADS; k += pairs) ssum += db_part[tid & 1][k];
+    p.db[i * TILE_M + (int)j * rows_own + tid] = ssum;
   }
   // no CTA may exit while a peer can still address its shared memory
   cluster_sync_all();
-  if (warp == 1) {
-    uint32_t cols = 2 * Npad < 32 ? 32 : 2 * Npad;
-    uint32_t pow2 = 32;
-    while (pow2 < cols) pow2 <<= 1;
-    ptx::tmem_dealloc(tmem_base, pow2);
-  }
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, tmem_cols);
 }
 
 // ---------------------------------------------------------------------------
@@ -447,7 +670,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-int make_state_tmap(CUtensorMap* out, const void* base, int slots, int B, int d, int box_rows) {
+int make_state_tmap(CUtensorMap* out, const void* base, int slots, int B, int d, int box_rows,
+                    int box_tiles) {
   static EncodeTiledFn fn = nullptr;
   if (fn == nullptr) {
     void* ptr = nullptr;
@@ -459,11 +683,13 @@ int make_state_tmap(CUtensorMap* out, const void* base, int slots, int B, int d,
     }
     fn = (EncodeTiledFn)ptr;
   }
-  cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)B, (cuuint64_t)slots};
-  cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)B * d * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+  // view [slots][B][d/64][64]: dim0 = 64 columns (one 128-byte swizzle row), dim1 = batch row,
+  // dim2 = 64-column tile index, dim3 = time slot; a box covers box_tiles tiles at once
+  cuuint64_t dims[4] = {64, (cuuint64_t)B, (cuuint64_t)(d / 64), (cuuint64_t)slots};
+  cuuint64_t strides[3] = {(cuuint64_t)d * 2, 128, (cuuint64_t)B * d * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_tiles, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides,
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS)
@@ -472,7 +698,8 @@ int make_state_tmap(CUtensorMap* out, const void* base, int slots, int B, int d,
 }
 
 struct RecPlan {
-  int S, Kc, G, Ng, Npad, nstages;
+  int S, Kc, G, Ng, Npad, nstages, nmw;
+  uint32_t tmem_cols;
   size_t smem;
   bool ok;
 };
@@ -480,7 +707,7 @@ struct RecPlan {
 size_t plan_smem(int S, int Kc, int Npad, int nstages) {
   size_t w = (size_t)TILE_M * Kc * 2;
   size_t st = (size_t)nstages * Npad * Kc * 2;
-  size_t stg = (size_t)2 * TILE_M * (Npad + 1) * 4;
+  size_t stg = (size_t)2 * TILE_M * Npad * 4;
   (void)S;
   return w + st + stg + 1024 + 64;
 }
@@ -505,23 +732,32 @@ RecPlan make_plan(int T, int B, int d) {
   }
   if (best_S == 0) return pl;
   const int S = best_S, Kc = d / S;
-  // batch groups: Ng <= MAX_E * S and Ng <= 32 by default; groups must tile B exactly
+  // batch groups: Ng <= 8 * MAX_QUADS * S and Ng <= 32 by default; groups must tile B exactly
   int G = 0, Ng = 0;
   if (want_G > 0) {
     if (B % want_G != 0) return pl;
     G = (int)want_G;
     Ng = B / G;
   } else {
-    int cap = MAX_E * S < 32 ? MAX_E * S : 32;
+    int cap = 8 * MAX_QUADS * S < 32 ? 8 * MAX_QUADS * S : 32;
     for (int g = 1; g <= MAX_GROUPS; ++g) {
       if (B % g != 0) continue;
       if (B / g <= cap) { G = g; Ng = B / g; break; }
     }
     if (G == 0) return pl;
   }
-  if (G > MAX_GROUPS || Ng > MAX_E * S || Ng > 256) return pl;
+  if (G > MAX_GROUPS || Ng > 8 * MAX_QUADS * S || Ng > 256) return pl;
   int Npad = (Ng + 15) / 16 * 16;
-  if (2 * Npad > 512) return pl;
+  int nmw = (int)options().rec_mma_warps;
+  if (nmw <= 0) nmw = NUM_MMA_WARPS;
+  if (nmw > NUM_MMA_WARPS) nmw = NUM_MMA_WARPS;
+  if (nmw > Kc / 16) nmw = Kc / 16;
+  while (nmw > 1 && 2 * nmw * Npad > 512) --nmw;
+  if (2 * nmw * Npad > 512) return pl;
+  uint32_t cols = 32;
+  while (cols < (uint32_t)(2 * nmw * Npad)) cols <<= 1;
+  pl.nmw = nmw;
+  pl.tmem_cols = cols;
   int nstages = 4;
   while (nstages > 2 && plan_smem(S, Kc, Npad, nstages) > smem_cap) --nstages;
   if (plan_smem(S, Kc, Npad, nstages) > smem_cap) return pl;
@@ -537,7 +773,7 @@ int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* 
   auto kern = rec_tc_kernel<BWD>;
   CUtensorMap tmW, tmState;
   ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmW, W, (uint64_t)p.d, (uint64_t)p.d, (uint64_t)p.d, TILE_M));
-  ELMAN_RETURN_IF(make_state_tmap(&tmState, state, p.T + 1, p.B, p.d, pl.Npad));
+  ELMAN_RETURN_IF(make_state_tmap(&tmState, state, p.T + 1, p.B, p.d, pl.Npad, pl.Kc / 64));
   ELMAN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)pl.smem));
   cudaLaunchConfig_t cfg{};
@@ -565,6 +801,7 @@ int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* 
 
 void fill_plan(const RecPlan& pl, RecTcParams& p) {
   p.S = pl.S; p.Kc = pl.Kc; p.G = pl.G; p.Ng = pl.Ng; p.Npad = pl.Npad; p.nstages = pl.nstages;
+  p.nmw = pl.nmw; p.tmem_cols = pl.tmem_cols;
   p.R = p.d / TILE_M;
   p.spin_limit = options().spin_limit;
   p.status = device_status_ptr();
@@ -575,7 +812,23 @@ void fill_plan(const RecPlan& pl, RecTcParams& p) {
 bool rec_tc_supported(int T, int B, int d) { return make_plan(T, B, d).ok; }
 
 size_t rec_tc_sync_bytes() {
-  return (size_t)(MAX_GROUPS * MAX_S * COUNTER_STRIDE + 64) * sizeof(int);
+  return (size_t)(MAX_GROUPS * MAX_S * COUNTER_STRIDE + 64) * sizeof(int) +
+         (size_t)TRACE_STEPS * TRACE_SLOTS * sizeof(long long);
+}
+
+static long long* g_last_trace = nullptr;
+static long long* trace_area(int* sync) {
+  if (options().rec_trace == 0) return nullptr;
+  g_last_trace = (long long*)(sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE + 64);
+  return g_last_trace;
+}
+int rec_tc_copy_trace(long long* dst, int max_entries) {
+  if (g_last_trace == nullptr) return set_error(ELMAN_ERR_ARG, "no trace was recorded");
+  int n = TRACE_STEPS * TRACE_SLOTS;
+  if (n > max_entries) n = max_entries;
+  ELMAN_CUDA_CHECK(cudaMemcpy(dst, g_last_trace, (size_t)n * sizeof(long long),
+                              cudaMemcpyDeviceToHost));
+  return ELMAN_OK;
 }
 
 int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
@@ -589,6 +842,7 @@ int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
   ELMAN_CUDA_CHECK(cudaMemsetAsync(a.sync, 0, rec_tc_sync_bytes(), stream));
   p.ready = a.sync;
   p.abort_word = a.sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE;
+  p.trace = trace_area(a.sync);
   return launch_rec_tc<false>(pl, p, a.W, a.h, stream);
 }
 
@@ -606,6 +860,7 @@ int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream) {
                                    (size_t)a.B * a.d * sizeof(bf16), stream));
   p.ready = a.sync;
   p.abort_word = a.sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE;
+  p.trace = trace_area(a.sync);
   return launch_rec_tc<true>(pl, p, a.Wt, a.dv, stream);
 }
 

@@ -61,6 +61,9 @@ int elman_b200_device_status(int* detail, int clear);
  *   "rec_ksplit"     K-split (cluster size) of the tensor-core recurrence, 0 = auto
  *   "rec_groups"     independent batch groups pipelined by the recurrence, 0 = auto
  *   "time_kernels"   1 = bracket the phases of E1/E0 calls with CUDA events
+ *   "rec_trace"      1 = the tensor-core recurrence records per-step cycle stamps
+ *   "rec_mma_warps"  MMA-issuing warps (independent accumulator chains) of the
+ *                    tensor-core recurrence, 1..4, 0 = auto
  * Returns ELMAN_OK or ELMAN_ERR_ARG for an unknown name.
  */
 int elman_b200_set_option(const char* name, long value);
@@ -84,6 +87,18 @@ int elman_b200_wait_probe(long spin_limit, void* scratch, void* stream);
  * most recent call.
  */
 int elman_b200_last_timing(int phase, float* ms);
+
+/*
+ * Diagnostics hook (no counterpart in the reference).  With option "rec_trace"
+ * set, CTA 0 of the tensor-core recurrence kernel stores SM cycle stamps for its
+ * first 64 steps, 16 slots per step: 0 dependency satisfied, 1 TMA issued,
+ * 2 state tile landed, 3 MMAs issued, 4 accumulator complete, 5 partials
+ * scattered, 6 all partials landed, 7 new state stored, 8 epilogue threads met,
+ * 9 step published, 10 next inputs requested.  This call synchronises and copies
+ * up to max_entries stamps of the most recent traced launch into dst (host).
+ * The buffer lives in that call's workspace, which must still be allocated.
+ */
+int elman_b200_recurrence_trace(long long* dst, int max_entries);
 
 /* Number of this library's kernel launches since load (for launch accounting). */
 long elman_b200_launch_count(void);
