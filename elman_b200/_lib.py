@@ -38,6 +38,8 @@ SIGNATURES = {
     "elman_b200_tc_launch_count": (_L, []),
     "elman_e1_forward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e1_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 6 + [_P] * 3 + [_P, _Z, _P]),
+    "elman_e1_forward_static_scratch_bytes": (_Z, []),
+    "elman_e1_forward_static": (_I, [_I, _I, _I, _I, _I] + [_P] * 6 + [_P] * 3 + [_P]),
     "elman_e1_backward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e1_backward": (_I, [_I, _I, _I, _I] + [_P] * 7 + [_P] * 5 + [_P, _Z, _P]),
     "elman_e0_forward_workspace": (_Z, [_I, _I, _I, _I]),

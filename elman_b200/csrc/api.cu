@@ -60,9 +60,15 @@ static int ensure_status(int dev) {
   return 0;
 }
 
+// Set while an entry point that promises not to allocate is running on this thread.
+static thread_local bool g_no_alloc = false;
+
 int* device_status_ptr() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (g_no_alloc) {  // use the status word only if an earlier call already created it
+    return (dev >= 0 && dev < kMaxDevices) ? g_status_dev[dev] : nullptr;
+  }
   if (ensure_status(dev) != 0) return nullptr;
   return g_status_dev[dev];
 }
@@ -162,7 +168,8 @@ struct PhaseTimer {
   int phase;
   cudaStream_t st;
   bool on;
-  PhaseTimer(int ph, cudaStream_t s) : phase(ph), st(s), on(options().time_kernels != 0) {
+  PhaseTimer(int ph, cudaStream_t s)
+      : phase(ph), st(s), on(options().time_kernels != 0 && !g_no_alloc) {
     if (!on) return;
     if (!g_ev_ready) {
       for (int i = 0; i < kPhases; ++i)
@@ -368,6 +375,59 @@ int elman_e1_backward(int dtype, int T, int B, int d, const void* W_x, const voi
   ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, w.dvT, false, w.xT, false, dW_x, st));
   ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, w.dvT, true, w.xT, false, dW_h, st));
   return ELMAN_OK;
+}
+
+// ---------------- E1 forward for callers that cannot allocate ----------------
+//
+// The scratch the forward pass needs (the projected inputs W_x x_t + b for all t,
+// plus the step counters) lives in this file-scope device array instead of a
+// caller-provided workspace.  Every device that loads the library carries the
+// array until the process exits.
+static __device__ __align__(256) unsigned char g_e1_static_scratch[ELMAN_E1_STATIC_SCRATCH_BYTES];
+// Device address of the array per device.  The symbol itself is only a host-side
+// handle; kernels must be given the address cudaGetSymbolAddress returns.
+static void* g_e1_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+size_t elman_e1_forward_static_scratch_bytes(void) { return ELMAN_E1_STATIC_SCRATCH_BYTES; }
+
+int elman_e1_forward_static(int dtype, int training, int T, int B, int d, const void* x,
+                            const void* z, const void* h0, const void* W_x, const void* W_h,
+                            const void* b, void* h, void* output, void* v, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (B == 0 || d == 0) return ELMAN_OK;
+  REQUIRE_PTR(h0); REQUIRE_PTR(h);
+  E1FwdWs w;
+  const size_t need = carve_e1_fwd(dtype, T, B, d, nullptr, &w);
+  if (need > (size_t)ELMAN_E1_STATIC_SCRATCH_BYTES)
+    return set_error(ELMAN_ERR_WORKSPACE,
+                     "T=%d B=%d d=%d needs %zu bytes of scratch; the built-in array of "
+                     "elman_e1_forward_static holds %zu (use elman_e1_forward with a workspace)",
+                     T, B, d, need, (size_t)ELMAN_E1_STATIC_SCRATCH_BYTES);
+  int dev = 0;
+  ELMAN_CUDA_CHECK(cudaGetDevice(&dev));
+  ELMAN_ARG_CHECK(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
+  if (g_e1_static_scratch_ptr[dev] == nullptr) {
+    // set-up, once per device, with that device current
+    void* ptr = nullptr;
+    ELMAN_CUDA_CHECK(cudaGetSymbolAddress((void**)&ptr, g_e1_static_scratch));
+    g_e1_static_scratch_ptr[dev] = ptr;
+  }
+  void* scratch = g_e1_static_scratch_ptr[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  struct NoAllocScope {
+    NoAllocScope() { g_no_alloc = true; }
+    ~NoAllocScope() { g_no_alloc = false; }
+  } scope;
+  ELMAN_RETURN_IF(copy_rows(dtype, h0, h, (long)B * d, st));
+  if (T == 0) return ELMAN_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(z); REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(b);
+  REQUIRE_PTR(output);
+  ELMAN_ARG_CHECK(!training || v != nullptr, "v must be provided when training");
+  carve_e1_fwd(dtype, T, B, d, scratch, &w);
+  // the step counters inside the array are cleared by the recurrence launcher on
+  // every call; the projected inputs are fully overwritten before they are read
+  ELMAN_RETURN_IF(proj_nt(dtype, T * B, d, d, x, d, W_x, d, b, w.pre, d, 0, st));
+  return run_rec_fwd(dtype, T, B, d, W_h, w.pre, z, h, output, training ? v : nullptr, w.sync, st);
 }
 
 // ------------------------------- E0 ----------------------------------------

@@ -132,6 +132,42 @@ int elman_e1_backward(int dtype, int T, int B, int d,
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * E1 forward for callers that cannot allocate device memory.
+ *
+ * This entry point has no counterpart in the reference.  It exists for callers
+ * that hold no allocator they may call at this point: code running inside a
+ * stream capture or a real-time section where cudaMalloc (which may synchronise
+ * the device) is forbidden, plugins of a host application that owns all device
+ * memory and hands out only tensors, or a C caller that simply has no workspace
+ * to give.  It computes exactly what elman_e1_forward computes and takes the same
+ * inputs and outputs, but no workspace: the scratch of the pass (the projected
+ * inputs for all time steps and the step counters) lives in a device array built
+ * into the library, ELMAN_E1_STATIC_SCRATCH_BYTES large.  Every GPU that loads
+ * the library holds that array until the process exits.
+ *
+ * Limits and rules:
+ *  - the pass must fit: elman_e1_forward_workspace(dtype,T,B,d) <=
+ *    ELMAN_E1_STATIC_SCRATCH_BYTES, otherwise ELMAN_ERR_WORKSPACE is returned and
+ *    nothing is launched (bf16: roughly T*B*d <= 8.3 million elements);
+ *  - the first call on a device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *  - the call itself performs no cudaMalloc/cudaFree/cudaHostAlloc and calls no
+ *    allocating library routine;
+ *  - all calls on a device share the one array, which keeps the previous call's
+ *    contents: the parts that must start at zero are cleared on the stream by
+ *    each call, and two calls whose GPU work may overlap (different streams, or
+ *    different host threads on the same device) race on it — serialise them;
+ *  - bounded-wait failures are reported through the status word only if an
+ *    earlier (allocating) call already created it for this device.
+ * ------------------------------------------------------------------------- */
+#define ELMAN_E1_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+size_t elman_e1_forward_static_scratch_bytes(void);
+int elman_e1_forward_static(int dtype, int training, int T, int B, int d,
+                            const void* x, const void* z, const void* h0,
+                            const void* W_x, const void* W_h, const void* b,
+                            void* h, void* output, void* v, void* stream);
+
+/* ---------------------------------------------------------------------------
  * E0 — stock Elman cell with a learned, x-only output gate.
  *   h_t as E1,  y_t = h_t * silu(W_gate x_t + b_gate)
  * Replaces stock_elman_forward / stock_elman_backward
