@@ -39,7 +39,7 @@ T, B, D = 512, 32, 1280
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes per launch of the dominant kernel from the committed ncu capture
 # (profiles/), or None while no capture of the current kernel exists.
-NCU_TRAFFIC_BYTES = {"rec_tc_kernel<fwd>": None, "rec_tc_kernel<bwd>": None}
+NCU_TRAFFIC_BYTES = {"rec_tc_kernel<fwd>": 169.9e6, "rec_tc_kernel<bwd>": 231.4e6}  # profiles/rec_tc_kernel_e1_c1.md
 
 
 def parse_args():
@@ -47,7 +47,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_cuda"],
+                    help="ours | reference (the reference's CPU path) | reference_cuda (the "
+                         "reference's own CUDA kernels rebuilt for sm_100, if oracle/_ref exists)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=128,
                     help="time steps of the workload the CPU baseline runs")
@@ -169,6 +171,44 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_cuda(args, rank, local_rank):
+    """The reference's unmodified CUDA kernels (cuBLAS GEMM + elementwise kernels per time
+    step) on the same GPU and inputs; prints the same JSON line with impl=reference_cuda."""
+    if rank != 0:
+        return
+    from oracle import ref_cuda
+    if not (torch.cuda.is_available() and ref_cuda.available()):
+        print(json.dumps({"impl": "reference_cuda",
+                          "unavailable": "oracle/_ref/libelman_ref_cuda.so not built or no GPU"}))
+        return
+    torch.cuda.set_device(local_rank)
+    inp = make_inputs(1234)
+    d = {k: v.to(torch.bfloat16).cuda().contiguous() for k, v in inp.items()}
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+
+    def step():
+        h, out, v, _ = ref_cuda.e1_forward(True, d["x"], d["z"], d["h0"], d["W_x"], d["W_h"], d["b"])
+        return ref_cuda.e1_backward(d["W_x"], d["W_h"], d["x"], d["z"], h, v, d["d_output"])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(args.steps):
+        flush_buf.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); step(); e.record(); e.synchronize()
+        total += s.elapsed_time(e)
+    value = B * T * args.steps / (total / 1e3)
+    print(json.dumps({
+        "impl": "reference_cuda", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total / args.steps,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "configs[1]: E1 cell fwd+bwd, bf16, d=1280, B=32, T=512",
+                   "what": "reference kernels (elman/cuda/lib, unmodified) compiled for sm_100"}}),
+        flush=True)
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -177,6 +217,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.impl == "reference_cuda":
+        run_reference_cuda(args, rank, local_rank)
         return
 
     import torch.distributed as dist
