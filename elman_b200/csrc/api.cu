@@ -131,11 +131,11 @@ static int proj_nt(int dtype, int M, int N, int K, const void* A, int lda, const
 static int gemm_nn(int dtype, int M, int N, int K, const void* A, int lda, const void* Bm, int ldb,
                    void* Bt, void* C, int ldc, int accumulate, cudaStream_t st) {
   if (M == 0 || N == 0) return ELMAN_OK;
-  if (use_tc(dtype) && Bt != nullptr && ldb == N &&
-      gemm_tc_supported(M, N, K, A, lda, Bt, K, C, ldc, 0)) {
-    ELMAN_RETURN_IF(transpose2d(dtype, K, N, Bm, Bt, st));
-    return gemm_tc_nt(M, N, K, (const bf16*)A, lda, (const bf16*)Bt, K, nullptr, C, ldc, 0,
-                      accumulate, st);
+  (void)Bt;
+  if (use_tc(dtype) && (N & 7) == 0 && gemm_tc_supported(M, N, K, A, lda, Bm, ldb, C, ldc, 0)) {
+    // Bm is [K, N] with N contiguous: an MN-major B operand, read in place
+    return gemm_tc(M, N, K, (const bf16*)A, lda, 0, (const bf16*)Bm, ldb, 1, nullptr, C, ldc, 0,
+                   accumulate, st);
   }
   return gemm_generic(dtype, M, N, K, A, lda, 1, Bm, ldb, 1, nullptr, C, ldc, accumulate, st);
 }
@@ -146,12 +146,12 @@ static int gemm_nn(int dtype, int M, int N, int K, const void* A, int lda, const
 static int gemm_tn(int dtype, int M, int N, long K, const void* Am, const void* Bm, void* AT,
                    bool at_ready, void* BT, bool bt_ready, void* C, cudaStream_t st) {
   if (M == 0 || N == 0) return ELMAN_OK;
-  if (use_tc(dtype) && AT != nullptr && BT != nullptr && K < (1L << 31) &&
-      gemm_tc_supported(M, N, (int)K, AT, (int)K, BT, (int)K, C, N, 0)) {
-    if (!at_ready) ELMAN_RETURN_IF(transpose2d(dtype, (int)K, M, Am, AT, st));
-    if (!bt_ready) ELMAN_RETURN_IF(transpose2d(dtype, (int)K, N, Bm, BT, st));
-    return gemm_tc_nt(M, N, (int)K, (const bf16*)AT, (int)K, (const bf16*)BT, (int)K, nullptr, C,
-                      N, 0, 0, st);
+  (void)AT; (void)BT; (void)at_ready; (void)bt_ready;
+  if (use_tc(dtype) && K < (1L << 31) && (M & 7) == 0 && (N & 7) == 0 && (K & 7) == 0 &&
+      gemm_tc_supported(M, N, (int)K, Am, M, Bm, N, C, N, 0)) {
+    // both operands are [K, *] with the M / N extent contiguous: MN-major A and B
+    return gemm_tc(M, N, (int)K, (const bf16*)Am, M, 1, (const bf16*)Bm, N, 1, nullptr, C, N, 0, 0,
+                   st);
   }
   return gemm_generic(dtype, M, N, (int)K, Am, 1, M, Bm, N, 1, nullptr, C, N, 0, st);
 }
@@ -210,13 +210,7 @@ static size_t carve_e1_bwd(int dtype, int T, int B, int d, void* ws, E1BwdWs* o)
   o->db = (float*)c.take((size_t)d * sizeof(float));
   size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
   o->sync = (int*)c.take(sb);
-  if (dtype == ELMAN_BF16) {
-    o->WxT = c.take((size_t)d * d * es);
-    o->dvT = c.take((size_t)T * B * d * es);
-    o->xT = c.take((size_t)T * B * d * es);
-  } else {
-    o->WxT = o->dvT = o->xT = nullptr;
-  }
+  o->WxT = o->dvT = o->xT = nullptr;  // the GEMMs read transposed operands in place
   return c.total();
 }
 
@@ -487,13 +481,7 @@ static size_t carve_e0_bwd(int dtype, int T, int B, int d, void* ws, E0BwdWs* o)
   o->cs = (float*)c.take(column_sum_scratch_bytes(d));
   size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
   o->sync = (int*)c.take(sb);
-  if (dtype == ELMAN_BF16) {
-    o->WT2 = c.take((size_t)d * d * es);
-    o->dvT = c.take((size_t)T * B * d * es);
-    o->xT = c.take((size_t)T * B * d * es);
-  } else {
-    o->WT2 = o->dvT = o->xT = nullptr;
-  }
+  o->WT2 = o->dvT = o->xT = nullptr;  // the GEMMs read transposed operands in place
   return c.total();
 }
 

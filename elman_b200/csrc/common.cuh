@@ -113,6 +113,11 @@ int gemm_generic(int dtype, int M, int N, int K, const void* A, long sAm, long s
 int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int ldw,
                const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
                cudaStream_t stream);
+// General form: a_mn / b_mn != 0 mean the operand is stored [K, M] resp. [K, N]
+// (MN-major), which the tensor core reads directly — no transpose pass.
+int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
+            int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
+            cudaStream_t stream);
 bool gemm_tc_supported(int M, int N, int K, const void* A, int lda, const void* W, int ldw,
                        const void* C, int ldc, int c_is_f32);
 

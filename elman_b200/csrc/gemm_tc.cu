@@ -33,6 +33,8 @@ struct GemmParams {
   int accumulate;
   long spin_limit;
   int* status;
+  int a_mn;  // A is given as [K, M] (M contiguous): MN-major operand, no transpose pass
+  int b_mn;  // W is given as [K, N] (N contiguous)
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -89,14 +91,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           break;
         }
         ptx::mbar_arrive_expect_tx(&full_bar[s], A_TILE_BYTES + B_TILE_BYTES);
-        ptx::tma_load_2d(sA + s * A_TILE_BYTES, &tmA, i * BK, m0, &full_bar[s]);
-        ptx::tma_load_2d(sB + s * B_TILE_BYTES, &tmB, i * BK, n0, &full_bar[s]);
+        if (p.a_mn) {  // two boxes of [64 K rows x 64 M elements]
+          ptx::tma_load_2d(sA + s * A_TILE_BYTES, &tmA, m0, i * BK, &full_bar[s]);
+          ptx::tma_load_2d(sA + s * A_TILE_BYTES + A_TILE_BYTES / 2, &tmA, m0 + 64, i * BK,
+                           &full_bar[s]);
+        } else {
+          ptx::tma_load_2d(sA + s * A_TILE_BYTES, &tmA, i * BK, m0, &full_bar[s]);
+        }
+        if (p.b_mn) {
+          ptx::tma_load_2d(sB + s * B_TILE_BYTES, &tmB, n0, i * BK, &full_bar[s]);
+          ptx::tma_load_2d(sB + s * B_TILE_BYTES + B_TILE_BYTES / 2, &tmB, n0 + 64, i * BK,
+                           &full_bar[s]);
+        } else {
+          ptx::tma_load_2d(sB + s * B_TILE_BYTES, &tmB, i * BK, n0, &full_bar[s]);
+        }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::umma_idesc_bf16(BM, BN);
+      const uint32_t idesc = ptx::umma_idesc_bf16(BM, BN) | (p.a_mn ? (1u << 15) : 0u) |
+                             (p.b_mn ? (1u << 16) : 0u);
       bool ok = true;
       for (int i = 0; i < nk && ok; ++i) {
         const int s = i % STAGES;
@@ -108,13 +123,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           break;
         }
         ptx::tc_fence_after();
-        const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(sA + s * A_TILE_BYTES));
-        const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(sB + s * B_TILE_BYTES));
+        const uint32_t a_addr = ptx::smem_u32(sA + s * A_TILE_BYTES);
+        const uint32_t b_addr = ptx::smem_u32(sB + s * B_TILE_BYTES);
+        const uint64_t da = p.a_mn ? ptx::umma_desc_mn_sw128(a_addr, A_TILE_BYTES / 2)
+                                   : ptx::umma_desc_k_sw128(a_addr);
+        const uint64_t db = p.b_mn ? ptx::umma_desc_mn_sw128(b_addr, B_TILE_BYTES / 2)
+                                   : ptx::umma_desc_k_sw128(b_addr);
+        // one K=16 step: 32 bytes along a K-major row (2 address units), or two 8-row
+        // groups = 2048 bytes of an MN-major tile (128 address units)
+        const uint64_t a_step = p.a_mn ? 128 : 2, b_step = p.b_mn ? 128 : 2;
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {
-          // 16 bf16 along K = 32 bytes = 2 descriptor address units
-          ptx::umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-        }
+        for (int k = 0; k < BK / 16; ++k)
+          ptx::umma_bf16(tmem_base, da + a_step * k, db + b_step * k, idesc,
+                         (i > 0 || k > 0) ? 1u : 0u);
         ptx::umma_commit(&empty_bar[s]);  // frees the stage when these MMAs retire
       }
       if (ok) ptx::umma_commit(&acc_bar);
@@ -255,6 +276,8 @@ bool gemm_tc_supported(int M, int N, int K, const void* A, int lda, const void* 
                        const void* C, int ldc, int c_is_f32) {
   (void)C; (void)ldc; (void)c_is_f32;
   if (M < 1 || N < 1 || K < 8) return false;
+  // (for an MN-major operand the contiguous extent is M or N instead of K; the callers
+  // of that form pass matrices whose both extents are multiples of 8)
   if ((K & 7) != 0 || (lda & 7) != 0 || (ldw & 7) != 0) return false;
   if (((uintptr_t)A & 15) != 0 || ((uintptr_t)W & 15) != 0) return false;
   return get_encode_fn() != nullptr;
@@ -263,6 +286,12 @@ bool gemm_tc_supported(int M, int N, int K, const void* A, int lda, const void* 
 int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int ldw,
                const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
                cudaStream_t stream) {
+  return gemm_tc(M, N, K, A, lda, 0, W, ldw, 0, bias, C, ldc, c_is_f32, accumulate, stream);
+}
+
+int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
+            int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
+            cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     ELMAN_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -270,13 +299,20 @@ int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int l
     attr_set = true;
   }
   CUtensorMap tmA, tmB;
-  ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM));
-  ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN));
+  if (a_mn)
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK));
+  else
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM));
+  if (b_mn)
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, BK));
+  else
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, BN));
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.bias = bias; p.C = C; p.ldc = ldc; p.c_is_f32 = c_is_f32; p.accumulate = accumulate;
   p.spin_limit = options().spin_limit;
   p.status = device_status_ptr();
+  p.a_mn = a_mn; p.b_mn = b_mn;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, p);
   count_launch(true);

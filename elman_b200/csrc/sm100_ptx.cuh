@@ -141,6 +141,22 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory matrix descriptor for an MN-major bf16 operand: the tile is stored as
+// rows of K, each row holding 64 consecutive M (or N) elements = 128 bytes, written by
+// TMA with 128-byte swizzle from a [K, MN] row-major matrix.  Groups of 8 K rows are
+// 1024 bytes apart (stride byte offset); the next block of 64 MN elements starts
+// `mn_block_bytes` further on (leading byte offset).  One K=16 MMA step covers two
+// 8-row groups: stepping 16 along K adds 2048 bytes to the start address.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((mn_block_bytes >> 4) & 0x3FFF) << 16;  // leading byte offset
+  d |= (uint64_t)(1024 >> 4) << 32;                       // stride byte offset
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // Instruction descriptor: kind::f16, A and B bf16 K-major, fp32 accumulate.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) |
