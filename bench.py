@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_cuda"],
                     help="ours | reference (the reference's CPU path) | reference_cuda (the "
                          "reference's own CUDA kernels rebuilt for sm_100, if oracle/_ref exists)")
+    ap.add_argument("--workload", default="cell", choices=["cell", "lm"],
+                    help="cell = configs[1] (the headline line); lm = configs[2] training step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=128,
                     help="time steps of the workload the CPU baseline runs")
@@ -209,12 +211,111 @@ def run_reference_cuda(args, rank, local_rank):
         flush=True)
 
 
+class _RefCudaBackend:
+    """Routes the E1 extension functions to the reference's own CUDA kernels (oracle/_ref);
+    used only by `--workload lm --impl reference_cuda` to time the reference LM step."""
+
+    @staticmethod
+    def mamba_gated_elman_forward(training, x, z, h0, W_x, W_h, b):
+        from oracle import ref_cuda
+        h, out, v, ws = ref_cuda.e1_forward(training, x, z, h0, W_x, W_h, b)
+        ws.record_stream(torch.cuda.current_stream())
+        return [h, out, v]
+
+    @staticmethod
+    def mamba_gated_elman_backward(W_x, W_h, x, z, h, v, d_output):
+        from oracle import ref_cuda
+        r = ref_cuda.e1_backward(W_x, W_h, x, z, h, v, d_output)
+        r[5].record_stream(torch.cuda.current_stream())
+        return list(r[:5])
+
+
+def run_lm(args, rank, world, local_rank):
+    """configs[2]: full E1 byte-level LM (d=1280 x 6 layers, 49.5M parameters), bf16, AdamW,
+    T=512, 32 sequences per GPU, seeded Zipf(1.1) token ids; one step = forward, loss,
+    backward, gradient clipping, optimizer step; data-parallel with DDP over NCCL for N > 1."""
+    import torch.distributed as dist
+    from elman_b200 import _lib
+    from elman_b200 import ladder_lm, mamba_gated_elman
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group(backend="nccl", device_id=dev)
+    if args.impl == "reference_cuda":
+        from oracle import ref_cuda
+        if not ref_cuda.available():
+            if rank == 0:
+                print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref not built"}))
+            return
+        mamba_gated_elman.hasty_pytorch_lib = _RefCudaBackend
+    torch.manual_seed(1234)
+    model = ladder_lm.LadderLM(vocab_size=256, dim=D, depth=6, level=1, expansion=1.0)
+    model = model.to(dev).bfloat16()
+    net = model
+    if world > 1:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank],
+                                                        find_unused_parameters=False)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    host_tokens = ladder_lm.zipf_tokens(B, T + 1, seed=1234 + rank).pin_memory()
+
+    def step():
+        tok = host_tokens.to(dev, non_blocking=True)
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+            loss = net(tok, return_loss=True)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    launches0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        loss = step()
+    ev1.record()
+    loss_val = float(loss)           # device -> host read of the step's result
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    t_all = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+    ms = float(t_all.cpu())
+    if rank == 0:
+        value = B * T * world * args.steps / (ms / 1e3)
+        print(json.dumps({
+            "impl": args.impl, "metric": "E1 d1280x6 LM training tokens/s (B32 x T512 per GPU)",
+            "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[2]: LadderLM level 1, d=1280, depth 6, AdamW, "
+                                   "Zipf(1.1) tokens, DDP" + (" (NCCL)" if world > 1 else ""),
+                       "params": model.get_num_params()},
+            "final_loss": loss_val,
+            "gpu_launches": _lib.launch_count() - launches0}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    if args.workload == "lm":
+        run_lm(args, rank, world, local_rank)
+        return
     if args.impl == "reference":
         run_reference(args, rank)
         return

@@ -128,10 +128,39 @@ def run_e1_layer(mod, B, T, dim, seed):
     return inp, res
 
 
+def run_ladder_lm(reference_root, seed):
+    """The reference's LadderLM (level 1, spectral-norm W_h as it defaults to) on seeded
+    token ids: loss and every parameter gradient.  Importing it pulls in the whole
+    `elman.models` package (slow, tens of seconds)."""
+    sys.path.insert(0, reference_root)
+    from elman.models.ladder_lm import LadderLM  # noqa: E402
+    torch.manual_seed(seed)
+    model = LadderLM(vocab_size=256, dim=32, depth=2, level=1, expansion=1.0)
+    g = torch.Generator().manual_seed(seed + 1)
+    tokens = torch.randint(0, 256, (3, 13), generator=g)
+    us = {}
+    for i, layer in enumerate(model.layers):  # pin the power-iteration start vectors
+        u = torch.randn(32, generator=g)
+        layer.cell._spectral_u = u / u.norm()
+        us[f"spectral_u_{i}"] = layer.cell._spectral_u.clone()
+    inp = {"tokens": tokens, **us}
+    inp.update({"p_" + k: v.detach().clone() for k, v in model.state_dict().items()})
+    loss = model(tokens, return_loss=True)
+    loss.backward()
+    res = {"loss": loss.detach().reshape(1)}
+    res.update({"g_" + k: p.grad for k, p in model.named_parameters()})
+    return inp, res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only-lm", action="store_true")
     args = ap.parse_args()
+    if args.only_lm:
+        inp, res = run_ladder_lm(args.reference, seed=51)
+        save("ladder_lm", True, inp, res, [3, 12, 32, 51])
+        return
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     torch.manual_seed(0)
 
@@ -164,6 +193,9 @@ def main():
 
     inp, res = run_e1_layer(m1, 2, 8, 64, seed=41)
     save("e1_layer", True, inp, res, [2, 8, 64, 41])
+
+    inp, res = run_ladder_lm(args.reference, seed=51)
+    save("ladder_lm", True, inp, res, [3, 12, 32, 51])
 
 
 if __name__ == "__main__":

@@ -1,0 +1,96 @@
+"""The LM wrapper (the caller of the hot path) on the CPU, against the fixture the
+reference's LadderLM produced, and its data-parallel training step on two gloo ranks.
+The CUDA library is replaced by the oracle-backed stand-in of test_host_logic (test only)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from elman_b200 import ladder_lm
+from elman_b200 import mamba_gated_elman as e1mod
+from oracle import elman_oracle as orc
+from tests.test_host_logic import OracleBackend
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+class _FakeCudaLayer(e1mod.MambaGatedElman):
+    """E1 layer whose cell input answers is_cuda=True, so the CPU stand-in can run."""
+
+    def forward(self, x, h0=None, **kw):
+        from tests.test_host_logic import as_fake_cuda
+        return super().forward(as_fake_cuda(x), h0, **kw)
+
+
+def _build(fix, monkeypatch_fn):
+    monkeypatch_fn(e1mod, "hasty_pytorch_lib", OracleBackend)
+    monkeypatch_fn(ladder_lm, "_LEVELS", {**ladder_lm._LEVELS, 1: _FakeCudaLayer})
+    model = ladder_lm.LadderLM(vocab_size=256, dim=32, depth=2, level=1, expansion=1.0)
+    sd = {k[5:]: torch.from_numpy(fix[k]) for k in fix.files if k.startswith("in_p_")}
+    assert set(sd) == set(model.state_dict()), "parameter names differ from the reference's"
+    model.load_state_dict(sd)
+    for i, layer in enumerate(model.layers):
+        layer.cell._spectral_u = torch.from_numpy(fix[f"in_spectral_u_{i}"]).clone()
+    return model
+
+
+def test_lm_loss_and_gradients_match_reference_fixture(monkeypatch):
+    fix = np.load(os.path.join(GOLDEN, "ladder_lm.npz"))
+    model = _build(fix, monkeypatch.setattr)
+    tokens = torch.from_numpy(fix["in_tokens"])
+    loss = model(tokens, return_loss=True)
+    loss.backward()
+    assert abs(float(loss) - float(fix["out_loss"][0])) < 1e-5
+    for k, p in model.named_parameters():
+        want = torch.from_numpy(fix["out_g_" + k])
+        assert orc.rel_err(p.grad, want) < 1e-4, k
+
+
+def test_lm_interfaces():
+    model = ladder_lm.LadderLM(vocab_size=256, dim=1280, depth=6, level=1, expansion=1.0)
+    assert model.get_num_params() == 49_496_320  # the "~50M" model of the benchmark
+    with pytest.raises(ValueError):
+        ladder_lm.get_ladder_level(7)
+    tok = ladder_lm.zipf_tokens(4, 33, seed=1)
+    assert tok.shape == (4, 33) and int(tok.min()) >= 0 and int(tok.max()) < 256
+    assert torch.equal(tok, ladder_lm.zipf_tokens(4, 33, seed=1))
+
+
+def _ddp_worker(rank, world, port, out):
+    torch.set_num_threads(1)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        fix = np.load(os.path.join(GOLDEN, "ladder_lm.npz"))
+
+        def setattr_(obj, name, val):
+            setattr(obj, name, val)
+        model = _build(fix, setattr_)
+        ddp = torch.nn.parallel.DistributedDataParallel(model)
+        tokens = ladder_lm.zipf_tokens(2, 9, seed=100 + rank)   # each rank its own shard
+        loss = ddp(tokens, return_loss=True)
+        loss.backward()
+        if rank == 0:
+            torch.save({k: p.grad.clone() for k, p in model.named_parameters()}, out)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_data_parallel_step_on_two_gloo_ranks_averages_shard_gradients(tmp_path, monkeypatch):
+    """world_size 2 on CPU: DDP's gradient equals the mean of the two shards' gradients."""
+    out = str(tmp_path / "grads.pt")
+    port = 29500 + (os.getpid() % 400)
+    mp.start_processes(_ddp_worker, args=(2, port, out), nprocs=2, join=True, start_method="spawn")
+    got = torch.load(out)
+    fix = np.load(os.path.join(GOLDEN, "ladder_lm.npz"))
+    ref = {}
+    for r in range(2):
+        model = _build(fix, monkeypatch.setattr)
+        model(ladder_lm.zipf_tokens(2, 9, seed=100 + r), return_loss=True).backward()
+        for k, p in model.named_parameters():
+            ref[k] = ref.get(k, 0) + p.grad / 2
+    for k in ref:
+        assert orc.rel_err(got[k], ref[k]) < 1e-5, k
