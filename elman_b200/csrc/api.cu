@@ -265,6 +265,8 @@ int elman_b200_set_option(const char* name, long value) {
   else if (!strcmp(name, "time_kernels")) o.time_kernels = value;
   else if (!strcmp(name, "rec_trace")) o.rec_trace = value;
   else if (!strcmp(name, "rec_mma_warps")) o.rec_mma_warps = value;
+  else if (!strcmp(name, "rec_direct_publish")) o.rec_direct_publish = value;
+  else if (!strcmp(name, "rec_w_tmem")) o.rec_w_tmem = value;
   else return set_error(ELMAN_ERR_ARG, "unknown option '%s'", name);
   return ELMAN_OK;
 }
@@ -279,6 +281,8 @@ long elman_b200_get_option(const char* name) {
   if (!strcmp(name, "time_kernels")) return o.time_kernels;
   if (!strcmp(name, "rec_trace")) return o.rec_trace;
   if (!strcmp(name, "rec_mma_warps")) return o.rec_mma_warps;
+  if (!strcmp(name, "rec_direct_publish")) return o.rec_direct_publish;
+  if (!strcmp(name, "rec_w_tmem")) return o.rec_w_tmem;
   return -1;
 }
 

@@ -48,6 +48,8 @@ struct Options {
   long time_kernels = 0;
   long rec_trace = 0;
   long rec_mma_warps = 0;
+  long rec_direct_publish = 0;
+  long rec_w_tmem = 0;
 };
 Options& options();
 void count_launch(bool tensor_core);

@@ -56,6 +56,10 @@ struct RecTcParams {
   int Npad;     // Ng rounded up to 16 (MMA N)
   int nstages;  // state ring depth
   int R;        // d / 128: producers per K slice and step
+  int direct_publish;  // 1: each epilogue warp releases the step counter itself
+  int w_tmem;          // 1: the resident tile of W lives in tensor memory (A operand from TMEM)
+  uint32_t w_col0;     // first TMEM column of that tile
+  const bf16* Wg;      // W in global memory (row-major [d,d]) for the one-time load
   int nmw;      // MMA-issuing warps (independent accumulator chains)
   uint32_t tmem_cols;
   // forward
@@ -332,20 +336,50 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const uint32_t tmem_base = tmem_slot;
   const int kid = BWD ? KID_REC_TC_BWD : KID_REC_TC_FWD;
 
+  if (p.w_tmem) {
+    // One-time load of my tile of W into tensor memory: row m of the tile goes to TMEM
+    // lane m, its Kc bf16 values packed two per 32-bit column.  The four epilogue
+    // warps cover the 128 lanes (warp w may touch lanes [32*(w%4), +32)).
+    if (warp > NUM_MMA_WARPS && warp <= NUM_MMA_WARPS + NUM_EPI_THREADS / 32) {
+      const int quarter = warp & 3;
+      const int m = quarter * 32 + lane;
+      const uint4* src = reinterpret_cast<const uint4*>(p.Wg + (long)(i * TILE_M + m) * p.d +
+                                                        (long)j * Kc);
+      const uint32_t tw = tmem_base + ((uint32_t)(quarter * 32) << 16) + p.w_col0;
+      for (int c = 0; c < Kc / 2; c += 16) {
+        uint32_t r[16];
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const uint4 w4 = __ldg(src + (c >> 2) + v4);
+          r[4 * v4] = w4.x; r[4 * v4 + 1] = w4.y; r[4 * v4 + 2] = w4.z; r[4 * v4 + 3] = w4.w;
+        }
+        ptx::tmem_st16(tw + (uint32_t)c, r);
+      }
+      ptx::tmem_st_wait();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+  }
+
   if (warp == 0) {
     // =========================== TMA producer ===============================
     if (lane == 0) {
-      // resident tile of W
-      ptx::mbar_arrive_expect_tx(&w_bar, (uint32_t)w_bytes);
-      for (int kk = 0; kk < nkt; ++kk)
-        ptx::tma_load_2d(sW + kk * (TILE_M * 128), &tmW, (int)j * Kc + kk * 64, i * TILE_M, &w_bar);
+      // resident tile of W (shared-memory variant)
+      if (!p.w_tmem) {
+        ptx::mbar_arrive_expect_tx(&w_bar, (uint32_t)w_bytes);
+        for (int kk = 0; kk < nkt; ++kk)
+          ptx::tma_load_2d(sW + kk * (TILE_M * 128), &tmW, (int)j * Kc + kk * 64, i * TILE_M,
+                           &w_bar);
+      }
       for (int q = 0; q < total_q; ++q) {
         const int step = q / G, grp = q - step * G;
         const int s = q % p.nstages;
         const uint32_t ph = (uint32_t)(q / p.nstages) & 1u;
         bool ok = waiter.wait(&empty_bar[s], ph ^ 1u);
         if (ok && step > 0)
-          ok = waiter.wait_counter(p.ready + (grp * MAX_S + (int)j) * COUNTER_STRIDE, step * p.R);
+          ok = waiter.wait_counter(p.ready + (grp * MAX_S + (int)j) * COUNTER_STRIDE,
+                                   step * p.R * (p.direct_publish ? NUM_EPI_THREADS / 32 : 1));
         if (!ok) {
           if (atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, kid, step);
           abort_flag = 1;
@@ -373,7 +407,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     if (lane == 0 && mw < nmw) {
       const uint32_t idesc = ptx::umma_idesc_bf16(TILE_M, Npad);
       const int nmma = nkt * 4;
-      bool ok = waiter.wait(&w_bar, 0);
+      bool ok = p.w_tmem ? true : waiter.wait(&w_bar, 0);
       for (int q = 0; q < total_q && ok; ++q) {
         const int s = q % p.nstages;
         const uint32_t ph = (uint32_t)(q / p.nstages) & 1u;
@@ -388,9 +422,14 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const uint32_t s0 = ptx::smem_u32(sState + s * state_stage_bytes);
         for (int m = mw; m < nmma; m += nmw) {
           const int kk = m >> 2, k = m & 3;
-          const uint64_t da = ptx::umma_desc_k_sw128(w0 + kk * (TILE_M * 128)) + 2 * k;
           const uint64_t db = ptx::umma_desc_k_sw128(s0 + kk * state_tile_bytes) + 2 * k;
-          ptx::umma_bf16(d_tmem, da, db, idesc, m >= nmw ? 1u : 0u);
+          if (p.w_tmem) {  // 16 bf16 of K = 8 columns of the tile in tensor memory
+            ptx::umma_bf16_ts(d_tmem, tmem_base + p.w_col0 + (uint32_t)(m * 8), db, idesc,
+                              m >= nmw ? 1u : 0u);
+          } else {
+            const uint64_t da = ptx::umma_desc_k_sw128(w0 + kk * (TILE_M * 128)) + 2 * k;
+            ptx::umma_bf16(d_tmem, da, db, idesc, m >= nmw ? 1u : 0u);
+          }
         }
         ptx::umma_commit(&empty_bar[s]);
         ptx::umma_commit(&acc_full_bar[a]);
@@ -417,6 +456,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const int qd0 = et / pairs;
     const int nquads = (Ng + 3) / 4;
     const int f = i * TILE_M + (int)j * rows_own + 2 * fp;  // first feature of the pair
+    const int my_kslice = (i * TILE_M + (int)j * rows_own) / Kc;
     const uint32_t stage_local = ptx::smem_u32(sStage);
     const long BD = (long)p.B * p.d;
     float db0 = 0.f, db1 = 0.f;
@@ -517,17 +557,21 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
                                (uint32_t)(a * nmw * Npad);
         for (int c = 0; c < Npad; c += 16) {
-          uint32_t r[16];
+          // all accumulators of this column chunk in flight at once, one wait
+          uint32_t r[16], rb[16], rc[16], rd[16];
           ptx::tmem_ld16(taddr + (uint32_t)c, r);
-          for (int w = 1; w < nmw; ++w) {
-            uint32_t r_[16];
-            ptx::tmem_ld16(taddr + (uint32_t)(w * Npad + c), r_);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int k = 0; k < 16; ++k)
-              r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(r_[k]));
-          }
+          if (nmw > 1) ptx::tmem_ld16(taddr + (uint32_t)(Npad + c), rb);
+          if (nmw > 2) ptx::tmem_ld16(taddr + (uint32_t)(2 * Npad + c), rc);
+          if (nmw > 3) ptx::tmem_ld16(taddr + (uint32_t)(3 * Npad + c), rd);
           ptx::tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            float acc = __uint_as_float(r[k]);
+            if (nmw > 1) acc += __uint_as_float(rb[k]);
+            if (nmw > 2) acc += __uint_as_float(rc[k]);
+            if (nmw > 3) acc += __uint_as_float(rd[k]);
+            r[k] = __float_as_uint(acc);
+          }
 #pragma unroll
           for (int k = 0; k < 16; k += 4)
             if (c + k < Ng)
@@ -552,7 +596,9 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           s0[e] = make_float4(0.f, 0.f, 0.f, 0.f);
           s1[e] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (qd < nquads) {
-            for (int src = 0; src < S; ++src) {
+#pragma unroll
+            for (int src = 0; src < MAX_S; ++src) {
+              if (src >= S) break;
               const uint32_t ad = stg + (uint32_t)(src * stg_src_floats + qd * rows_own * 4) * 4u;
               const float4 x0 = lds_f4(ad), x1 = lds_f4(ad + 16);
               s0[e].x += x0.x; s0[e].y += x0.y; s0[e].z += x0.z; s0[e].w += x0.w;
@@ -592,7 +638,12 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       // hand the publication of this chunk to the publisher warp: its gpu-scope
       // release would otherwise stall this warp's next loads and stores
       __syncwarp();
-      if (lane == 0 && good) ptx::mbar_arrive(&stored_bar[a]);
+      if (lane == 0 && good) {
+        if (p.direct_publish)  // one gpu-scope release per epilogue warp, no hand-off
+          red_release_gpu_add(p.ready + ((q - step * G) * MAX_S + my_kslice) * COUNTER_STRIDE, 1);
+        else
+          ptx::mbar_arrive(&stored_bar[a]);
+      }
       if (et == 0) stamp(p.trace, q, 7);  // new state stored
       // all 128 epilogue threads meet here, whether their waits succeeded or not,
       // and agree on whether to stop
@@ -620,6 +671,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           }
         }
       }
+      if (et == 0) stamp(p.trace, q, 15);  // late outputs stored
       if (q + 1 < total_q) prefetch(q + 1);
       if (et == 0) stamp(p.trace, q, 10);  // next step's inputs requested
     }
@@ -629,7 +681,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // Waits until the four epilogue warps have stored their part of the new state
     // (mbarrier, CTA scope), then bumps the step counter with a gpu-scope release:
     // the stores are ordered before the counter for every CTA that acquires it.
-    if (lane == 0) {
+    if (lane == 0 && !p.direct_publish) {
       const int my_kslice = (i * TILE_M + (int)j * rows_own) / Kc;
       for (int q = 0; q < total_q; ++q) {
         const int step = q / G, grp = q - step * G;
@@ -698,7 +750,7 @@ int make_state_tmap(CUtensorMap* out, const void* base, int slots, int B, int d,
 }
 
 struct RecPlan {
-  int S, Kc, G, Ng, Npad, nstages, nmw;
+  int S, Kc, G, Ng, Npad, nstages, nmw, w_tmem;
   uint32_t tmem_cols;
   size_t smem;
   bool ok;
@@ -712,34 +764,23 @@ size_t plan_smem(int S, int Kc, int Npad, int nstages) {
   return w + st + stg + 1024 + 64;
 }
 
-RecPlan make_plan(int T, int B, int d) {
+// Full plan for one K split S and one cap on the batch-group size, or ok == false.
+RecPlan plan_for(int B, int d, int S, int ng_cap) {
   RecPlan pl{};
   pl.ok = false;
-  if (T < 1 || B < 1 || d < 128 || (d % 128) != 0) return pl;
-  const size_t smem_cap = 200 * 1024;
-  long want_S = options().rec_ksplit;
-  long want_G = options().rec_groups;
-  int best_S = 0;
-  for (int S = MAX_S; S >= 1; S >>= 1) {
-    if (want_S > 0 && S != want_S) continue;
-    if (d % S != 0) continue;
-    int Kc = d / S;
-    if (Kc % 64 != 0) continue;
-    if ((d / 128) * S > 148) continue;
-    if (plan_smem(S, Kc, 16, 2) > smem_cap) continue;
-    best_S = S;
-    break;
-  }
-  if (best_S == 0) return pl;
-  const int S = best_S, Kc = d / S;
-  // batch groups: Ng <= 8 * MAX_QUADS * S and Ng <= 32 by default; groups must tile B exactly
+  pl.w_tmem = 0;
+  const size_t smem_cap = 225 * 1024;
+  if (d % S != 0) return pl;
+  const int Kc = d / S;
+  if (Kc % 64 != 0 || (d / 128) * S > 148) return pl;
+  const long want_G = options().rec_groups;
   int G = 0, Ng = 0;
   if (want_G > 0) {
     if (B % want_G != 0) return pl;
     G = (int)want_G;
     Ng = B / G;
   } else {
-    int cap = 8 * MAX_QUADS * S < 32 ? 8 * MAX_QUADS * S : 32;
+    int cap = 8 * MAX_QUADS * S < ng_cap ? 8 * MAX_QUADS * S : ng_cap;
     for (int g = 1; g <= MAX_GROUPS; ++g) {
       if (B % g != 0) continue;
       if (B / g <= cap) { G = g; Ng = B / g; break; }
@@ -747,24 +788,86 @@ RecPlan make_plan(int T, int B, int d) {
     if (G == 0) return pl;
   }
   if (G > MAX_GROUPS || Ng > 8 * MAX_QUADS * S || Ng > 256) return pl;
-  int Npad = (Ng + 15) / 16 * 16;
+  const int Npad = (Ng + 15) / 16 * 16;
   int nmw = (int)options().rec_mma_warps;
   if (nmw <= 0) nmw = NUM_MMA_WARPS;
   if (nmw > NUM_MMA_WARPS) nmw = NUM_MMA_WARPS;
   if (nmw > Kc / 16) nmw = Kc / 16;
   while (nmw > 1 && 2 * nmw * Npad > 512) --nmw;
   if (2 * nmw * Npad > 512) return pl;
+  const bool w_tmem = options().rec_w_tmem != 0 && 2 * nmw * Npad + Kc / 2 <= 512;
   uint32_t cols = 32;
-  while (cols < (uint32_t)(2 * nmw * Npad)) cols <<= 1;
-  pl.nmw = nmw;
-  pl.tmem_cols = cols;
-  int nstages = 4;
-  while (nstages > 2 && plan_smem(S, Kc, Npad, nstages) > smem_cap) --nstages;
+  while (cols < (uint32_t)(2 * nmw * Npad + (w_tmem ? Kc / 2 : 0))) cols <<= 1;
+  pl.w_tmem = w_tmem ? 1 : 0;
+  // a single batch group runs strictly step after step: one ring stage is enough
+  const int min_stages = G > 1 ? 2 : 1;
+  int nstages = G > 1 ? 4 : 2;
+  while (nstages > min_stages && plan_smem(S, Kc, Npad, nstages) > smem_cap) --nstages;
   if (plan_smem(S, Kc, Npad, nstages) > smem_cap) return pl;
   pl.S = S; pl.Kc = Kc; pl.G = G; pl.Ng = Ng; pl.Npad = Npad; pl.nstages = nstages;
+  pl.nmw = nmw; pl.tmem_cols = cols;
   pl.smem = plan_smem(S, Kc, Npad, nstages);
   pl.ok = true;
   return pl;
+}
+
+// Every CTA waits on every other one, so the whole grid must be resident at once:
+// ask the runtime how many clusters of this shape fit.
+bool plan_is_coresident(const RecPlan& pl, int d) {
+  auto kern = rec_tc_kernel<false>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((d / TILE_M) * pl.S);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = pl.smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = pl.S;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int max_clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return max_clusters * pl.S >= (int)cfg.gridDim.x;
+}
+
+// Largest K split first (most CTAs, smallest resident tile); a split whose clusters do
+// not all fit on the device at once is skipped.  Results are cached per shape.
+RecPlan make_plan(int T, int B, int d) {
+  RecPlan none{};
+  none.ok = false;
+  if (T < 1 || B < 1 || d < 128 || (d % 128) != 0) return none;
+  struct Key { int B, d; long s, g, w, wt; };
+  struct Entry { Key k; RecPlan pl; };
+  static Entry cache[16];
+  static int ncache = 0;
+  const Key key{B, d, options().rec_ksplit, options().rec_groups, options().rec_mma_warps,
+                options().rec_w_tmem};
+  for (int i = 0; i < ncache; ++i) {
+    const Key& c = cache[i].k;
+    if (c.B == key.B && c.d == key.d && c.s == key.s && c.g == key.g && c.w == key.w &&
+        c.wt == key.wt)
+      return cache[i].pl;
+  }
+  RecPlan found = none;
+  const long want_S = options().rec_ksplit;
+  for (int S = MAX_S; S >= 1 && !found.ok; S >>= 1) {
+    if (want_S > 0 && S != want_S) continue;
+    for (int ng_cap = 32; ng_cap >= 16 && !found.ok; ng_cap >>= 1) {
+      RecPlan pl = plan_for(B, d, S, ng_cap);
+      if (pl.ok && plan_is_coresident(pl, d)) found = pl;
+    }
+  }
+  if (ncache < 16) cache[ncache++] = Entry{key, found};
+  return found;
 }
 
 template <bool BWD>
@@ -802,6 +905,9 @@ int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* 
 void fill_plan(const RecPlan& pl, RecTcParams& p) {
   p.S = pl.S; p.Kc = pl.Kc; p.G = pl.G; p.Ng = pl.Ng; p.Npad = pl.Npad; p.nstages = pl.nstages;
   p.nmw = pl.nmw; p.tmem_cols = pl.tmem_cols;
+  p.direct_publish = options().rec_direct_publish != 0 ? 1 : 0;
+  p.w_tmem = pl.w_tmem;
+  p.w_col0 = (uint32_t)(2 * pl.nmw * pl.Npad);
   p.R = p.d / TILE_M;
   p.spin_limit = options().spin_limit;
   p.status = device_status_ptr();
@@ -843,6 +949,7 @@ int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
   p.ready = a.sync;
   p.abort_word = a.sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE;
   p.trace = trace_area(a.sync);
+  p.Wg = (const bf16*)a.W;
   return launch_rec_tc<false>(pl, p, a.W, a.h, stream);
 }
 
@@ -861,6 +968,7 @@ int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream) {
   p.ready = a.sync;
   p.abort_word = a.sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE;
   p.trace = trace_area(a.sync);
+  p.Wg = (const bf16*)a.Wt;
   return launch_rec_tc<true>(pl, p, a.Wt, a.dv, stream);
 }
 
