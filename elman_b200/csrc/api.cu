@@ -538,7 +538,7 @@ int elman_e0_backward(int dtype, int T, int B, int d, const void* W_x, const voi
 
 // ------------------------------- E5 ----------------------------------------
 
-struct E5FwdWs { void* Vx; void* pre; void* Vz; void* gate; float* tmp; int* sync; };
+struct E5FwdWs { void* Vx; void* pre; void* Vz; void* gate; float* tmp; int* sync; void* UP; void* VP; };
 static size_t carve_e5_fwd(int dtype, int T, int B, int d, int r, void* ws, E5FwdWs* o) {
   Carver c(ws);
   size_t es = esize(dtype);
@@ -548,6 +548,13 @@ static size_t carve_e5_fwd(int dtype, int T, int B, int d, int r, void* ws, E5Fw
   o->gate = c.take((size_t)T * B * d * es);
   o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
   o->sync = (int*)c.take(rec_sync_bytes());
+  o->UP = o->VP = nullptr;
+  if (dtype == ELMAN_BF16) {  // zero-padded factors for the tensor-core kernel
+    size_t up = 0, vp = 0;
+    lowrank_tc_pad_bytes(d, r, &up, &vp);
+    o->UP = c.take(up);
+    o->VP = c.take(vp);
+  }
   return c.total();
 }
 
@@ -582,6 +589,15 @@ int elman_e5_forward(int dtype, int training, int T, int B, int d, int r, const 
   ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vx, r, U_x, r, b, w.pre, d, 0, st));
   ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_z, d, nullptr, w.Vz, r, 0, st));
   ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vz, r, U_z, r, nullptr, w.gate, d, 0, st));
+  if (use_tc(dtype) && lowrank_tc_supported(T, B, d, r, 0)) {
+    LowRankTcArgs ta{};
+    ta.T = T; ta.B = B; ta.d = d; ta.r = r; ta.bwd = 0;
+    ta.Urole = U_h; ta.Vrole = V_h;
+    ta.in0 = w.pre; ta.in1 = w.gate;
+    ta.state = h; ta.out0 = training ? v : nullptr; ta.out1 = output;
+    ta.UP = w.UP; ta.VP = w.VP; ta.sync = w.sync;
+    return lowrank_tc(ta, st);
+  }
   LowRankFwdArgs a{T, B, d, r, U_h, V_h, w.pre, w.gate, h, output, training ? v : nullptr, w.tmp,
                    w.sync};
   return lowrank_fwd_generic(dtype, a, st);
@@ -590,6 +606,7 @@ int elman_e5_forward(int dtype, int training, int T, int B, int d, int r, const 
 struct E5BwdWs {
   void* Vz; void* gate; void* Ut; void* Vt; void* dv; void* dg; float* db; float* tmp; int* sync;
   void* Vx; void* Vh; void* dVx; void* dVz; void* dVh;
+  void* UP; void* VP;
 };
 static size_t carve_e5_bwd(int dtype, int T, int B, int d, int r, void* ws, E5BwdWs* o) {
   Carver c(ws);
@@ -599,7 +616,7 @@ static size_t carve_e5_bwd(int dtype, int T, int B, int d, int r, void* ws, E5Bw
   o->gate = c.take(TBd);
   o->Ut = c.take((size_t)d * r * es);
   o->Vt = c.take((size_t)d * r * es);
-  o->dv = c.take(TBd);
+  o->dv = c.take(TBd + (size_t)B * d * es);  // one extra time slot: the zero gradient from the future
   o->dg = c.take(TBd);
   o->db = (float*)c.take((size_t)d * sizeof(float));
   o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
@@ -609,6 +626,13 @@ static size_t carve_e5_bwd(int dtype, int T, int B, int d, int r, void* ws, E5Bw
   o->dVx = c.take(TBr);
   o->dVz = c.take(TBr);
   o->dVh = c.take(TBr);
+  o->UP = o->VP = nullptr;
+  if (dtype == ELMAN_BF16) {
+    size_t up = 0, vp = 0;
+    lowrank_tc_pad_bytes(d, r, &up, &vp);
+    o->UP = c.take(up);
+    o->VP = c.take(vp);
+  }
   return c.total();
 }
 
@@ -649,8 +673,20 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, co
   ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vz, r, U_z, r, nullptr, w.gate, d, 0, st));
   ELMAN_RETURN_IF(transpose2d(dtype, d, r, U_h, w.Ut, st));  // [r,d]
   ELMAN_RETURN_IF(transpose2d(dtype, r, d, V_h, w.Vt, st));  // [d,r]
-  LowRankBwdArgs a{T, B, d, r, w.Ut, w.Vt, h, v, w.gate, d_output, w.dv, w.dg, w.db, w.tmp, w.sync};
-  ELMAN_RETURN_IF(lowrank_bwd_generic(dtype, a, st));
+  if (use_tc(dtype) && lowrank_tc_supported(T, B, d, r, 1)) {
+    // dh_rec = (dv U) V: first product with U^T [r,d], second with V^T [d,r]
+    LowRankTcArgs ta{};
+    ta.T = T; ta.B = B; ta.d = d; ta.r = r; ta.bwd = 1;
+    ta.Urole = w.Vt; ta.Vrole = w.Ut;
+    ta.in0 = w.gate; ta.in1 = d_output; ta.in2 = h; ta.in3 = v;
+    ta.state = w.dv; ta.out0 = w.dg; ta.out1 = nullptr; ta.db = w.db;
+    ta.UP = w.UP; ta.VP = w.VP; ta.sync = w.sync;
+    ELMAN_RETURN_IF(lowrank_tc(ta, st));
+  } else {
+    LowRankBwdArgs a{T, B, d, r, w.Ut, w.Vt, h, v, w.gate, d_output, w.dv, w.dg, w.db, w.tmp,
+                     w.sync};
+    ELMAN_RETURN_IF(lowrank_bwd_generic(dtype, a, st));
+  }
   ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
   // rank-r activations and their gradients, all time steps at once
   ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_x, d, nullptr, w.Vx, r, 0, st));

@@ -60,7 +60,7 @@ int* device_status_ptr();   // device-side alias, or nullptr if unavailable
 
 // kernel ids recorded in the status word
 enum KernelId { KID_REC_SIMT = 1, KID_REC_TC_FWD = 2, KID_REC_TC_BWD = 3, KID_GEMM_TC = 4,
-                KID_LOWRANK_SIMT = 5, KID_WAIT_PROBE = 6 };
+                KID_LOWRANK_SIMT = 5, KID_WAIT_PROBE = 6, KID_LOWRANK_TC = 7 };
 
 // ---------------------------------------------------------------------------
 // device helpers
@@ -191,5 +191,24 @@ int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream);
 int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream);
 // Copies the cycle stamps of the last traced launch (option rec_trace) to the host.
 int rec_tc_copy_trace(long long* dst, int max_entries);
+
+// Low-rank (E5) recurrence, bf16, tcgen05: one cluster of d/128 CTAs, the rank-r
+// intermediate exchanged through distributed shared memory only.
+//   forward : in0 = pre, in1 = gate, state = h [T+1,B,d] (h[0] filled), out0 = v (or null),
+//             out1 = y
+//   backward: in0 = gate, in1 = dy, in2 = h [T+1,B,d], in3 = v, state = dv [T+1,B,d],
+//             out0 = dgate, db = fp32 [d]; Urole = V^T [d,r], Vrole = U^T [r,d]
+struct LowRankTcArgs {
+  int T, B, d, r, bwd;
+  const void* Urole;   // [d, r]  second product
+  const void* Vrole;   // [r, d]  first product
+  const void* in0; const void* in1; const void* in2; const void* in3;
+  void* state; void* out0; void* out1; float* db;
+  void* UP; void* VP;  // scratch for the zero-padded factors (lowrank_tc_pad_bytes)
+  int* sync;           // 256 bytes
+};
+bool lowrank_tc_supported(int T, int B, int d, int r, int bwd);
+void lowrank_tc_pad_bytes(int d, int r, size_t* up_bytes, size_t* vp_bytes);
+int lowrank_tc(const LowRankTcArgs& a, cudaStream_t stream);
 
 }  // namespace elman

@@ -69,3 +69,29 @@ def test_e5_bf16_matches_oracle(T, B, d, r):
     inp = orc.make_e5_inputs(T, B, d, r, seed=700 + d)
     got, ref = run_e5(inp, torch.bfloat16)
     assert_close(errors(got, oracle_e5(ref)), TOL[torch.bfloat16], f"E5 bf16 {T},{B},{d},{r}")
+
+
+@pytest.mark.parametrize("T,B,d,r", [(16, 32, 256, 30), (20, 16, 512, 100), (10, 32, 1024, 200),
+                                     (8, 32, 1536, 270), (9, 8, 256, 64)])
+def test_e5_bf16_tensor_core_cluster_kernel_matches_oracle(T, B, d, r):
+    """Shapes the single-cluster tcgen05 kernel takes (d/128 CTAs, rank chunks <= CTAs)."""
+    from elman_b200 import _lib
+    inp = orc.make_e5_inputs(T, B, d, r, seed=900 + d + r)
+    before = _lib.tc_launch_count()
+    got, ref = run_e5(inp, torch.bfloat16)
+    # forward and backward recurrences plus tensor-core GEMMs where K allows it
+    assert _lib.tc_launch_count() >= before + 2, "the low-rank tensor-core kernel was not used"
+    assert _lib.device_status()[0] == 0
+    assert_close(errors(got, oracle_e5(ref)), TOL[torch.bfloat16], f"E5 tcgen05 {T},{B},{d},{r}")
+    with option("force_generic", 1):
+        gen, _ = run_e5(inp, torch.bfloat16)
+    assert_close({k: orc.rel_err(got[k].float().cpu(), gen[k].float().cpu()) for k in got
+                  if got[k].numel()}, TOL[torch.bfloat16], "tcgen05 vs CUDA-core path")
+
+
+def test_e5_bf16_results_are_bit_reproducible():
+    inp = orc.make_e5_inputs(12, 32, 512, 96, seed=5)
+    a, _ = run_e5(inp, torch.bfloat16)
+    b, _ = run_e5(inp, torch.bfloat16)
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
