@@ -538,22 +538,36 @@ int elman_e0_backward(int dtype, int T, int B, int d, const void* W_x, const voi
 
 // ------------------------------- E5 ----------------------------------------
 
-struct E5FwdWs { void* Vx; void* pre; void* Vz; void* gate; float* tmp; int* sync; void* UP; void* VP; };
+// In the bf16 tensor-core path every factor is used zero-padded to rp = rank rounded
+// up to 64: the time-parallel GEMMs then meet the TMA alignment rules for any rank
+// (e.g. 270) and the extra columns contribute exact zeros.
+static inline int e5_rank_alloc(int dtype, int r) { return dtype == ELMAN_BF16 ? (r + 63) / 64 * 64 : r; }
+static inline int e5_rank_run(int dtype, int r) { return use_tc(dtype) ? (r + 63) / 64 * 64 : r; }
+
+struct E5FwdWs {
+  void* Vx; void* pre; void* Vz; void* gate; float* tmp; int* sync; void* UP; void* VP;
+  void* UxP; void* VxP; void* UzP; void* VzP;
+};
 static size_t carve_e5_fwd(int dtype, int T, int B, int d, int r, void* ws, E5FwdWs* o) {
   Carver c(ws);
   size_t es = esize(dtype);
-  o->Vx = c.take((size_t)T * B * r * es);
+  const int ra = e5_rank_alloc(dtype, r);
+  o->Vx = c.take((size_t)T * B * ra * es);
   o->pre = c.take((size_t)T * B * d * es);
-  o->Vz = c.take((size_t)T * B * r * es);
+  o->Vz = c.take((size_t)T * B * ra * es);
   o->gate = c.take((size_t)T * B * d * es);
   o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
   o->sync = (int*)c.take(rec_sync_bytes());
-  o->UP = o->VP = nullptr;
-  if (dtype == ELMAN_BF16) {  // zero-padded factors for the tensor-core kernel
+  o->UP = o->VP = o->UxP = o->VxP = o->UzP = o->VzP = nullptr;
+  if (dtype == ELMAN_BF16) {  // zero-padded factors
     size_t up = 0, vp = 0;
     lowrank_tc_pad_bytes(d, r, &up, &vp);
     o->UP = c.take(up);
     o->VP = c.take(vp);
+    o->UxP = c.take((size_t)d * ra * es);
+    o->VxP = c.take((size_t)d * ra * es);
+    o->UzP = c.take((size_t)d * ra * es);
+    o->VzP = c.take((size_t)d * ra * es);
   }
   return c.total();
 }
@@ -584,11 +598,20 @@ int elman_e5_forward(int dtype, int training, int T, int B, int d, int r, const 
   if (workspace_bytes < need)
     return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
   const int TB = T * B;
+  const int rp = e5_rank_run(dtype, r);
+  const void *Ux = U_x, *Vx = V_x, *Uz = U_z, *Vz = V_z;
+  if (rp != r) {
+    ELMAN_RETURN_IF(resize2d(dtype, U_x, d, r, w.UxP, d, rp, st));
+    ELMAN_RETURN_IF(resize2d(dtype, V_x, r, d, w.VxP, rp, d, st));
+    ELMAN_RETURN_IF(resize2d(dtype, U_z, d, r, w.UzP, d, rp, st));
+    ELMAN_RETURN_IF(resize2d(dtype, V_z, r, d, w.VzP, rp, d, st));
+    Ux = w.UxP; Vx = w.VxP; Uz = w.UzP; Vz = w.VzP;
+  }
   // pre = (x V_x^T) U_x^T + b ; gate = (x V_z^T) U_z^T
-  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_x, d, nullptr, w.Vx, r, 0, st));
-  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vx, r, U_x, r, b, w.pre, d, 0, st));
-  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_z, d, nullptr, w.Vz, r, 0, st));
-  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vz, r, U_z, r, nullptr, w.gate, d, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, rp, d, x, d, Vx, d, nullptr, w.Vx, rp, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, rp, w.Vx, rp, Ux, rp, b, w.pre, d, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, rp, d, x, d, Vz, d, nullptr, w.Vz, rp, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, rp, w.Vz, rp, Uz, rp, nullptr, w.gate, d, 0, st));
   if (use_tc(dtype) && lowrank_tc_supported(T, B, d, r, 0)) {
     LowRankTcArgs ta{};
     ta.T = T; ta.B = B; ta.d = d; ta.r = r; ta.bwd = 0;
@@ -607,11 +630,14 @@ struct E5BwdWs {
   void* Vz; void* gate; void* Ut; void* Vt; void* dv; void* dg; float* db; float* tmp; int* sync;
   void* Vx; void* Vh; void* dVx; void* dVz; void* dVh;
   void* UP; void* VP;
+  void* P[6];    // zero-padded U_h, V_h, U_x, V_x, U_z, V_z
+  void* dUP; void* dVP;  // padded weight-gradient scratch
 };
 static size_t carve_e5_bwd(int dtype, int T, int B, int d, int r, void* ws, E5BwdWs* o) {
   Carver c(ws);
   size_t es = esize(dtype);
-  size_t TBr = (size_t)T * B * r * es, TBd = (size_t)T * B * d * es;
+  const int ra = e5_rank_alloc(dtype, r);
+  size_t TBr = (size_t)T * B * ra * es, TBd = (size_t)T * B * d * es;
   o->Vz = c.take(TBr);
   o->gate = c.take(TBd);
   o->Ut = c.take((size_t)d * r * es);
@@ -626,12 +652,16 @@ static size_t carve_e5_bwd(int dtype, int T, int B, int d, int r, void* ws, E5Bw
   o->dVx = c.take(TBr);
   o->dVz = c.take(TBr);
   o->dVh = c.take(TBr);
-  o->UP = o->VP = nullptr;
+  o->UP = o->VP = o->dUP = o->dVP = nullptr;
+  for (int i = 0; i < 6; ++i) o->P[i] = nullptr;
   if (dtype == ELMAN_BF16) {
     size_t up = 0, vp = 0;
     lowrank_tc_pad_bytes(d, r, &up, &vp);
     o->UP = c.take(up);
     o->VP = c.take(vp);
+    for (int i = 0; i < 6; ++i) o->P[i] = c.take((size_t)d * ra * es);
+    o->dUP = c.take((size_t)d * ra * es);
+    o->dVP = c.take((size_t)d * ra * es);
   }
   return c.total();
 }
@@ -668,9 +698,21 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, co
   if (workspace_bytes < need)
     return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
   const int TB = T * B;
+  const int rp = e5_rank_run(dtype, r);
+  const bool padded = rp != r;
+  // factors as the time-parallel GEMMs see them: U [d, rp], V [rp, d]
+  const void* F[6] = {U_h, V_h, U_x, V_x, U_z, V_z};
+  if (padded) {
+    for (int i = 0; i < 6; ++i) {
+      if (i % 2 == 0) ELMAN_RETURN_IF(resize2d(dtype, F[i], d, r, w.P[i], d, rp, st));
+      else ELMAN_RETURN_IF(resize2d(dtype, F[i], r, d, w.P[i], rp, d, st));
+      F[i] = w.P[i];
+    }
+  }
+  const void *Uh = F[0], *Vh = F[1], *Ux = F[2], *Vx = F[3], *Uz = F[4], *Vz = F[5];
   // recompute the gate pre-activation (the reference does the same per step)
-  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_z, d, nullptr, w.Vz, r, 0, st));
-  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, r, w.Vz, r, U_z, r, nullptr, w.gate, d, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, rp, d, x, d, Vz, d, nullptr, w.Vz, rp, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, rp, w.Vz, rp, Uz, rp, nullptr, w.gate, d, 0, st));
   ELMAN_RETURN_IF(transpose2d(dtype, d, r, U_h, w.Ut, st));  // [r,d]
   ELMAN_RETURN_IF(transpose2d(dtype, r, d, V_h, w.Vt, st));  // [d,r]
   if (use_tc(dtype) && lowrank_tc_supported(T, B, d, r, 1)) {
@@ -689,21 +731,29 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, co
   }
   ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
   // rank-r activations and their gradients, all time steps at once
-  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, x, d, V_x, d, nullptr, w.Vx, r, 0, st));
-  ELMAN_RETURN_IF(proj_nt(dtype, TB, r, d, h, d, V_h, d, nullptr, w.Vh, r, 0, st));
-  ELMAN_RETURN_IF(gemm_nn(dtype, TB, r, d, w.dv, d, U_x, r, nullptr, w.dVx, r, 0, st));
-  ELMAN_RETURN_IF(gemm_nn(dtype, TB, r, d, w.dg, d, U_z, r, nullptr, w.dVz, r, 0, st));
-  ELMAN_RETURN_IF(gemm_nn(dtype, TB, r, d, w.dv, d, U_h, r, nullptr, w.dVh, r, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, rp, d, x, d, Vx, d, nullptr, w.Vx, rp, 0, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, rp, d, h, d, Vh, d, nullptr, w.Vh, rp, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, rp, d, w.dv, d, Ux, rp, nullptr, w.dVx, rp, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, rp, d, w.dg, d, Uz, rp, nullptr, w.dVz, rp, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, rp, d, w.dv, d, Uh, rp, nullptr, w.dVh, rp, 0, st));
   // dx = dVx V_x + dVz V_z
-  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, r, w.dVx, r, V_x, d, nullptr, dx, d, 0, st));
-  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, r, w.dVz, r, V_z, d, nullptr, dx, d, 1, st));
-  // weight gradients: sums over all T*B rows
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, r, TB, w.dv, w.Vh, nullptr, false, nullptr, false, dU_h, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, r, d, TB, w.dVh, h, nullptr, false, nullptr, false, dV_h, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, r, TB, w.dv, w.Vx, nullptr, false, nullptr, false, dU_x, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, r, d, TB, w.dVx, x, nullptr, false, nullptr, false, dV_x, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, r, TB, w.dg, w.Vz, nullptr, false, nullptr, false, dU_z, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, r, d, TB, w.dVz, x, nullptr, false, nullptr, false, dV_z, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, rp, w.dVx, rp, Vx, d, nullptr, dx, d, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, rp, w.dVz, rp, Vz, d, nullptr, dx, d, 1, st));
+  // weight gradients: sums over all T*B rows (into padded scratch when the rank is padded)
+  struct Job { const void* A; const void* Bm; void* dU_or_dV; bool is_u; };
+  const Job jobs[6] = {{w.dv, w.Vh, dU_h, true},  {w.dVh, h, dV_h, false}, {w.dv, w.Vx, dU_x, true},
+                       {w.dVx, x, dV_x, false},   {w.dg, w.Vz, dU_z, true}, {w.dVz, x, dV_z, false}};
+  for (const Job& jb : jobs) {
+    if (jb.is_u) {  // dU [d, r] = A^T [d, TB] * Bm [TB, rp]
+      void* out = padded ? w.dUP : jb.dU_or_dV;
+      ELMAN_RETURN_IF(gemm_tn(dtype, d, rp, TB, jb.A, jb.Bm, nullptr, false, nullptr, false, out, st));
+      if (padded) ELMAN_RETURN_IF(resize2d(dtype, out, d, rp, jb.dU_or_dV, d, r, st));
+    } else {        // dV [r, d] = A^T [rp, TB] * Bm [TB, d]
+      void* out = padded ? w.dVP : jb.dU_or_dV;
+      ELMAN_RETURN_IF(gemm_tn(dtype, rp, d, TB, jb.A, jb.Bm, nullptr, false, nullptr, false, out, st));
+      if (padded) ELMAN_RETURN_IF(copy_rows(dtype, out, jb.dU_or_dV, (long)r * d, st));
+    }
+  }
   return ELMAN_OK;
 }
 

@@ -132,6 +132,9 @@ int column_sum(int dtype, long M, int N, const void* in, void* out, float* scrat
 size_t column_sum_scratch_bytes(int N);
 int copy_rows(int dtype, const void* src, void* dst, long n, cudaStream_t stream);
 int float_to_dtype(int dtype, const float* src, void* dst, long n, cudaStream_t stream);
+// dst[rows_dst, cols_dst] = src[rows, cols], cropped or zero-padded (dense row-major both).
+int resize2d(int dtype, const void* src, int rows, int cols, void* dst, int rows_dst, int cols_dst,
+             cudaStream_t stream);
 
 // Dense recurrence, CUDA-core persistent kernel.
 //   forward : h[t+1] = tanh(pre[t] + h[t] W^T);  y[t] = h[t+1] * silu(g[t])

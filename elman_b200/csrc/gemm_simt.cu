@@ -193,6 +193,35 @@ int copy_rows(int dtype, const void* src, void* dst, long n, cudaStream_t stream
   return ELMAN_OK;
 }
 
+namespace {
+// dst[rows_dst, cols_dst] = src[rows, cols] cropped or zero-padded to the new extents
+template <typename T>
+__global__ void resize2d_kernel(const T* __restrict__ src, int rows, int cols, T* __restrict__ dst,
+                                int rows_dst, int cols_dst) {
+  const long n = (long)rows_dst * cols_dst;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / cols_dst), c = (int)(i - (long)r * cols_dst);
+    dst[i] = (r < rows && c < cols) ? src[(long)r * cols + c] : from_f<T>(0.f);
+  }
+}
+}  // namespace
+
+int resize2d(int dtype, const void* src, int rows, int cols, void* dst, int rows_dst, int cols_dst,
+             cudaStream_t stream) {
+  const long n = (long)rows_dst * cols_dst;
+  if (n <= 0) return ELMAN_OK;
+  if (dtype == ELMAN_F32)
+    resize2d_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)src, rows, cols,
+                                                                 (float*)dst, rows_dst, cols_dst);
+  else
+    resize2d_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)src, rows, cols,
+                                                                (bf16*)dst, rows_dst, cols_dst);
+  count_launch(false);
+  ELMAN_CUDA_CHECK(cudaGetLastError());
+  return ELMAN_OK;
+}
+
 int float_to_dtype(int dtype, const float* src, void* dst, long n, cudaStream_t stream) {
   if (n <= 0) return ELMAN_OK;
   if (dtype == ELMAN_F32)
