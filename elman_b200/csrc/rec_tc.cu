@@ -102,6 +102,11 @@ __device__ __forceinline__ void st_async_v4(uint32_t remote_addr, uint32_t a, ui
       ::"r"(remote_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(remote_bar)
       : "memory");
 }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -268,6 +273,8 @@ __device__ __forceinline__ void stg_u32(bf16* p, uint32_t v) {
 template <bool BWD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmState,
+              const __grid_constant__ CUtensorMap tmI0, const __grid_constant__ CUtensorMap tmI1,
+              const __grid_constant__ CUtensorMap tmI2, const __grid_constant__ CUtensorMap tmI3,
               RecTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t w_bar;
@@ -278,6 +285,8 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   __shared__ __align__(8) uint64_t red_full_bar[2];   // peers' partials landed (owner side)
   __shared__ __align__(8) uint64_t red_empty_bar[2];  // owners consumed my partials (source side)
   __shared__ __align__(8) uint64_t stored_bar[2];     // epilogue warps stored the new state
+  __shared__ __align__(8) uint64_t in_full[2];        // epilogue inputs of a step landed (TMA)
+  __shared__ __align__(8) uint64_t in_empty[2];       // ... and were consumed
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ float db_part[2][NUM_EPI_THREADS];
@@ -301,6 +310,11 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   float* sStage = (float*)(sState + p.nstages * state_stage_bytes);
   const int stg_src_floats = Npad * rows_own;
   const int stg_buf_floats = S * stg_src_floats;
+  // epilogue inputs of my feature chunk for one (step, batch group), double buffered:
+  // [2][NIN arrays][Npad batch rows][rows_own features] bf16, fetched by TMA one step ahead
+  constexpr int NIN = BWD ? 4 : 2;
+  uint8_t* sIn = (uint8_t*)(sStage + 2 * stg_buf_floats);
+  const int in_tile_bytes = Npad * rows_own * 2;
   const uint32_t tmem_cols = p.tmem_cols;
 
   Waiter waiter{p.spin_limit, &abort_flag, p.abort_word};
@@ -318,6 +332,8 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       ptx::mbar_init(&red_full_bar[a], 1);  // the owner's expect_tx arrive; data credits bytes
       ptx::mbar_init(&red_empty_bar[a], S);
       ptx::mbar_init(&stored_bar[a], NUM_EPI_THREADS / 32);
+      ptx::mbar_init(&in_full[a], 1);
+      ptx::mbar_init(&in_empty[a], NUM_EPI_THREADS / 32);
     }
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmW);
@@ -376,7 +392,22 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const int step = q / G, grp = q - step * G;
         const int s = q % p.nstages;
         const uint32_t ph = (uint32_t)(q / p.nstages) & 1u;
-        bool ok = waiter.wait(&empty_bar[s], ph ^ 1u);
+        // the epilogue's inputs for this (step, group) do not depend on the recurrence:
+        // fetch them now, a whole dependency chain before they are needed
+        bool ok = waiter.wait(&in_empty[q & 1], ((uint32_t)(q >> 1) & 1u) ^ 1u);
+        if (ok) {
+          const int t = BWD ? (p.T - 1 - step) : step;
+          const int f0 = i * TILE_M + (int)j * rows_own;
+          uint8_t* dst = sIn + (q & 1) * NIN * in_tile_bytes;
+          ptx::mbar_arrive_expect_tx(&in_full[q & 1], (uint32_t)(NIN * in_tile_bytes));
+          tma_load_3d(dst, &tmI0, f0, grp * Ng, t, &in_full[q & 1]);
+          tma_load_3d(dst + in_tile_bytes, &tmI1, f0, grp * Ng, t, &in_full[q & 1]);
+          if (BWD) {
+            tma_load_3d(dst + 2 * in_tile_bytes, &tmI2, f0, grp * Ng, t + 1, &in_full[q & 1]);
+            tma_load_3d(dst + 3 * in_tile_bytes, &tmI3, f0, grp * Ng, t, &in_full[q & 1]);
+          }
+        }
+        ok = ok && waiter.wait(&empty_bar[s], ph ^ 1u);
         if (ok && step > 0)
           ok = waiter.wait_counter(p.ready + (grp * MAX_S + (int)j) * COUNTER_STRIDE,
                                    step * p.R * (p.direct_publish ? NUM_EPI_THREADS / 32 : 1));
@@ -462,7 +493,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     float db0 = 0.f, db1 = 0.f;
 
     // raw prefetched inputs of the next step, and the values derived from them
-    uint32_t r0[MAX_QUADS][4], r1[MAX_QUADS][4], r2[MAX_QUADS][4], r3[MAX_QUADS][4];
+    const uint32_t in_a = ptx::smem_u32(sIn);
     float2 e0[MAX_QUADS][4], e1[MAX_QUADS][4];
     uint32_t late0[MAX_QUADS][4], late1[MAX_QUADS][4];  // outputs nobody waits for
     // element offsets inside one (time step, batch group) block; -1 marks padding
@@ -479,43 +510,24 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       const int t = BWD ? (p.T - 1 - step) : step;
       return ((long)t * p.B + (long)grp * Ng) * p.d;
     };
-    auto prefetch = [&](int q) {
-      const long base = block_base(q);
-#pragma unroll
-      for (int e = 0; e < MAX_QUADS; ++e) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (eoff[e][u] >= 0) {
-            const long idx = base + eoff[e][u];
-            if (!BWD) {
-              r0[e][u] = ldg_u32(p.pre + idx);
-              r1[e][u] = ldg_u32(p.g + idx);
-            } else {
-              r0[e][u] = ldg_u32(p.g + idx);
-              r1[e][u] = ldg_u32(p.dy + idx);
-              r2[e][u] = ldg_u32(p.h_in + idx + BD);
-              r3[e][u] = ldg_u32(p.v_in + idx);
-            }
-          }
-        }
-      }
-    };
     // everything that does not depend on the recurrent term
-    auto premath = [&]() {
+    auto premath = [&](int q) {
+      const uint32_t tile0 = in_a + (uint32_t)((q & 1) * NIN * in_tile_bytes + 4 * fp);
 #pragma unroll
       for (int e = 0; e < MAX_QUADS; ++e) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           if (eoff[e][u] >= 0) {
+            const uint32_t ia = tile0 + (uint32_t)((4 * (qd0 + e * nbq) + u) * rows_own * 2);
             if (!BWD) {
-              e0[e][u] = bf16x2_to_f2(r0[e][u]);
-              const float2 gz = bf16x2_to_f2(r1[e][u]);
+              e0[e][u] = bf16x2_to_f2(lds_u32(ia));
+              const float2 gz = bf16x2_to_f2(lds_u32(ia + in_tile_bytes));
               e1[e][u] = make_float2(gz.x * sigmoid_fast(gz.x), gz.y * sigmoid_fast(gz.y));
             } else {
-              const float2 gz = bf16x2_to_f2(r0[e][u]);
-              const float2 dy = bf16x2_to_f2(r1[e][u]);
-              const float2 hv = bf16x2_to_f2(r2[e][u]);
-              const float2 vv = bf16x2_to_f2(r3[e][u]);
+              const float2 gz = bf16x2_to_f2(lds_u32(ia));
+              const float2 dy = bf16x2_to_f2(lds_u32(ia + in_tile_bytes));
+              const float2 hv = bf16x2_to_f2(lds_u32(ia + 2 * in_tile_bytes));
+              const float2 vv = bf16x2_to_f2(lds_u32(ia + 3 * in_tile_bytes));
               const float sx = sigmoid_fast(gz.x), sy = sigmoid_fast(gz.y);
               late0[e][u] = f2_to_bf16x2(dy.x * hv.x * sx * (1.f + gz.x * (1.f - sx)),
                                          dy.y * hv.y * sy * (1.f + gz.y * (1.f - sy)));
@@ -526,7 +538,6 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
       }
     };
-    if (total_q > 0) prefetch(0);
 
     for (int q = 0; q < total_q; ++q) {
       const int step = q / G;
@@ -536,13 +547,19 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       if (et == 0)  // arm this step's reduction barrier with the bytes all S sources will send me
         ptx::mbar_arrive_expect_tx(&red_full_bar[a], (uint32_t)(S * rows_own * nquads * 16));
       // everything that does not need the recurrent term, while the MMAs are in flight
-      premath();
+      bool in_ok = waiter.wait(&in_full[q & 1], (uint32_t)(q >> 1) & 1u);
+      in_ok = __all_sync(0xffffffffu, in_ok);
+      if (in_ok) {
+        premath(q);
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&in_empty[q & 1]);  // the buffer may be refilled
+      }
       if (et == 0) stamp(p.trace, q, 12);  // step-local math done
       // A failed (timed-out / aborted) wait never skips the named barrier below:
       // the thread marks the CTA aborted, skips the data movement, and everybody
       // leaves the loop together after the barrier.
       // ---- drain my accumulator row and scatter it to the owning peer ----
-      bool good = waiter.wait(&acc_full_bar[a], aph) &&
+      bool good = in_ok && waiter.wait(&acc_full_bar[a], aph) &&
                   waiter.wait_cluster(&red_empty_bar[a], aph ^ 1u);
       good = __all_sync(0xffffffffu, good);
       if (et == 0) stamp(p.trace, q, 4);  // accumulator complete
@@ -672,7 +689,6 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
       }
       if (et == 0) stamp(p.trace, q, 15);  // late outputs stored
-      if (q + 1 < total_q) prefetch(q + 1);
       if (et == 0) stamp(p.trace, q, 10);  // next step's inputs requested
     }
     if (BWD) { db_part[0][et] = db0; db_part[1][et] = db1; }
@@ -749,6 +765,33 @@ int make_state_tmap(CUtensorMap* out, const void* base, int slots, int B, int d,
   return ELMAN_OK;
 }
 
+// [slots][B][d] bf16 seen as (d, B, slots), no swizzle: box = box_cols features x box_rows
+// batch rows x 1 time slot.  Used for the epilogue's input tiles.
+int make_io_tmap(CUtensorMap* out, const void* base, int slots, int B, int d, int box_cols,
+                 int box_rows) {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) !=
+            cudaSuccess || qres != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return set_error(ELMAN_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    }
+    fn = (EncodeTiledFn)ptr;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)d, (cuuint64_t)B, (cuuint64_t)slots};
+  cuuint64_t strides[2] = {(cuuint64_t)d * 2, (cuuint64_t)B * d * 2};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return set_error(ELMAN_ERR_CUDA, "cuTensorMapEncodeTiled (epilogue inputs) failed (%d)", (int)rc);
+  return ELMAN_OK;
+}
+
 struct RecPlan {
   int S, Kc, G, Ng, Npad, nstages, nmw, w_tmem;
   uint32_t tmem_cols;
@@ -760,8 +803,8 @@ size_t plan_smem(int S, int Kc, int Npad, int nstages) {
   size_t w = (size_t)TILE_M * Kc * 2;
   size_t st = (size_t)nstages * Npad * Kc * 2;
   size_t stg = (size_t)2 * TILE_M * Npad * 4;
-  (void)S;
-  return w + st + stg + 1024 + 64;
+  size_t in = (size_t)2 * 4 * Npad * (TILE_M / S) * 2;  // epilogue input tiles (backward: 4 arrays)
+  return w + st + stg + in + 1024 + 64;
 }
 
 // Full plan for one K split S and one cap on the batch-group size, or ok == false.
@@ -874,9 +917,19 @@ template <bool BWD>
 int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* state,
                   cudaStream_t stream) {
   auto kern = rec_tc_kernel<BWD>;
-  CUtensorMap tmW, tmState;
+  CUtensorMap tmW, tmState, tmI[4];
   ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmW, W, (uint64_t)p.d, (uint64_t)p.d, (uint64_t)p.d, TILE_M));
   ELMAN_RETURN_IF(make_state_tmap(&tmState, state, p.T + 1, p.B, p.d, pl.Npad, pl.Kc / 64));
+  {
+    // forward: pre, gate;  backward: gate, dy, h (T+1 slots), v
+    const void* ins[4] = {BWD ? (const void*)p.g : (const void*)p.pre,
+                          BWD ? (const void*)p.dy : (const void*)p.g,
+                          BWD ? (const void*)p.h_in : (const void*)p.pre,
+                          BWD ? (const void*)p.v_in : (const void*)p.g};
+    const int slots[4] = {p.T, p.T, BWD ? p.T + 1 : p.T, p.T};
+    for (int k = 0; k < 4; ++k)
+      ELMAN_RETURN_IF(make_io_tmap(&tmI[k], ins[k], slots[k], p.B, p.d, TILE_M / pl.S, pl.Npad));
+  }
   ELMAN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)pl.smem));
   cudaLaunchConfig_t cfg{};
@@ -897,7 +950,7 @@ int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* 
   if (max_clusters * pl.S < (int)cfg.gridDim.x)
     return set_error(ELMAN_ERR_UNSUPPORTED, "recurrence grid of %d CTAs is not co-resident (%d clusters of %d fit)",
                      (int)cfg.gridDim.x, max_clusters, pl.S);
-  ELMAN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmW, tmState, p));
+  ELMAN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmW, tmState, tmI[0], tmI[1], tmI[2], tmI[3], p));
   count_launch(true);
   return ELMAN_OK;
 }
@@ -905,7 +958,7 @@ int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* 
 void fill_plan(const RecPlan& pl, RecTcParams& p) {
   p.S = pl.S; p.Kc = pl.Kc; p.G = pl.G; p.Ng = pl.Ng; p.Npad = pl.Npad; p.nstages = pl.nstages;
   p.nmw = pl.nmw; p.tmem_cols = pl.tmem_cols;
-  p.direct_publish = options().rec_direct_publish != 0 ? 1 : 0;
+  p.direct_publish = 0;  // set per direction by the callers
   p.w_tmem = pl.w_tmem;
   p.w_col0 = (uint32_t)(2 * pl.nmw * pl.Npad);
   p.R = p.d / TILE_M;
@@ -950,6 +1003,9 @@ int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
   p.abort_word = a.sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE;
   p.trace = trace_area(a.sync);
   p.Wg = (const bf16*)a.W;
+  // option rec_direct_publish: 0 = auto (measured best: forward direct, backward through the
+  // publisher warp), 1 = direct in both, 2 = publisher warp in both
+  p.direct_publish = options().rec_direct_publish == 2 ? 0 : 1;
   return launch_rec_tc<false>(pl, p, a.W, a.h, stream);
 }
 
@@ -969,6 +1025,7 @@ int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream) {
   p.abort_word = a.sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE;
   p.trace = trace_area(a.sync);
   p.Wg = (const bf16*)a.Wt;
+  p.direct_publish = options().rec_direct_publish == 1 ? 1 : 0;
   return launch_rec_tc<true>(pl, p, a.Wt, a.dv, stream);
 }
 

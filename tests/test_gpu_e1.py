@@ -164,3 +164,42 @@ def test_empty_sequence_and_empty_batch():
     x0 = torch.zeros(3, 0, 8, device="cuda")
     h, out, v = H.mamba_gated_elman_forward(True, x0, x0, torch.zeros(0, 8, device="cuda"), W, W, b)
     assert out.shape == (3, 0, 8)
+
+
+def test_wide_large_batch_forward_shape_of_config4():
+    """configs[4] is forward-only bf16 d=2048, B=256, T=2048; same d and B here with a short T
+    (the recurrence is the same program for any T): tensor-core path with 16 pipelined batch
+    groups, against the CPU oracle on a prefix and against the CUDA-core path."""
+    T, B, d = 24, 256, 2048
+    inp = orc.make_e1_inputs(T, B, d, seed=1238)
+    before = _lib.tc_launch_count()
+    got, ref = run_e1(inp, torch.bfloat16, training=False)
+    assert _lib.tc_launch_count() >= before + 2
+    assert _lib.device_status()[0] == 0
+    Tp = 6
+    pref = {k: (v[:Tp].contiguous() if v.dim() == 3 else v) for k, v in ref.items()}
+    o = orc.e1_forward(pref["x"], pref["z"], pref["h0"], pref["W_x"], pref["W_h"], pref["b"])
+    assert orc.rel_err(got["output"][:Tp].float().cpu(), o["output"]) < TOL[torch.bfloat16]
+    with option("force_generic", 1):
+        gen, _ = run_e1(inp, torch.bfloat16, training=False)
+    assert orc.rel_err(got["output"].float().cpu(), gen["output"].float().cpu()) < TOL[torch.bfloat16]
+    assert orc.rel_err(got["h"].float().cpu(), gen["h"].float().cpu()) < TOL[torch.bfloat16]
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_both_publication_modes_give_identical_results(mode):
+    inp = orc.make_e1_inputs(20, 32, 512, seed=31)
+    a, _ = run_e1(inp, torch.bfloat16)
+    with option("rec_direct_publish", mode):
+        b, _ = run_e1(inp, torch.bfloat16)
+    for k in FWD_BWD_KEYS:
+        assert torch.equal(a[k], b[k]), k
+
+
+def test_weights_in_tensor_memory_variant_is_bit_identical():
+    inp = orc.make_e1_inputs(20, 32, 512, seed=32)
+    a, _ = run_e1(inp, torch.bfloat16)
+    with option("rec_w_tmem", 1):
+        b, _ = run_e1(inp, torch.bfloat16)
+    for k in FWD_BWD_KEYS:
+        assert torch.equal(a[k], b[k]), k
