@@ -39,7 +39,7 @@ T, B, D = 512, 32, 1280
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes per launch of the dominant kernel from the committed ncu capture
 # (profiles/), or None while no capture of the current kernel exists.
-NCU_TRAFFIC_BYTES = {"rec_tc_kernel<fwd>": 169.9e6, "rec_tc_kernel<bwd>": 231.4e6}  # profiles/rec_tc_kernel_e1_c1.md
+NCU_TRAFFIC_BYTES = {"rec_tc_kernel<fwd>": 170.6e6, "rec_tc_kernel<bwd>": 232.3e6}  # profiles/rec_tc_kernel_e1_c1.md
 
 
 def parse_args():
@@ -50,8 +50,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_cuda"],
                     help="ours | reference (the reference's CPU path) | reference_cuda (the "
                          "reference's own CUDA kernels rebuilt for sm_100, if oracle/_ref exists)")
-    ap.add_argument("--workload", default="cell", choices=["cell", "lm"],
-                    help="cell = configs[1] (the headline line); lm = configs[2] training step")
+    ap.add_argument("--workload", default="cell", choices=["cell", "lm", "e5"],
+                    help="cell = configs[1] (the headline line); lm = configs[2] training step; "
+                         "e5 = configs[3] low-rank cell")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=128,
                     help="time steps of the workload the CPU baseline runs")
@@ -230,6 +231,66 @@ class _RefCudaBackend:
         return list(r[:5])
 
 
+def run_e5(args, rank, world, local_rank):
+    """configs[3]: E5 low-rank cell forward + backward, bf16, d=1536, rank 270, B=32, T=512.
+    U,V ~ N(0, 1/sqrt(d r)) with U_h V_h rescaled to spectral radius 0.9, x ~ N(0,1).
+    `--impl reference_cuda` runs the reference's fused E5 kernels on the same inputs."""
+    from elman_b200 import _lib
+    from elman_b200 import hasty_pytorch_lib as H
+    Td, Bd, d, r = 512, 32, 1536, 270
+    torch.cuda.set_device(local_rank)
+    g = torch.Generator().manual_seed(1237 + rank)
+    s = (d * r) ** -0.25
+    mats = {}
+    for nm in ("h", "x", "z"):
+        mats["U_" + nm] = torch.randn(d, r, generator=g) * s
+        mats["V_" + nm] = torch.randn(r, d, generator=g) * s
+    rho = float(torch.linalg.eigvals((mats["V_h"] @ mats["U_h"]).double()).abs().max())
+    mats["U_h"] *= math.sqrt(0.9 / rho)
+    mats["V_h"] *= math.sqrt(0.9 / rho)
+    dev = {k: v.to(torch.bfloat16).cuda().contiguous() for k, v in mats.items()}
+    x = torch.randn(Td, Bd, d, generator=g).to(torch.bfloat16).cuda()
+    dy = torch.randn(Td, Bd, d, generator=g).to(torch.bfloat16).cuda()
+    h0 = torch.zeros(Bd, d, dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros(d, dtype=torch.bfloat16, device="cuda")
+    w = [dev[k] for k in ("U_h", "V_h", "U_x", "V_x", "U_z", "V_z")]
+    if args.impl == "reference_cuda":
+        from oracle import ref_cuda
+        if not ref_cuda.available():
+            if rank == 0:
+                print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref not built"}))
+            return
+
+        def step():
+            h, out, v, _ = ref_cuda.e5_forward(True, x, h0, *w, b)
+            return ref_cuda.e5_backward(*w, x, h, v, dy)
+    else:
+        def step():
+            h, out, v = H.pure_lowrank_elman_forward(True, x, h0, *w, b)
+            return H.pure_lowrank_elman_backward(*w, x, h, v, dy)
+    flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    launches0 = _lib.launch_count()
+    total = 0.0
+    for _ in range(args.steps):
+        flush_buf.zero_()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(); step(); s1.record(); s1.synchronize()
+        total += s0.elapsed_time(s1)
+    if rank == 0:
+        print(json.dumps({
+            "impl": args.impl, "metric": "E5 layer fwd+bwd tokens/s @ d1536 r270 B32 T512",
+            "value": Bd * Td * args.steps / (total / 1e3), "unit": UNIT, "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total / args.steps,
+            "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[3]: E5 low-rank cell fwd+bwd, bf16, d=1536, r=270, "
+                                   "B=32, T=512"},
+            "gpu_launches": _lib.launch_count() - launches0,
+            "device_status": _lib.device_status()[0]}), flush=True)
+
+
 def run_lm(args, rank, world, local_rank):
     """configs[2]: full E1 byte-level LM (d=1280 x 6 layers, 49.5M parameters), bf16, AdamW,
     T=512, 32 sequences per GPU, seeded Zipf(1.1) token ids; one step = forward, loss,
@@ -315,6 +376,9 @@ def main():
 
     if args.workload == "lm":
         run_lm(args, rank, world, local_rank)
+        return
+    if args.workload == "e5":
+        run_e5(args, rank, world, local_rank)
         return
     if args.impl == "reference":
         run_reference(args, rank)
