@@ -64,6 +64,13 @@ int elman_b200_device_status(int* detail, int clear);
  *   "rec_trace"      1 = the tensor-core recurrence records per-step cycle stamps
  *   "rec_mma_warps"  MMA-issuing warps (independent accumulator chains) of the
  *                    tensor-core recurrence, 1..4, 0 = auto
+ *   "rec_direct_publish"  who advances the step counter of the tensor-core
+ *                    recurrence: 0 = auto (forward: each epilogue warp after its own
+ *                    stores; backward: a dedicated publisher warp), 1 = epilogue
+ *                    warps in both directions, 2 = publisher warp in both.  All
+ *                    modes give bit-identical results.
+ *   "rec_w_tmem"     1 = keep the recurrent weight tile in tensor memory instead
+ *                    of shared memory (A operand read from TMEM); bit-identical
  * Returns ELMAN_OK or ELMAN_ERR_ARG for an unknown name.
  */
 int elman_b200_set_option(const char* name, long value);
