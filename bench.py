@@ -53,6 +53,13 @@ def parse_args():
     ap.add_argument("--workload", default="cell", choices=["cell", "lm", "e5"],
                     help="cell = configs[1] (the headline line); lm = configs[2] training step; "
                          "e5 = configs[3] low-rank cell")
+    ap.add_argument("--pipeline-chunks", type=int, default=8,
+                    help="lm workload, our arm: time chunks of the (layer, time chunk) pipeline "
+                         "over CUDA streams; 0 or 1 = layers one after another as the reference")
+    ap.add_argument("--pipeline-streams", type=int, default=0, help="0 = from the SM count")
+    ap.add_argument("--cuda-graph", type=int, default=-1,
+                    help="lm workload, our arm: 1 = capture the training step into a CUDA graph; "
+                         "-1 = on for one GPU, off under DDP")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=128,
                     help="time steps of the workload the CPU baseline runs")
@@ -311,16 +318,26 @@ def run_lm(args, rank, world, local_rank):
             return
         mamba_gated_elman.hasty_pytorch_lib = _RefCudaBackend
     torch.manual_seed(1234)
-    model = ladder_lm.LadderLM(vocab_size=256, dim=D, depth=6, level=1, expansion=1.0)
+    chunks = args.pipeline_chunks if args.impl == "ours" else 0
+    model = ladder_lm.LadderLM(vocab_size=256, dim=D, depth=6, level=1, expansion=1.0,
+                               pipeline_chunks=chunks, pipeline_streams=args.pipeline_streams)
     model = model.to(dev).bfloat16()
     net = model
     if world > 1:
         net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank],
                                                         find_unused_parameters=False)
-    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    graphed = args.impl == "ours" and (args.cuda_graph == 1 or (args.cuda_graph < 0 and world == 1))
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
+                            capturable=graphed)
     host_tokens = ladder_lm.zipf_tokens(B, T + 1, seed=1234 + rank).pin_memory()
+    if graphed:
+        from elman_b200.train_step import GraphedTrainStep
+        gstep = GraphedTrainStep(net, opt, host_tokens.to(dev), max_grad_norm=1.0,
+                                 autocast_dtype=torch.bfloat16)
 
     def step():
+        if graphed:
+            return gstep(host_tokens)
         tok = host_tokens.to(dev, non_blocking=True)
         opt.zero_grad(set_to_none=True)
         with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
@@ -344,7 +361,7 @@ def run_lm(args, rank, world, local_rank):
     for _ in range(args.steps):
         loss = step()
     ev1.record()
-    loss_val = float(loss)           # device -> host read of the step's result
+    loss_val = float(loss.detach())  # device -> host read of the step's result
     barrier()
     ms = ev0.elapsed_time(ev1)
     t_all = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -360,9 +377,11 @@ def run_lm(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "configs[2]: LadderLM level 1, d=1280, depth 6, AdamW, "
                                    "Zipf(1.1) tokens, DDP" + (" (NCCL)" if world > 1 else ""),
-                       "params": model.get_num_params()},
+                       "params": model.get_num_params(),
+                       "pipeline_chunks": chunks, "cuda_graph": bool(graphed)},
             "final_loss": loss_val,
-            "gpu_launches": _lib.launch_count() - launches0}), flush=True)
+            "gpu_launches": (gstep.library_launches_per_step * args.steps if graphed
+                             else _lib.launch_count() - launches0)}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -42,6 +42,9 @@ SIGNATURES = {
     "elman_e1_forward_static": (_I, [_I, _I, _I, _I, _I] + [_P] * 6 + [_P] * 3 + [_P]),
     "elman_e1_backward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e1_backward": (_I, [_I, _I, _I, _I] + [_P] * 7 + [_P] * 5 + [_P, _Z, _P]),
+    "elman_e1_forward_flags": (_I, [_I, _I, _I, _I, _I, _I] + [_P] * 6 + [_P] * 3 + [_P, _Z, _P]),
+    "elman_e1_backward_carry": (_I, [_I, _I, _I, _I, _I] + [_P] * 8 + [_P] * 6 + [_P, _Z, _P]),
+    "elman_b200_recurrence_blocks": (_I, [_I, _I, _I, _I, _I]),
     "elman_e0_forward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e0_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 7 + [_P] * 4 + [_P, _Z, _P]),
     "elman_e0_backward_workspace": (_Z, [_I, _I, _I, _I]),

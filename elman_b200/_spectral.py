@@ -24,6 +24,13 @@ def spectrally_normalised(module, W_h: torch.Tensor) -> torch.Tensor:
             v = v / (v.norm() + EPS)
             u = W_h @ v
             u = u / (u.norm() + EPS)
-        module._spectral_u = u
+        # keep the vector in place once it exists: a captured CUDA graph then reads
+        # and advances the same buffer on every replay
+        if getattr(module, "_spectral_u", None) is not None and module._spectral_u.shape == u.shape \
+                and module._spectral_u.device == u.device and module._spectral_u.dtype == u.dtype:
+            module._spectral_u.copy_(u)
+            u = module._spectral_u
+        else:
+            module._spectral_u = u
     sigma = (u @ W_h @ v).abs()
     return W_h * (TARGET_RADIUS / (sigma + EPS))

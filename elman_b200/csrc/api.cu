@@ -215,18 +215,31 @@ static size_t carve_e1_bwd(int dtype, int T, int B, int d, void* ws, E1BwdWs* o)
 }
 
 static int run_rec_fwd(int dtype, int T, int B, int d, const void* W, const void* pre,
-                       const void* g, void* h, void* y, void* v, int* sync, cudaStream_t st) {
+                       const void* g, void* h, void* y, void* v, int* sync, cudaStream_t st,
+                       int compact = 0) {
   PhaseTimer timer(0, st);
   RecFwdArgs a{T, B, d, W, pre, g, h, y, v, sync};
+  a.compact = compact;
   if (dense_tc_ok(dtype, T, B, d)) return rec_fwd_tc(a, st);
   return rec_fwd_generic(dtype, a, st);
 }
 
+// dv_in: [B,d] gradient of the pre-activation of the step after this call's last
+// one (null = none); it becomes slot T of dv, the state the first reverse step reads.
 static int run_rec_bwd(int dtype, int T, int B, int d, const void* Wt, const void* h,
                        const void* v, const void* g, const void* dy, void* dv, void* dg, float* db,
-                       int* sync, cudaStream_t st) {
+                       int* sync, const void* dv_in, cudaStream_t st, int compact = 0) {
+  {
+    const size_t slot = (size_t)B * d * esize(dtype);
+    char* last = (char*)dv + (size_t)T * slot;
+    if (dv_in != nullptr)
+      ELMAN_CUDA_CHECK(cudaMemcpyAsync(last, dv_in, slot, cudaMemcpyDeviceToDevice, st));
+    else
+      ELMAN_CUDA_CHECK(cudaMemsetAsync(last, 0, slot, st));
+  }
   PhaseTimer timer(1, st);
   RecBwdArgs a{T, B, d, Wt, h, v, g, dy, dv, dg, db, sync};
+  a.compact = compact;
   if (dense_tc_ok(dtype, T, B, d)) return rec_bwd_tc(a, st);
   return rec_bwd_generic(dtype, a, st);
 }
@@ -303,6 +316,12 @@ int elman_b200_recurrence_trace(long long* dst, int max_entries) {
 long elman_b200_launch_count(void) { return g_launches.load(); }
 long elman_b200_tc_launch_count(void) { return g_tc_launches.load(); }
 
+int elman_b200_recurrence_blocks(int dtype, int flags, int T, int B, int d) {
+  if (T <= 0 || B <= 0 || d <= 0) return 0;
+  return dense_tc_ok(dtype, T, B, d) ? rec_tc_blocks(T, B, d, (flags & ELMAN_FLAG_COMPACT) ? 1 : 0)
+                                     : 0;
+}
+
 // ------------------------------- E1 ----------------------------------------
 
 size_t elman_e1_forward_workspace(int dtype, int T, int B, int d) {
@@ -314,6 +333,15 @@ int elman_e1_forward(int dtype, int training, int T, int B, int d, const void* x
                      const void* h0, const void* W_x, const void* W_h, const void* b, void* h,
                      void* output, void* v, void* workspace, size_t workspace_bytes,
                      void* stream) {
+  return elman_e1_forward_flags(dtype, 0, training, T, B, d, x, z, h0, W_x, W_h, b, h, output, v,
+                                workspace, workspace_bytes, stream);
+}
+
+int elman_e1_forward_flags(int dtype, int flags, int training, int T, int B, int d, const void* x,
+                           const void* z, const void* h0, const void* W_x, const void* W_h,
+                           const void* b, void* h, void* output, void* v, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  ELMAN_ARG_CHECK((flags & ~ELMAN_FLAG_COMPACT) == 0, "unknown flags 0x%x", flags);
   ELMAN_RETURN_IF(check_common(dtype, T, B, d));
   if (B == 0 || d == 0) return ELMAN_OK;
   REQUIRE_PTR(h0); REQUIRE_PTR(h);
@@ -333,7 +361,8 @@ int elman_e1_forward(int dtype, int training, int T, int B, int d, const void* x
     PhaseTimer timer(2, st);
     ELMAN_RETURN_IF(proj_nt(dtype, T * B, d, d, x, d, W_x, d, b, w.pre, d, 0, st));
   }
-  return run_rec_fwd(dtype, T, B, d, W_h, w.pre, z, h, output, training ? v : nullptr, w.sync, st);
+  return run_rec_fwd(dtype, T, B, d, W_h, w.pre, z, h, output, training ? v : nullptr, w.sync, st,
+                     (flags & ELMAN_FLAG_COMPACT) ? 1 : 0);
 }
 
 size_t elman_e1_backward_workspace(int dtype, int T, int B, int d) {
@@ -345,6 +374,17 @@ int elman_e1_backward(int dtype, int T, int B, int d, const void* W_x, const voi
                       const void* x, const void* z, const void* h, const void* v,
                       const void* d_output, void* dx, void* dz, void* dW_x, void* dW_h, void* db,
                       void* workspace, size_t workspace_bytes, void* stream) {
+  return elman_e1_backward_carry(dtype, 0, T, B, d, W_x, W_h, x, z, h, v, d_output, nullptr, dx,
+                                 dz, dW_x, dW_h, db, nullptr, workspace, workspace_bytes, stream);
+}
+
+int elman_e1_backward_carry(int dtype, int flags, int T, int B, int d, const void* W_x,
+                            const void* W_h,
+                            const void* x, const void* z, const void* h, const void* v,
+                            const void* d_output, const void* dv_in, void* dx, void* dz,
+                            void* dW_x, void* dW_h, void* db, void* dv_out, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  ELMAN_ARG_CHECK((flags & ~ELMAN_FLAG_COMPACT) == 0, "unknown flags 0x%x", flags);
   ELMAN_RETURN_IF(check_common(dtype, T, B, d));
   if (d == 0) return ELMAN_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -354,6 +394,14 @@ int elman_e1_backward(int dtype, int T, int B, int d, const void* W_x, const voi
     ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_x, 0, (size_t)d * d * es, st));
     ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_h, 0, (size_t)d * d * es, st));
     ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    // no steps: the carried gradient passes through unchanged
+    if (dv_out != nullptr && B > 0) {
+      if (dv_in != nullptr)
+        ELMAN_CUDA_CHECK(cudaMemcpyAsync(dv_out, dv_in, (size_t)B * d * es,
+                                         cudaMemcpyDeviceToDevice, st));
+      else
+        ELMAN_CUDA_CHECK(cudaMemsetAsync(dv_out, 0, (size_t)B * d * es, st));
+    }
     return ELMAN_OK;
   }
   REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(x); REQUIRE_PTR(z); REQUIRE_PTR(h);
@@ -365,7 +413,10 @@ int elman_e1_backward(int dtype, int T, int B, int d, const void* W_x, const voi
     return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
   const int TB = T * B;
   ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
-  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, z, d_output, w.dv, dz, w.db, w.sync, st));
+  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, z, d_output, w.dv, dz, w.db, w.sync,
+                              dv_in, st, (flags & ELMAN_FLAG_COMPACT) ? 1 : 0));
+  if (dv_out != nullptr)
+    ELMAN_CUDA_CHECK(cudaMemcpyAsync(dv_out, w.dv, (size_t)B * d * es, cudaMemcpyDeviceToDevice, st));
   ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
   // dx = dv W_x ; dW_x = dv^T x ; dW_h = dv^T h[0:T]
   PhaseTimer timer(3, st);
@@ -523,7 +574,7 @@ int elman_e0_backward(int dtype, int T, int B, int d, const void* W_x, const voi
   const int TB = T * B;
   ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
   ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, gate_cache, d_output, w.dv, w.dg, w.db,
-                              w.sync, st));
+                              w.sync, nullptr, st));
   ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
   ELMAN_RETURN_IF(column_sum(dtype, TB, d, w.dg, db_gate, w.cs, st));
   // dx = dv W_x + dg W_gate

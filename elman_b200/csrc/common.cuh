@@ -148,6 +148,7 @@ struct RecFwdArgs {
   void* y;            // [T,B,d]
   void* v;            // [T,B,d] or null
   int* sync;          // zeroed ints (barrier / step counters)
+  int compact = 0;    // tensor-core kernel: prefer the plan with the fewest resident blocks
 };
 struct RecBwdArgs {
   int T, B, d;
@@ -160,6 +161,7 @@ struct RecBwdArgs {
   void* dg;           // [T,B,d]
   float* db;          // [d] fp32 sum over t,b of dv
   int* sync;
+  int compact = 0;
 };
 size_t rec_sync_bytes();
 int rec_fwd_generic(int dtype, const RecFwdArgs& a, cudaStream_t stream);
@@ -189,6 +191,8 @@ int lowrank_bwd_generic(int dtype, const LowRankBwdArgs& a, cudaStream_t stream)
 
 // Dense recurrence, bf16, tcgen05 + TMA persistent cluster kernel.
 bool rec_tc_supported(int T, int B, int d);
+// resident thread blocks of one launch (compact: smallest-footprint plan), 0 if unsupported
+int rec_tc_blocks(int T, int B, int d, int compact);
 size_t rec_tc_sync_bytes();
 int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream);
 int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream);

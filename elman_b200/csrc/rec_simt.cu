@@ -203,7 +203,9 @@ __global__ void __launch_bounds__(NTHREADS) rec_bwd_simt_kernel(DenseParams p) {
   __syncthreads();
 
   for (int t = p.T - 1; t >= 0; --t) {
-    const bool has_rec = (t + 1 < p.T);
+    // slot T of dv holds the gradient carried in from the steps after this call
+    // (all zero when there are none), so the first step reads it like any other
+    const bool has_rec = true;
     for (int b0 = 0; b0 < p.B; b0 += p.Bc) {
       int nb = p.B - b0 < p.Bc ? p.B - b0 : p.Bc;
       if (has_rec) {

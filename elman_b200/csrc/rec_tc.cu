@@ -302,7 +302,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   // dynamic shared memory carve-up (1024-byte aligned for the swizzled tiles)
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sW = smem;                                    // nkt tiles of [128 x 64] bf16
-  const int w_bytes = TILE_M * Kc * 2;
+  const int w_bytes = p.w_tmem ? 0 : TILE_M * Kc * 2;    // W in tensor memory needs no tile here
   uint8_t* sState = sW + w_bytes;                        // nstages x nkt tiles of [Npad x 64]
   const int state_tile_bytes = Npad * 64 * 2;
   const int state_stage_bytes = nkt * state_tile_bytes;
@@ -799,8 +799,8 @@ struct RecPlan {
   bool ok;
 };
 
-size_t plan_smem(int S, int Kc, int Npad, int nstages) {
-  size_t w = (size_t)TILE_M * Kc * 2;
+size_t plan_smem(int S, int Kc, int Npad, int nstages, bool w_tmem) {
+  size_t w = w_tmem ? 0 : (size_t)TILE_M * Kc * 2;
   size_t st = (size_t)nstages * Npad * Kc * 2;
   size_t stg = (size_t)2 * TILE_M * Npad * 4;
   size_t in = (size_t)2 * 4 * Npad * (TILE_M / S) * 2;  // epilogue input tiles (backward: 4 arrays)
@@ -808,7 +808,7 @@ size_t plan_smem(int S, int Kc, int Npad, int nstages) {
 }
 
 // Full plan for one K split S and one cap on the batch-group size, or ok == false.
-RecPlan plan_for(int B, int d, int S, int ng_cap) {
+RecPlan plan_for(int B, int d, int S, int ng_cap, bool want_w_tmem) {
   RecPlan pl{};
   pl.ok = false;
   pl.w_tmem = 0;
@@ -838,18 +838,20 @@ RecPlan plan_for(int B, int d, int S, int ng_cap) {
   if (nmw > Kc / 16) nmw = Kc / 16;
   while (nmw > 1 && 2 * nmw * Npad > 512) --nmw;
   if (2 * nmw * Npad > 512) return pl;
-  const bool w_tmem = options().rec_w_tmem != 0 && 2 * nmw * Npad + Kc / 2 <= 512;
+  if (want_w_tmem)  // fewer accumulator chains if that lets the W tile fit
+    while (nmw > 2 && 2 * nmw * Npad + Kc / 2 > 512) --nmw;
+  const bool w_tmem = want_w_tmem && 2 * nmw * Npad + Kc / 2 <= 512;
   uint32_t cols = 32;
   while (cols < (uint32_t)(2 * nmw * Npad + (w_tmem ? Kc / 2 : 0))) cols <<= 1;
   pl.w_tmem = w_tmem ? 1 : 0;
   // a single batch group runs strictly step after step: one ring stage is enough
   const int min_stages = G > 1 ? 2 : 1;
   int nstages = G > 1 ? 4 : 2;
-  while (nstages > min_stages && plan_smem(S, Kc, Npad, nstages) > smem_cap) --nstages;
-  if (plan_smem(S, Kc, Npad, nstages) > smem_cap) return pl;
+  while (nstages > min_stages && plan_smem(S, Kc, Npad, nstages, w_tmem) > smem_cap) --nstages;
+  if (plan_smem(S, Kc, Npad, nstages, w_tmem) > smem_cap) return pl;
   pl.S = S; pl.Kc = Kc; pl.G = G; pl.Ng = Ng; pl.Npad = Npad; pl.nstages = nstages;
   pl.nmw = nmw; pl.tmem_cols = cols;
-  pl.smem = plan_smem(S, Kc, Npad, nstages);
+  pl.smem = plan_smem(S, Kc, Npad, nstages, w_tmem);
   pl.ok = true;
   return pl;
 }
@@ -884,32 +886,44 @@ bool plan_is_coresident(const RecPlan& pl, int d) {
 
 // Largest K split first (most CTAs, smallest resident tile); a split whose clusters do
 // not all fit on the device at once is skipped.  Results are cached per shape.
-RecPlan make_plan(int T, int B, int d) {
+RecPlan make_plan(int T, int B, int d, int compact) {
   RecPlan none{};
   none.ok = false;
   if (T < 1 || B < 1 || d < 128 || (d % 128) != 0) return none;
-  struct Key { int B, d; long s, g, w, wt; };
+  struct Key { int B, d, compact; long s, g, w, wt; };
   struct Entry { Key k; RecPlan pl; };
-  static Entry cache[16];
+  static Entry cache[32];
   static int ncache = 0;
-  const Key key{B, d, options().rec_ksplit, options().rec_groups, options().rec_mma_warps,
+  const Key key{B, d, compact, options().rec_ksplit, options().rec_groups, options().rec_mma_warps,
                 options().rec_w_tmem};
   for (int i = 0; i < ncache; ++i) {
     const Key& c = cache[i].k;
-    if (c.B == key.B && c.d == key.d && c.s == key.s && c.g == key.g && c.w == key.w &&
-        c.wt == key.wt)
+    if (c.B == key.B && c.d == key.d && c.compact == key.compact && c.s == key.s &&
+        c.g == key.g && c.w == key.w && c.wt == key.wt)
       return cache[i].pl;
   }
   RecPlan found = none;
   const long want_S = options().rec_ksplit;
-  for (int S = MAX_S; S >= 1 && !found.ok; S >>= 1) {
-    if (want_S > 0 && S != want_S) continue;
-    for (int ng_cap = 32; ng_cap >= 16 && !found.ok; ng_cap >>= 1) {
-      RecPlan pl = plan_for(B, d, S, ng_cap);
-      if (pl.ok && plan_is_coresident(pl, d)) found = pl;
+  if (compact) {
+    // smallest footprint: the smallest K split whose tile of W fits in shared memory
+    // or, failing that, in tensor memory
+    for (int S = 1; S <= MAX_S && !found.ok; S <<= 1) {
+      if (want_S > 0 && S != want_S) continue;
+      for (int wt = 0; wt <= 1 && !found.ok; ++wt) {
+        RecPlan pl = plan_for(B, d, S, 32, wt != 0);
+        if (pl.ok && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d)) found = pl;
+      }
+    }
+  } else {
+    for (int S = MAX_S; S >= 1 && !found.ok; S >>= 1) {
+      if (want_S > 0 && S != want_S) continue;
+      for (int ng_cap = 32; ng_cap >= 16 && !found.ok; ng_cap >>= 1) {
+        RecPlan pl = plan_for(B, d, S, ng_cap, options().rec_w_tmem != 0);
+        if (pl.ok && plan_is_coresident(pl, d)) found = pl;
+      }
     }
   }
-  if (ncache < 16) cache[ncache++] = Entry{key, found};
+  if (ncache < 32) cache[ncache++] = Entry{key, found};
   return found;
 }
 
@@ -968,7 +982,12 @@ void fill_plan(const RecPlan& pl, RecTcParams& p) {
 
 }  // namespace
 
-bool rec_tc_supported(int T, int B, int d) { return make_plan(T, B, d).ok; }
+bool rec_tc_supported(int T, int B, int d) { return make_plan(T, B, d, 0).ok; }
+
+int rec_tc_blocks(int T, int B, int d, int compact) {
+  RecPlan pl = make_plan(T, B, d, compact);
+  return pl.ok ? (d / TILE_M) * pl.S * pl.G : 0;
+}
 
 size_t rec_tc_sync_bytes() {
   return (size_t)(MAX_GROUPS * MAX_S * COUNTER_STRIDE + 64) * sizeof(int) +
@@ -991,7 +1010,7 @@ int rec_tc_copy_trace(long long* dst, int max_entries) {
 }
 
 int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
-  RecPlan pl = make_plan(a.T, a.B, a.d);
+  RecPlan pl = make_plan(a.T, a.B, a.d, a.compact);
   if (!pl.ok) return set_error(ELMAN_ERR_UNSUPPORTED, "shape not supported by the tensor-core recurrence");
   RecTcParams p{};
   p.T = a.T; p.B = a.B; p.d = a.d;
@@ -1010,7 +1029,7 @@ int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
 }
 
 int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream) {
-  RecPlan pl = make_plan(a.T, a.B, a.d);
+  RecPlan pl = make_plan(a.T, a.B, a.d, a.compact);
   if (!pl.ok) return set_error(ELMAN_ERR_UNSUPPORTED, "shape not supported by the tensor-core recurrence");
   RecTcParams p{};
   p.T = a.T; p.B = a.B; p.d = a.d;
@@ -1018,9 +1037,7 @@ int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream) {
   p.h_in = (const bf16*)a.h; p.v_in = (const bf16*)a.v; p.g = (const bf16*)a.g;
   p.dy = (const bf16*)a.dy; p.dv = (bf16*)a.dv; p.dg = (bf16*)a.dg; p.db = a.db;
   ELMAN_CUDA_CHECK(cudaMemsetAsync(a.sync, 0, rec_tc_sync_bytes(), stream));
-  // slot T of dv is the all-zero "gradient from the future" read by the first step
-  ELMAN_CUDA_CHECK(cudaMemsetAsync((bf16*)a.dv + (size_t)a.T * a.B * a.d, 0,
-                                   (size_t)a.B * a.d * sizeof(bf16), stream));
+  // slot T of dv (the gradient carried in from later steps, or zeros) is filled by the caller
   p.ready = a.sync;
   p.abort_word = a.sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE;
   p.trace = trace_area(a.sync);

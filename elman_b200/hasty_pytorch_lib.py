@@ -57,8 +57,13 @@ def _stream(device):
 
 # --------------------------------------------------------------------------- E1
 
-def mamba_gated_elman_forward(training, x, z, h0, W_x, W_h, b):
-    """-> [h[T+1,B,d], output[T,B,d], v[T,B,d] (empty if not training)]"""
+FLAG_COMPACT = 1   # ELMAN_FLAG_COMPACT: smallest-footprint recurrence launch
+
+
+def mamba_gated_elman_forward(training, x, z, h0, W_x, W_h, b, flags=0):
+    """-> [h[T+1,B,d], output[T,B,d], v[T,B,d] (empty if not training)]
+
+    `flags` is not a reference argument (see elman_e1_forward_flags)."""
     fn = "mamba_gated_elman_forward"
     dt = _check_inputs(fn, x, x=x, z=z, h0=h0, W_x=W_x, W_h=W_h, b=b)
     if x.dim() != 3:
@@ -73,9 +78,10 @@ def mamba_gated_elman_forward(training, x, z, h0, W_x, W_h, b):
         v = torch.empty((T, B, d) if training else (0,), dtype=x.dtype, device=x.device)
         nws = lib.elman_e1_forward_workspace(dt, T, B, d)
         ws = _workspace(nws, x.device)
-        rc = lib.elman_e1_forward(dt, 1 if training else 0, T, B, d, _ptr(x), _ptr(z), _ptr(h0),
-                                  _ptr(W_x), _ptr(W_h), _ptr(b), _ptr(h), _ptr(out), _ptr(v),
-                                  ws.data_ptr(), ws.numel(), _stream(x.device))
+        rc = lib.elman_e1_forward_flags(dt, int(flags), 1 if training else 0, T, B, d, _ptr(x),
+                                        _ptr(z), _ptr(h0), _ptr(W_x), _ptr(W_h), _ptr(b), _ptr(h),
+                                        _ptr(out), _ptr(v), ws.data_ptr(), ws.numel(),
+                                        _stream(x.device))
         _lib.check(rc, fn)
         ws.record_stream(torch.cuda.current_stream(x.device))
     return [h, out, v]
@@ -104,6 +110,52 @@ def mamba_gated_elman_backward(W_x, W_h, x, z, h, v, d_output):
         _lib.check(rc, fn)
         ws.record_stream(torch.cuda.current_stream(x.device))
     return [dx, dz, dW_x, dW_h, db]
+
+
+def mamba_gated_elman_backward_carry(W_x, W_h, x, z, h, v, d_output, dv_in=None, flags=0):
+    """Backward over one time chunk -> [dx, dz, dW_x, dW_h, db, dv_out].
+
+    An extension with no counterpart in the reference: `dv_in` [B,d] is the
+    `dv_out` of the chunk that follows in time (None for the last chunk) and
+    `dv_out` [B,d] goes to the chunk that precedes.  With dv_in=None the first
+    five results equal mamba_gated_elman_backward's.
+    """
+    fn = "mamba_gated_elman_backward_carry"
+    tensors = dict(W_x=W_x, W_h=W_h, x=x, z=z, h=h, v=v, d_output=d_output)
+    if dv_in is not None:
+        tensors["dv_in"] = dv_in
+    dt = _check_inputs(fn, x, **tensors)
+    T, B, d = x.shape
+    _shape(fn, z, (T, B, d), "z"); _shape(fn, h, (T + 1, B, d), "h")
+    _shape(fn, v, (T, B, d), "v"); _shape(fn, d_output, (T, B, d), "d_output")
+    _shape(fn, W_x, (d, d), "W_x"); _shape(fn, W_h, (d, d), "W_h")
+    if dv_in is not None:
+        _shape(fn, dv_in, (B, d), "dv_in")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        dx = torch.empty_like(x)
+        dz = torch.empty_like(z)
+        dW_x = torch.empty(d, d, dtype=x.dtype, device=x.device)
+        dW_h = torch.empty(d, d, dtype=x.dtype, device=x.device)
+        db = torch.empty(d, dtype=x.dtype, device=x.device)
+        dv_out = torch.empty(B, d, dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e1_backward_workspace(dt, T, B, d), x.device)
+        rc = lib.elman_e1_backward_carry(dt, int(flags), T, B, d, _ptr(W_x), _ptr(W_h), _ptr(x), _ptr(z),
+                                         _ptr(h), _ptr(v), _ptr(d_output), _ptr(dv_in), _ptr(dx),
+                                         _ptr(dz), _ptr(dW_x), _ptr(dW_h), _ptr(db), _ptr(dv_out),
+                                         ws.data_ptr(), ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [dx, dz, dW_x, dW_h, db, dv_out]
+
+
+def recurrence_blocks(dtype, T, B, d, flags=0):
+    """Thread blocks one E1/E0 recurrence launch of this shape keeps resident (0 when the
+    shape takes a cooperative-launch kernel); see elman_b200_recurrence_blocks."""
+    if dtype not in _DT:
+        raise RuntimeError(f"recurrence_blocks: dtype {dtype} is not supported")
+    return int(_lib.load().elman_b200_recurrence_blocks(_DT[dtype], int(flags), int(T), int(B),
+                                                        int(d)))
 
 
 # --------------------------------------------------------------------------- E0

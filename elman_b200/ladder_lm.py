@@ -31,8 +31,16 @@ def get_ladder_level(level):
 class LadderLM(nn.Module):
     def __init__(self, vocab_size=256, dim=512, depth=12, level=0, expansion=1.0, rank=None,
                  dropout=0.0, r_h_mode="spectral_norm", r_h_init_gain=0.1, mamba2_init=False,
-                 use_conv=False, d_conv=4, loss_chunk_size=0, **unused):
+                 use_conv=False, d_conv=4, loss_chunk_size=0, pipeline_chunks=0,
+                 pipeline_streams=0, **unused):
         super().__init__()
+        # pipeline_chunks > 1 (not a reference argument): run the layer stack as a
+        # wavefront over (layer, time chunk) on several CUDA streams, see _pipelined_layers
+        self.pipeline_chunks = int(pipeline_chunks)
+        self.pipeline_streams = int(pipeline_streams)
+        # overlapped recurrences run with their smallest footprint (ELMAN_FLAG_COMPACT)
+        self.pipeline_flags = 1
+        self._streams = {}
         self.vocab_size = vocab_size
         self.dim = dim
         self.depth = depth
@@ -64,15 +72,18 @@ class LadderLM(nn.Module):
         h = self.embedding(inp)
         if prev_hiddens is None:
             prev_hiddens = [None] * self.depth
-        new_hiddens = []
-        residual = None
-        for i, (ln, layer) in enumerate(zip(self.layer_norms, self.layers)):
-            residual = (h + residual) if residual is not None else h
-            h = ln(residual.to(dtype=ln.weight.dtype))
-            if self.residual_in_fp32:
-                residual = residual.to(torch.float32)
-            h, h_final = layer(h, prev_hiddens[i])
-            new_hiddens.append(h_final)
+        if self._can_pipeline(h):
+            h, residual, new_hiddens = self._pipelined_layers(h, prev_hiddens)
+        else:
+            new_hiddens = []
+            residual = None
+            for i, (ln, layer) in enumerate(zip(self.layer_norms, self.layers)):
+                residual = (h + residual) if residual is not None else h
+                h = ln(residual.to(dtype=ln.weight.dtype))
+                if self.residual_in_fp32:
+                    residual = residual.to(torch.float32)
+                h, h_final = layer(h, prev_hiddens[i])
+                new_hiddens.append(h_final)
         h = self.norm((h + residual).to(dtype=self.norm.weight.dtype))
         if not return_loss:
             logits = self.lm_head(h)
@@ -95,6 +106,98 @@ class LadderLM(nn.Module):
             loss = F.cross_entropy(self.lm_head(h).view(-1, self.vocab_size), target.reshape(-1),
                                    ignore_index=-100)
         return (loss, (new_hiddens, None)) if return_prev_hiddens else loss
+
+    # ------------------------------------------------------------------ pipeline
+    #
+    # A recurrence launch is a chain of T dependent steps that keeps only a
+    # fraction of the GPU's SMs busy, and layer l+1 at time t needs layer l only
+    # up to time t.  Cutting the sequence into C time chunks turns the depth x C
+    # (layer, chunk) units into a wavefront: unit (l, c) needs (l-1, c) for its
+    # input and (l, c-1) for its initial state.  Layers are dealt round-robin to a
+    # few CUDA streams, so up to that many recurrences (and the projections, norms
+    # and copies around them) run side by side.  Autograd runs every backward op on
+    # the stream of its forward op, so the backward pass forms the mirrored
+    # wavefront by itself.  Chained chunks reproduce the unchunked layer exactly
+    # (state carried forward, pre-activation gradient carried backward).
+
+    def _can_pipeline(self, h):
+        return (self.pipeline_chunks > 1 and h.is_cuda and h.size(1) >= 2 * self.pipeline_chunks
+                and all(getattr(layer, "supports_time_chunks", False) for layer in self.layers))
+
+    def _pipeline_streams(self, device, n):
+        key = (device, n)
+        if key not in self._streams:
+            self._streams[key] = [torch.cuda.Stream(device=device) for _ in range(n)]
+        return self._streams[key]
+
+    def _stream_count(self, h, chunk_len):
+        """Streams = recurrences that may run at once.  The thread blocks of one
+        recurrence launch wait for one another, so all launches that can be in
+        flight together must fit on the device at the same time."""
+        if self.pipeline_streams > 0:
+            return self.pipeline_streams
+        from . import hasty_pytorch_lib
+        layer = self.layers[0]
+        d_inner = getattr(layer, "d_inner", self.dim)
+        blocks = hasty_pytorch_lib.recurrence_blocks(h.dtype, chunk_len, h.size(0), d_inner,
+                                                     self.pipeline_flags)
+        sms = torch.cuda.get_device_properties(h.device).multi_processor_count
+        # one stream per layer while all their recurrences fit on the device together
+        n = sms // blocks if blocks > 0 else 2
+        return max(1, min(n, self.depth))
+
+    def _pipelined_layers(self, h, prev_hiddens):
+        B, T, _ = h.shape
+        C = self.pipeline_chunks
+        edges = [(T * c) // C for c in range(C + 1)]
+        main = torch.cuda.current_stream(h.device)
+        streams = self._pipeline_streams(h.device, self._stream_count(h, edges[1] - edges[0]))
+        shared = [layer.chunk_weights() for layer in self.layers]
+        start = torch.cuda.Event()
+        start.record(main)
+        for s in streams:
+            s.wait_event(start)
+        h_chunks = [h[:, edges[c]:edges[c + 1]] for c in range(C)]
+        res_chunks = [None] * C
+        states = []
+        done = [[None] * C for _ in range(self.depth)]
+        for i, (ln, layer) in enumerate(zip(self.layer_norms, self.layers)):
+            s = streams[i % len(streams)]
+            d_inner = getattr(layer, "d_inner", self.dim)
+            state = prev_hiddens[i]
+            state = (torch.zeros(B, d_inner, device=h.device, dtype=h.dtype) if state is None
+                     else state.detach())
+            state.record_stream(s)
+            shared[i].record_stream(s)
+            with torch.cuda.stream(s):
+                for c in range(C):
+                    if i > 0:
+                        s.wait_event(done[i - 1][c])
+                    hin, rin = h_chunks[c], res_chunks[c]
+                    hin.record_stream(s)
+                    if rin is not None:
+                        rin.record_stream(s)
+                    residual = (hin + rin) if rin is not None else hin
+                    hn = ln(residual.to(dtype=ln.weight.dtype))
+                    if self.residual_in_fp32:
+                        residual = residual.to(torch.float32)
+                    out, state = layer.forward_chunk(hn, state, shared[i], self.pipeline_flags)
+                    h_chunks[c], res_chunks[c] = out, residual
+                    done[i][c] = torch.cuda.Event()
+                    done[i][c].record(s)
+            states.append(state)
+        for c in range(C):
+            main.wait_event(done[-1][c])
+            h_chunks[c].record_stream(main)
+            res_chunks[c].record_stream(main)
+        for st in states:
+            st.record_stream(main)
+        for s in streams:  # every stream rejoins the caller's (required under graph capture)
+            joined = torch.cuda.Event()
+            joined.record(s)
+            main.wait_event(joined)
+        return (torch.cat(h_chunks, dim=1), torch.cat(res_chunks, dim=1),
+                [st.detach() for st in states])
 
     def get_num_params(self):
         return sum(p.numel() for p in self.parameters())

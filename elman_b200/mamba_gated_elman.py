@@ -40,6 +40,39 @@ class MambaGatedElmanFunction(torch.autograd.Function):
         return None, dx, dz, None, dW_x, dW_h, db
 
 
+class MambaGatedElmanChunkFunction(torch.autograd.Function):
+    """One time chunk of a longer sequence (no counterpart in the reference).
+
+    forward(x, z, h0, W_x, W_h, b) -> (output [T,B,d], h_last [B,d]).  Chunks are
+    chained by passing h_last as the next chunk's h0.  Between two chained chunks
+    the "gradient" that autograd carries along the h_last -> h0 edge is NOT
+    dL/dh: it is the pre-activation gradient dv of the later chunk's first step,
+    which is what the backward kernel takes as its state from the future
+    (dL/dh would be dv W_h, one more matrix product the kernel does anyway).
+    h_last must therefore only ever feed another chunk's h0 (or be detached), and
+    the h0 of the first chunk gets no gradient, like the reference's Function.
+    """
+
+    @staticmethod
+    def forward(ctx, x, z, h0, W_x, W_h, b, flags=0):
+        h, output, v = hasty_pytorch_lib.mamba_gated_elman_forward(True, x, z, h0, W_x, W_h, b,
+                                                                   flags)
+        ctx.save_for_backward(W_x, W_h, x, z, h, v)
+        ctx.set_materialize_grads(False)
+        ctx.flags = flags
+        return output, h[-1].clone()
+
+    @staticmethod
+    def backward(ctx, d_output, dv_in):
+        W_x, W_h, x, z, h, v = ctx.saved_tensors
+        if d_output is None:
+            d_output = torch.zeros_like(x)
+        dx, dz, dW_x, dW_h, db, dv_out = hasty_pytorch_lib.mamba_gated_elman_backward_carry(
+            W_x, W_h, x, z, h, v, d_output.contiguous(),
+            None if dv_in is None else dv_in.contiguous(), ctx.flags)
+        return dx, dz, dv_out, dW_x, dW_h, db, None
+
+
 class MambaGatedElmanCell(nn.Module):
     """Weights of the recurrence and the dispatch into the CUDA library."""
 
@@ -132,6 +165,29 @@ class MambaGatedElman(nn.Module):
         cell_out, h_all = self.cell(x_rnn, z_rnn, h0)
         y = self.dropout(cell_out.permute(1, 0, 2).contiguous())
         return self.out_proj(y), h_all[-1]
+
+    # ---- time-chunked execution (used by LadderLM's layer/time pipeline) ----
+    @property
+    def supports_time_chunks(self):
+        return not self.use_conv  # the causal conv would need its own carry
+
+    def chunk_weights(self):
+        """What every chunk of one forward pass shares: the effective W_h, computed once
+        (the spectral-norm power iteration advances once per pass, as in forward())."""
+        return self.cell.get_W_h().contiguous()
+
+    def forward_chunk(self, x, h0, W_h, flags=0):
+        """x: [B,Tc,dim], h0: [B,d_inner] (last state of the preceding chunk) ->
+        (output [B,Tc,dim], h_last).  Chained over the chunks of a sequence this equals
+        forward() on the whole sequence."""
+        x_proj, z = self.in_proj(x).chunk(2, dim=-1)
+        x_rnn = F.silu(x_proj).permute(1, 0, 2).contiguous()
+        z_rnn = z.permute(1, 0, 2).contiguous()
+        cell = self.cell
+        cell_out, h_last = MambaGatedElmanChunkFunction.apply(
+            x_rnn, z_rnn, h0.contiguous(), cell.W_x.contiguous(), W_h, cell.b.contiguous(), flags)
+        y = self.dropout(cell_out.permute(1, 0, 2).contiguous())
+        return self.out_proj(y), h_last
 
     def extra_repr(self):
         return f"dim={self.dim}, d_inner={self.d_inner}, use_conv={self.use_conv}, LEVEL=1_MAMBA_GATED"

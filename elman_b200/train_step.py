@@ -1,0 +1,59 @@
+"""A whole training step (forward, loss, backward, gradient clipping, optimizer)
+captured once into a CUDA graph and replayed.
+
+The layer/time pipeline of LadderLM issues a few thousand small launches per step
+on several streams; issued from Python they are bound by the host.  Captured, the
+streams' fork/join structure becomes graph dependencies and a step costs one
+launch.  The reference trains eagerly (train_ladder.py); this is an addition on
+the caller's side and changes no arithmetic.
+
+Requirements: fixed token shape; an optimizer constructed with capturable=True;
+no host synchronisation inside the model (LadderLM has none).
+"""
+import torch
+
+
+class GraphedTrainStep:
+    def __init__(self, net, optimizer, example_tokens, max_grad_norm=1.0, autocast_dtype=None,
+                 warmup_steps=3):
+        self.net, self.opt = net, optimizer
+        self.max_grad_norm = max_grad_norm
+        self.autocast_dtype = autocast_dtype
+        self.tokens = example_tokens.clone()
+        self.params = [p for g in optimizer.param_groups for p in g["params"]]
+        side = torch.cuda.Stream(device=self.tokens.device)
+        side.wait_stream(torch.cuda.current_stream(self.tokens.device))
+        with torch.cuda.stream(side):
+            for _ in range(warmup_steps):  # eager: creates optimizer state, library handles, streams
+                self._eager_step()
+        torch.cuda.current_stream(self.tokens.device).wait_stream(side)
+        torch.cuda.synchronize(self.tokens.device)
+        self.graph = torch.cuda.CUDAGraph()
+        self.opt.zero_grad(set_to_none=True)
+        from . import _lib
+        before = _lib.launch_count()
+        with torch.cuda.graph(self.graph):
+            self.loss = self._eager_step(zero=False)
+        # kernels of the CUDA library inside one captured step (each replay runs them again)
+        self.library_launches_per_step = _lib.launch_count() - before
+
+    def _eager_step(self, zero=True):
+        if zero:
+            self.opt.zero_grad(set_to_none=True)
+        if self.autocast_dtype is not None:
+            with torch.autocast(device_type="cuda", dtype=self.autocast_dtype):
+                loss = self.net(self.tokens, return_loss=True)
+        else:
+            loss = self.net(self.tokens, return_loss=True)
+        loss.backward()
+        if self.max_grad_norm:
+            torch.nn.utils.clip_grad_norm_(self.params, self.max_grad_norm)
+        self.opt.step()
+        return loss.detach()
+
+    def __call__(self, tokens):
+        """Copies `tokens` (host or device) into the captured input and replays the step.
+        Returns the captured loss tensor (valid until the next call)."""
+        self.tokens.copy_(tokens, non_blocking=True)
+        self.graph.replay()
+        return self.loss

@@ -138,6 +138,56 @@ int elman_e1_backward(int dtype, int T, int B, int d,
                       void* dx, void* dz, void* dW_x, void* dW_h, void* db,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * elman_e1_forward with launch flags (an extension; elman_e1_forward is flags 0).
+ *   ELMAN_FLAG_COMPACT  run the recurrence with the plan that keeps the fewest thread
+ *                       blocks resident (a smaller split of the reduction dimension, the
+ *                       weight tile in tensor memory where shared memory cannot hold it)
+ *                       instead of the plan with the shortest step.  For callers that
+ *                       overlap several recurrence launches on different streams: a step
+ *                       gets somewhat slower, the launch leaves more of the GPU to others.
+ * Results differ from flags 0 only by the summation order of the split reduction.
+ */
+#define ELMAN_FLAG_COMPACT 1
+int elman_e1_forward_flags(int dtype, int flags, int training, int T, int B, int d,
+                           const void* x, const void* z, const void* h0,
+                           const void* W_x, const void* W_h, const void* b,
+                           void* h, void* output, void* v,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * E1 backward over one time chunk of a longer sequence (an extension: the
+ * reference's backward, elman/cuda/pytorch/elman_ladder.cc:219-281, always sees
+ * the whole sequence and has no such arguments).  A caller that splits a sequence
+ * into chunks — running elman_e1_forward per chunk with h0 = the previous chunk's
+ * last state — calls this once per chunk in reverse order:
+ *   dv_in  : [B,d] or NULL.  Gradient of the pre-activation of the first step of
+ *            the FOLLOWING chunk, i.e. that chunk's dv_out; NULL for the last chunk.
+ *   dv_out : [B,d] or NULL.  Receives the gradient of this chunk's first
+ *            pre-activation, to be handed to the preceding chunk.
+ * Chained this way the chunks give bit-for-bit the dx, dz of one whole-sequence
+ * call, and dW_x, dW_h, db that sum (over chunks) to its weight gradients.
+ * elman_e1_backward is this function with both pointers NULL and flags 0; the
+ * workspace size is the same.  `flags` as for elman_e1_forward_flags.
+ */
+int elman_e1_backward_carry(int dtype, int flags, int T, int B, int d,
+                            const void* W_x, const void* W_h, const void* x, const void* z,
+                            const void* h, const void* v, const void* d_output,
+                            const void* dv_in,
+                            void* dx, void* dz, void* dW_x, void* dW_h, void* db,
+                            void* dv_out,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Number of thread blocks the recurrence kernel of an E1/E0 call of this shape
+ * keeps resident for the whole launch (each occupies one SM), or 0 when the shape
+ * takes a cooperative-launch kernel, which the driver only starts when it fits.
+ * The blocks of one launch wait for one another, so a caller that overlaps
+ * several recurrence launches on different streams must keep the sum of their
+ * resident blocks within the device's SM count (no counterpart in the reference).
+ */
+int elman_b200_recurrence_blocks(int dtype, int flags, int T, int B, int d);
+
 /* ---------------------------------------------------------------------------
  * E1 forward for callers that cannot allocate device memory.
  *

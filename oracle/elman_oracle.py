@@ -72,16 +72,20 @@ def e1_forward(x: Tensor, z: Tensor, h0: Tensor, W_x: Tensor, W_h: Tensor,
 
 
 def e1_backward(W_x: Tensor, W_h: Tensor, x: Tensor, z: Tensor, h: Tensor,
-                v: Tensor, d_output: Tensor) -> Dict[str, Tensor]:
+                v: Tensor, d_output: Tensor, dv_in: Tensor = None) -> Dict[str, Tensor]:
     """Explicit BPTT in the order of the reference's backward Run().
 
     The gradient of the returned hidden-state sequence is not an input: the
-    reference Function ignores it.
+    reference Function ignores it.  `dv_in` ([B,d], optional) is not part of the
+    reference either: when a sequence is processed in time chunks it carries the
+    pre-activation gradient of the first step of the following chunk, which is
+    all the loop below needs from the future (dh_rec = dv_{t+1} W_h); the
+    result's "dv0" is what the preceding chunk takes as its `dv_in`.
     """
     T, B, d = x.shape
     dv_all = torch.zeros_like(x)
     dz = torch.zeros_like(z)
-    dh_rec = torch.zeros(B, d, dtype=x.dtype)
+    dh_rec = torch.zeros(B, d, dtype=x.dtype) if dv_in is None else dv_in @ W_h
     for t in range(T - 1, -1, -1):
         h_t = h[t + 1]
         dh = d_output[t] * silu(z[t]) + dh_rec
@@ -97,6 +101,7 @@ def e1_backward(W_x: Tensor, W_h: Tensor, x: Tensor, z: Tensor, h: Tensor,
         "dW_x": dv2.T @ x.reshape(T * B, d),
         "dW_h": dv2.T @ h[:T].reshape(T * B, d),
         "db": dv2.sum(0),
+        "dv0": dv_all[0] if T > 0 else dv_in,
     }
 
 

@@ -22,7 +22,7 @@ class OracleBackend:
     """Oracle-backed stand-in with the extension module's function names."""
 
     @staticmethod
-    def mamba_gated_elman_forward(training, x, z, h0, W_x, W_h, b):
+    def mamba_gated_elman_forward(training, x, z, h0, W_x, W_h, b, flags=0):
         o = orc.e1_forward(x, z, h0, W_x, W_h, b)
         return [o["h"], o["output"], o["v"] if training else x.new_empty(0)]
 
@@ -30,6 +30,11 @@ class OracleBackend:
     def mamba_gated_elman_backward(W_x, W_h, x, z, h, v, d_output):
         g = orc.e1_backward(W_x, W_h, x, z, h, v, d_output)
         return [g["dx"], g["dz"], g["dW_x"], g["dW_h"], g["db"]]
+
+    @staticmethod
+    def mamba_gated_elman_backward_carry(W_x, W_h, x, z, h, v, d_output, dv_in=None, flags=0):
+        g = orc.e1_backward(W_x, W_h, x, z, h, v, d_output, dv_in)
+        return [g["dx"], g["dz"], g["dW_x"], g["dW_h"], g["db"], g["dv0"]]
 
     @staticmethod
     def stock_elman_forward(training, x, h0, W_x, W_h, W_gate, b, b_gate):
@@ -164,3 +169,33 @@ def test_state_dict_names_match_reference_layout():
         "out_proj.weight"}
     assert set(e5mod.PureLowRankElman(16, rank=4).state_dict()) == {
         "cell.U_h", "cell.V_h", "cell.U_x", "cell.V_x", "cell.U_z", "cell.V_z", "cell.b"}
+
+
+@pytest.mark.parametrize("cuts", [(0, 3, 5), (0, 1), (0,)])
+def test_e1_layer_in_time_chunks_equals_reference_fixture(golden_dir, oracle_backend, cuts):
+    """forward_chunk chained over time chunks (state forward, pre-activation gradient
+    backward) reproduces the reference layer's whole-sequence output and gradients."""
+    inp, want = load(golden_dir, "e1_layer")
+    dim = inp["x"].shape[-1]
+    layer = e1mod.MambaGatedElman(dim, expansion=1.0)
+    layer.load_state_dict({k[2:]: v for k, v in inp.items() if k.startswith("p_")})
+    x = inp["x"].clone().requires_grad_(True)
+    B, T, _ = x.shape
+    edges = list(cuts) + [T]
+    W_h = layer.chunk_weights()
+    state = torch.zeros(B, layer.d_inner)
+    outs = []
+    for t0, t1 in zip(edges[:-1], edges[1:]):
+        out, state = layer.forward_chunk(x[:, t0:t1], state, W_h)
+        outs.append(out)
+    out = torch.cat(outs, dim=1)
+    (out * inp["d_output"]).sum().backward()
+    got = {"output": out, "h_final": state, "dx": x.grad}
+    for n, p_ in layer.named_parameters():
+        got["g_" + n] = p_.grad
+    checked = 0
+    for k, vref in want.items():
+        if k in got:
+            assert orc.rel_err(got[k], vref) < 2e-5, k
+            checked += 1
+    assert checked >= 4
