@@ -185,8 +185,8 @@ struct PhaseTimer {
   }
 };
 
-static bool dense_tc_ok(int dtype, int T, int B, int d) {
-  return use_tc(dtype) && rec_tc_supported(T, B, d);
+static bool dense_tc_ok(int dtype, int T, int B, int d, int bwd) {
+  return use_tc(dtype) && rec_tc_supported(T, B, d, bwd);
 }
 
 // ---------------------------------------------------------------------------
@@ -220,7 +220,7 @@ static int run_rec_fwd(int dtype, int T, int B, int d, const void* W, const void
   PhaseTimer timer(0, st);
   RecFwdArgs a{T, B, d, W, pre, g, h, y, v, sync};
   a.compact = compact;
-  if (dense_tc_ok(dtype, T, B, d)) return rec_fwd_tc(a, st);
+  if (dense_tc_ok(dtype, T, B, d, 0)) return rec_fwd_tc(a, st);
   return rec_fwd_generic(dtype, a, st);
 }
 
@@ -240,7 +240,7 @@ static int run_rec_bwd(int dtype, int T, int B, int d, const void* Wt, const voi
   PhaseTimer timer(1, st);
   RecBwdArgs a{T, B, d, Wt, h, v, g, dy, dv, dg, db, sync};
   a.compact = compact;
-  if (dense_tc_ok(dtype, T, B, d)) return rec_bwd_tc(a, st);
+  if (dense_tc_ok(dtype, T, B, d, 1)) return rec_bwd_tc(a, st);
   return rec_bwd_generic(dtype, a, st);
 }
 
@@ -280,6 +280,7 @@ int elman_b200_set_option(const char* name, long value) {
   else if (!strcmp(name, "rec_mma_warps")) o.rec_mma_warps = value;
   else if (!strcmp(name, "rec_direct_publish")) o.rec_direct_publish = value;
   else if (!strcmp(name, "rec_w_tmem")) o.rec_w_tmem = value;
+  else if (!strcmp(name, "rec_large_batch")) o.rec_large_batch = value;
   else return set_error(ELMAN_ERR_ARG, "unknown option '%s'", name);
   return ELMAN_OK;
 }
@@ -296,6 +297,7 @@ long elman_b200_get_option(const char* name) {
   if (!strcmp(name, "rec_mma_warps")) return o.rec_mma_warps;
   if (!strcmp(name, "rec_direct_publish")) return o.rec_direct_publish;
   if (!strcmp(name, "rec_w_tmem")) return o.rec_w_tmem;
+  if (!strcmp(name, "rec_large_batch")) return o.rec_large_batch;
   return -1;
 }
 
@@ -318,7 +320,7 @@ long elman_b200_tc_launch_count(void) { return g_tc_launches.load(); }
 
 int elman_b200_recurrence_blocks(int dtype, int flags, int T, int B, int d) {
   if (T <= 0 || B <= 0 || d <= 0) return 0;
-  return dense_tc_ok(dtype, T, B, d) ? rec_tc_blocks(T, B, d, (flags & ELMAN_FLAG_COMPACT) ? 1 : 0)
+  return dense_tc_ok(dtype, T, B, d, 0) && dense_tc_ok(dtype, T, B, d, 1) ? rec_tc_blocks(T, B, d, (flags & ELMAN_FLAG_COMPACT) ? 1 : 0)
                                      : 0;
 }
 

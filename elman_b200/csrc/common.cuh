@@ -50,6 +50,7 @@ struct Options {
   long rec_mma_warps = 0;
   long rec_direct_publish = 0;
   long rec_w_tmem = 0;
+  long rec_large_batch = 1;    // 1: batches over 32 take the wide-group throughput plan
 };
 Options& options();
 void count_launch(bool tensor_core);
@@ -190,7 +191,7 @@ int lowrank_fwd_generic(int dtype, const LowRankFwdArgs& a, cudaStream_t stream)
 int lowrank_bwd_generic(int dtype, const LowRankBwdArgs& a, cudaStream_t stream);
 
 // Dense recurrence, bf16, tcgen05 + TMA persistent cluster kernel.
-bool rec_tc_supported(int T, int B, int d);
+bool rec_tc_supported(int T, int B, int d, int bwd);   // per direction: the plans differ
 // resident thread blocks of one launch (compact: smallest-footprint plan), 0 if unsupported
 int rec_tc_blocks(int T, int B, int d, int compact);
 size_t rec_tc_sync_bytes();

@@ -20,9 +20,11 @@
 //      (forward: + W_x x_t + b, tanh, h*silu(z); backward: the tanh / gate
 //      derivatives and the running bias gradient) and writes the new state, then
 //      bumps the counter.
-// Roles are warp-specialised: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
-// owner, warps 2..5 = epilogue.  Independent batch groups are pipelined through
-// the same rings, so one group's global round trip overlaps another's math.
+// Roles are warp-specialised: warp 0 = TMA producer, warps 1..4 = MMA issuers (warp 1
+// owns the TMEM allocation), warps 5..8 = drain (step 4), warps 9..12 = finalise
+// (step 5), warp 13 = publisher of the step counter.  Independent batch groups are
+// pipelined through the same rings, so one group's global round trip, its drain and
+// its finalising each overlap another group's math.
 //
 // Every wait (global counters, mbarriers) is bounded; a wait that gives up raises
 // an abort word all CTAs poll, records a status code and the kernel drains and
@@ -39,7 +41,9 @@ namespace {
 constexpr int TILE_M = 128;
 constexpr int NUM_EPI_THREADS = 128;
 constexpr int NUM_MMA_WARPS = 4;
-constexpr int NUM_THREADS = 32 + NUM_MMA_WARPS * 32 + NUM_EPI_THREADS + 32;  // + publisher warp
+constexpr int NUM_DRAIN_THREADS = 128;  // four warps: one per quarter of the TMEM lanes
+constexpr int NUM_THREADS =
+    32 + NUM_MMA_WARPS * 32 + NUM_DRAIN_THREADS + NUM_EPI_THREADS + 32;  // + publisher warp
 constexpr int MAX_S = 8;
 constexpr int MAX_GROUPS = 16;
 constexpr int MAX_QUADS = 2;       // batch quads (4 rows) per epilogue thread and step
@@ -354,9 +358,9 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
   if (p.w_tmem) {
     // One-time load of my tile of W into tensor memory: row m of the tile goes to TMEM
-    // lane m, its Kc bf16 values packed two per 32-bit column.  The four epilogue
+    // lane m, its Kc bf16 values packed two per 32-bit column.  The four drain
     // warps cover the 128 lanes (warp w may touch lanes [32*(w%4), +32)).
-    if (warp > NUM_MMA_WARPS && warp <= NUM_MMA_WARPS + NUM_EPI_THREADS / 32) {
+    if (warp > NUM_MMA_WARPS && warp <= NUM_MMA_WARPS + NUM_DRAIN_THREADS / 32) {
       const int quarter = warp & 3;
       const int m = quarter * 32 + lane;
       const uint4* src = reinterpret_cast<const uint4*>(p.Wg + (long)(i * TILE_M + m) * p.d +
@@ -472,13 +476,71 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       }
     }
     __syncwarp();
-  } else if (warp <= NUM_MMA_WARPS + NUM_EPI_THREADS / 32) {
-    // =========================== epilogue ===================================
-    const int et = tid - (1 + NUM_MMA_WARPS) * 32;   // 0..127
+  } else if (warp <= NUM_MMA_WARPS + NUM_DRAIN_THREADS / 32) {
+    // ============================ drain ======================================
+    // Reads the finished accumulators out of tensor memory, adds the nmw chains and
+    // scatters each row to the shared memory of the CTA that finalises it.  A role of
+    // its own so that, with several batch groups in flight, the scatter of one group
+    // overlaps the finalising of the previous one.
     const int quarter = warp & 3;            // TMEM lane quarter this warp may read
     const int m = quarter * 32 + lane;       // accumulator row held by this thread
     const int owner = m / rows_own;          // cluster rank that finalises row m
     const int m_local = m - owner * rows_own;
+    const bool tracer = (warp == NUM_MMA_WARPS + 1 && lane == 0);
+    const uint32_t stage_local = ptx::smem_u32(sStage);
+    for (int q = 0; q < total_q; ++q) {
+      const int a = q & 1;
+      const uint32_t aph = (uint32_t)(q >> 1) & 1u;
+      bool good = waiter.wait(&acc_full_bar[a], aph) &&
+                  waiter.wait_cluster(&red_empty_bar[a], aph ^ 1u);
+      good = __all_sync(0xffffffffu, good);
+      if (tracer) stamp(p.trace, q, 4);  // accumulator complete
+      if (!good) {
+        if (abort_flag == 0 && atomicExch(p.abort_word, 1) == 0)
+          report_timeout(p.status, kid, 0xFFFFF2);
+        abort_flag = 1;
+        break;
+      }
+      ptx::tc_fence_after();
+      // staging layout at the owner: [source][batch quad][row][4 batch values];
+      // a warp's 16-byte stores for one quad cover 32 consecutive rows = 512 bytes
+      const uint32_t remote =
+          mapa(stage_local + (uint32_t)((a * S + (int)j) * stg_src_floats + m_local * 4) * 4u,
+               (uint32_t)owner);
+      const uint32_t remote_bar = mapa(ptx::smem_u32(&red_full_bar[a]), (uint32_t)owner);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                             (uint32_t)(a * nmw * Npad);
+      for (int c = 0; c < Npad; c += 16) {
+        // all accumulators of this column chunk in flight at once, one wait
+        uint32_t r[16], rb[16], rc[16], rd[16];
+        ptx::tmem_ld16(taddr + (uint32_t)c, r);
+        if (nmw > 1) ptx::tmem_ld16(taddr + (uint32_t)(Npad + c), rb);
+        if (nmw > 2) ptx::tmem_ld16(taddr + (uint32_t)(2 * Npad + c), rc);
+        if (nmw > 3) ptx::tmem_ld16(taddr + (uint32_t)(3 * Npad + c), rd);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          float acc = __uint_as_float(r[k]);
+          if (nmw > 1) acc += __uint_as_float(rb[k]);
+          if (nmw > 2) acc += __uint_as_float(rc[k]);
+          if (nmw > 3) acc += __uint_as_float(rd[k]);
+          r[k] = __float_as_uint(acc);
+        }
+#pragma unroll
+        for (int k = 0; k < 16; k += 4)
+          if (c + k < Ng)
+            st_async_v4(remote + (uint32_t)(((c + k) >> 2) * rows_own * 4) * 4u, r[k], r[k + 1],
+                        r[k + 2], r[k + 3], remote_bar);
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty_bar[a]);
+      if (tracer) stamp(p.trace, q, 5);  // partials scattered
+    }
+    __syncwarp();
+  } else if (warp <= NUM_MMA_WARPS + (NUM_DRAIN_THREADS + NUM_EPI_THREADS) / 32) {
+    // ============================ finalise ===================================
+    const int et = tid - (1 + NUM_MMA_WARPS) * 32 - NUM_DRAIN_THREADS;   // 0..127
     // finalise mapping: this thread owns the feature pair fp of my chunk for the
     // batch quads qd0, qd0 + nbq, ... (a quad = 4 consecutive batch rows)
     const int pairs = rows_own / 2;
@@ -558,48 +620,9 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       // A failed (timed-out / aborted) wait never skips the named barrier below:
       // the thread marks the CTA aborted, skips the data movement, and everybody
       // leaves the loop together after the barrier.
-      // ---- drain my accumulator row and scatter it to the owning peer ----
-      bool good = in_ok && waiter.wait(&acc_full_bar[a], aph) &&
-                  waiter.wait_cluster(&red_empty_bar[a], aph ^ 1u);
-      good = __all_sync(0xffffffffu, good);
-      if (et == 0) stamp(p.trace, q, 4);  // accumulator complete
+      // ---- owner: add the S partials, fused epilogue, write the new state ----
+      bool good = in_ok;
       if (good) {
-        ptx::tc_fence_after();
-        // staging layout at the owner: [source][batch quad][row][4 batch values];
-        // a warp's 16-byte stores for one quad cover 32 consecutive rows = 512 bytes
-        const uint32_t remote =
-            mapa(stage_local + (uint32_t)((a * S + (int)j) * stg_src_floats + m_local * 4) * 4u,
-                 (uint32_t)owner);
-        const uint32_t remote_bar = mapa(ptx::smem_u32(&red_full_bar[a]), (uint32_t)owner);
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) +
-                               (uint32_t)(a * nmw * Npad);
-        for (int c = 0; c < Npad; c += 16) {
-          // all accumulators of this column chunk in flight at once, one wait
-          uint32_t r[16], rb[16], rc[16], rd[16];
-          ptx::tmem_ld16(taddr + (uint32_t)c, r);
-          if (nmw > 1) ptx::tmem_ld16(taddr + (uint32_t)(Npad + c), rb);
-          if (nmw > 2) ptx::tmem_ld16(taddr + (uint32_t)(2 * Npad + c), rc);
-          if (nmw > 3) ptx::tmem_ld16(taddr + (uint32_t)(3 * Npad + c), rd);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            float acc = __uint_as_float(r[k]);
-            if (nmw > 1) acc += __uint_as_float(rb[k]);
-            if (nmw > 2) acc += __uint_as_float(rc[k]);
-            if (nmw > 3) acc += __uint_as_float(rd[k]);
-            r[k] = __float_as_uint(acc);
-          }
-#pragma unroll
-          for (int k = 0; k < 16; k += 4)
-            if (c + k < Ng)
-              st_async_v4(remote + (uint32_t)(((c + k) >> 2) * rows_own * 4) * 4u, r[k], r[k + 1],
-                          r[k + 2], r[k + 3], remote_bar);
-        }
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&acc_empty_bar[a]);
-        if (et == 0) stamp(p.trace, q, 5);  // partials scattered
-        // ---- owner: add the S partials, fused epilogue, write the new state ----
         good = waiter.wait_cluster(&red_full_bar[a], aph);
         good = __all_sync(0xffffffffu, good);
         if (et == 0) stamp(p.trace, q, 6);  // all partials landed
@@ -799,16 +822,16 @@ struct RecPlan {
   bool ok;
 };
 
-size_t plan_smem(int S, int Kc, int Npad, int nstages, bool w_tmem) {
+size_t plan_smem(int S, int Kc, int Npad, int nstages, bool w_tmem, int nin) {
   size_t w = w_tmem ? 0 : (size_t)TILE_M * Kc * 2;
   size_t st = (size_t)nstages * Npad * Kc * 2;
   size_t stg = (size_t)2 * TILE_M * Npad * 4;
-  size_t in = (size_t)2 * 4 * Npad * (TILE_M / S) * 2;  // epilogue input tiles (backward: 4 arrays)
+  size_t in = (size_t)2 * nin * Npad * (TILE_M / S) * 2;  // epilogue input tiles, double buffered
   return w + st + stg + in + 1024 + 64;
 }
 
 // Full plan for one K split S and one cap on the batch-group size, or ok == false.
-RecPlan plan_for(int B, int d, int S, int ng_cap, bool want_w_tmem) {
+RecPlan plan_for(int B, int d, int S, int ng_cap, bool want_w_tmem, int nin) {
   RecPlan pl{};
   pl.ok = false;
   pl.w_tmem = 0;
@@ -847,11 +870,11 @@ RecPlan plan_for(int B, int d, int S, int ng_cap, bool want_w_tmem) {
   // a single batch group runs strictly step after step: one ring stage is enough
   const int min_stages = G > 1 ? 2 : 1;
   int nstages = G > 1 ? 4 : 2;
-  while (nstages > min_stages && plan_smem(S, Kc, Npad, nstages, w_tmem) > smem_cap) --nstages;
-  if (plan_smem(S, Kc, Npad, nstages, w_tmem) > smem_cap) return pl;
+  while (nstages > min_stages && plan_smem(S, Kc, Npad, nstages, w_tmem, nin) > smem_cap) --nstages;
+  if (plan_smem(S, Kc, Npad, nstages, w_tmem, nin) > smem_cap) return pl;
   pl.S = S; pl.Kc = Kc; pl.G = G; pl.Ng = Ng; pl.Npad = Npad; pl.nstages = nstages;
   pl.nmw = nmw; pl.tmem_cols = cols;
-  pl.smem = plan_smem(S, Kc, Npad, nstages, w_tmem);
+  pl.smem = plan_smem(S, Kc, Npad, nstages, w_tmem, nin);
   pl.ok = true;
   return pl;
 }
@@ -886,42 +909,59 @@ bool plan_is_coresident(const RecPlan& pl, int d) {
 
 // Largest K split first (most CTAs, smallest resident tile); a split whose clusters do
 // not all fit on the device at once is skipped.  Results are cached per shape.
-RecPlan make_plan(int T, int B, int d, int compact) {
+RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
   RecPlan none{};
   none.ok = false;
   if (T < 1 || B < 1 || d < 128 || (d % 128) != 0) return none;
-  struct Key { int B, d, compact; long s, g, w, wt; };
+  struct Key { int B, d, compact; long s, g, w, wt, lb; };  // compact also carries the direction
+  const int nin = bwd ? 4 : 2;  // arrays the epilogue reads per step
+  compact = (compact ? 1 : 0) | (bwd ? 2 : 0);
   struct Entry { Key k; RecPlan pl; };
   static Entry cache[32];
   static int ncache = 0;
   const Key key{B, d, compact, options().rec_ksplit, options().rec_groups, options().rec_mma_warps,
-                options().rec_w_tmem};
+                options().rec_w_tmem, options().rec_large_batch};
   for (int i = 0; i < ncache; ++i) {
     const Key& c = cache[i].k;
     if (c.B == key.B && c.d == key.d && c.compact == key.compact && c.s == key.s &&
-        c.g == key.g && c.w == key.w && c.wt == key.wt)
+        c.g == key.g && c.w == key.w && c.wt == key.wt && c.lb == key.lb)
       return cache[i].pl;
   }
   RecPlan found = none;
   const long want_S = options().rec_ksplit;
-  if (compact) {
+  if (compact & 1) {
     // smallest footprint: the smallest K split whose tile of W fits in shared memory
     // or, failing that, in tensor memory
     for (int S = 1; S <= MAX_S && !found.ok; S <<= 1) {
       if (want_S > 0 && S != want_S) continue;
       for (int wt = 0; wt <= 1 && !found.ok; ++wt) {
-        RecPlan pl = plan_for(B, d, S, 32, wt != 0);
+        RecPlan pl = plan_for(B, d, S, 32, wt != 0, nin);
         if (pl.ok && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d)) found = pl;
       }
     }
-  } else {
+  } else if (B <= 32 || options().rec_groups > 0 || options().rec_large_batch == 0) {
+    // latency plan: the largest K split (shortest per-step chain)
     for (int S = MAX_S; S >= 1 && !found.ok; S >>= 1) {
       if (want_S > 0 && S != want_S) continue;
       for (int ng_cap = 32; ng_cap >= 16 && !found.ok; ng_cap >>= 1) {
-        RecPlan pl = plan_for(B, d, S, ng_cap, options().rec_w_tmem != 0);
+        RecPlan pl = plan_for(B, d, S, ng_cap, options().rec_w_tmem != 0, nin);
         if (pl.ok && plan_is_coresident(pl, d)) found = pl;
       }
     }
+  } else {
+    // throughput plan for batches that need several groups anyway: the widest group
+    // first (fixed per-group costs are paid fewer times per step), the weight tile in
+    // tensor memory when shared memory cannot hold it beside the wider state tiles
+    for (int ng_cap = 64; ng_cap >= 16 && !found.ok; ng_cap >>= 1)
+      for (int S = MAX_S; S >= 1 && !found.ok; S >>= 1) {
+        if (want_S > 0 && S != want_S) continue;
+        for (int wt = 0; wt <= 1 && !found.ok; ++wt) {
+          if (wt == 0 && options().rec_w_tmem != 0) continue;
+          RecPlan pl = plan_for(B, d, S, ng_cap, wt != 0, nin);
+          if (pl.ok && pl.Ng > ng_cap / 2 && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d))
+            found = pl;
+        }
+      }
   }
   if (ncache < 32) cache[ncache++] = Entry{key, found};
   return found;
@@ -982,11 +1022,13 @@ void fill_plan(const RecPlan& pl, RecTcParams& p) {
 
 }  // namespace
 
-bool rec_tc_supported(int T, int B, int d) { return make_plan(T, B, d, 0).ok; }
+bool rec_tc_supported(int T, int B, int d, int bwd) { return make_plan(T, B, d, 0, bwd != 0).ok; }
 
 int rec_tc_blocks(int T, int B, int d, int compact) {
-  RecPlan pl = make_plan(T, B, d, compact);
-  return pl.ok ? (d / TILE_M) * pl.S * pl.G : 0;
+  // batch groups are pipelined through the same blocks, so they do not add any
+  RecPlan f = make_plan(T, B, d, compact, false), b = make_plan(T, B, d, compact, true);
+  if (!f.ok || !b.ok) return 0;
+  return (d / TILE_M) * (f.S > b.S ? f.S : b.S);
 }
 
 size_t rec_tc_sync_bytes() {
@@ -1010,7 +1052,8 @@ int rec_tc_copy_trace(long long* dst, int max_entries) {
 }
 
 int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
-  RecPlan pl = make_plan(a.T, a.B, a.d, a.compact);
+  RecPlan pl = make_plan(a.T, a.B, a.d, a.compact, false);
+  if (!pl.ok && a.compact) pl = make_plan(a.T, a.B, a.d, 0, false);  // no compact plan: the regular one
   if (!pl.ok) return set_error(ELMAN_ERR_UNSUPPORTED, "shape not supported by the tensor-core recurrence");
   RecTcParams p{};
   p.T = a.T; p.B = a.B; p.d = a.d;
@@ -1024,12 +1067,16 @@ int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
   p.Wg = (const bf16*)a.W;
   // option rec_direct_publish: 0 = auto (measured best: forward direct, backward through the
   // publisher warp), 1 = direct in both, 2 = publisher warp in both
-  p.direct_publish = options().rec_direct_publish == 2 ? 0 : 1;
+  // with several batch groups in flight the release's latency only stalls the epilogue
+  // warps, which are the busiest role: hand it to the publisher warp then
+  p.direct_publish = options().rec_direct_publish == 2 ? 0
+                     : options().rec_direct_publish == 1 ? 1 : (pl.G == 1 ? 1 : 0);
   return launch_rec_tc<false>(pl, p, a.W, a.h, stream);
 }
 
 int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream) {
-  RecPlan pl = make_plan(a.T, a.B, a.d, a.compact);
+  RecPlan pl = make_plan(a.T, a.B, a.d, a.compact, true);
+  if (!pl.ok && a.compact) pl = make_plan(a.T, a.B, a.d, 0, true);  // no compact plan: the regular one
   if (!pl.ok) return set_error(ELMAN_ERR_UNSUPPORTED, "shape not supported by the tensor-core recurrence");
   RecTcParams p{};
   p.T = a.T; p.B = a.B; p.d = a.d;

@@ -71,6 +71,9 @@ int elman_b200_device_status(int* detail, int clear);
  *                    modes give bit-identical results.
  *   "rec_w_tmem"     1 = keep the recurrent weight tile in tensor memory instead
  *                    of shared memory (A operand read from TMEM); bit-identical
+ *   "rec_large_batch" 1 (default) = batches over 32 rows take the throughput plan of
+ *                    the tensor-core recurrence (widest batch group first), 0 = the
+ *                    latency plan for every batch size
  * Returns ELMAN_OK or ELMAN_ERR_ARG for an unknown name.
  */
 int elman_b200_set_option(const char* name, long value);
