@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_cuda"],
                     help="ours | reference (the reference's CPU path) | reference_cuda (the "
                          "reference's own CUDA kernels rebuilt for sm_100, if oracle/_ref exists)")
-    ap.add_argument("--workload", default="cell", choices=["cell", "lm", "e5"],
+    ap.add_argument("--workload", default="cell", choices=["cell", "lm", "e5", "c4"],
                     help="cell = configs[1] (the headline line); lm = configs[2] training step; "
                          "e5 = configs[3] low-rank cell")
     ap.add_argument("--pipeline-chunks", type=int, default=8,
@@ -92,18 +92,55 @@ def read_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs: an
+    NVML polling thread (read-only queries, every 20 ms) started before the warm-up, with
+    the timed region marked by begin()/end() so only samples taken inside it count.  Falls
+    back to an `nvidia-smi -lms` child process when NVML cannot be loaded."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
         self.proc = None
         self.path = None
+        self.thread = None
+        self.samples = []      # (time, sm_mhz, reasons bitmask)
+        self.windows = []
+        self.max_mhz = None
+        self._stop = False
+
+    def _nvml_loop(self, nv, handle):
+        while not self._stop:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append((time.perf_counter(), float(mhz), int(mask)))
+            except Exception:
+                pass
+            time.sleep(0.02)
 
     def start(self):
+        try:
+            import pynvml as nv
+            import threading
+            nv.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(self.gpu).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            handle = nv.nvmlDeviceGetHandleByUUID(uuid)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -115,7 +152,28 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def begin(self):
+        self._t0 = time.perf_counter()
+
+    def end(self):
+        self.windows.append((self._t0, time.perf_counter()))
+
     def stop(self):
+        if self.thread is not None:
+            self._stop = True
+            self.thread.join(timeout=2)
+            inside = [s for s in self.samples if any(a <= s[0] <= b for a, b in self.windows)]
+            where = "timed regions"
+            if not inside:  # a timed region shorter than one polling interval
+                inside, where = self.samples, "warm-up and timed regions"
+            reasons = set()
+            for _, _, mask in inside:
+                for bit, nm in self.REASONS.items():
+                    if mask & bit:
+                        reasons.add(nm)
+            return {"sm_mhz": statistics.median([s[1] for s in inside]) if inside else None,
+                    "sm_max_mhz": self.max_mhz, "samples": len(inside), "sampled": where,
+                    "source": "nvml", "reasons": sorted(reasons)}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -141,6 +199,7 @@ class ClockSampler:
         os.unlink(self.path)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "sampled": "warm-up and timed regions", "source": "nvidia-smi",
                 "reasons": sorted(reasons)}
 
 
@@ -298,6 +357,60 @@ def run_e5(args, rank, world, local_rank):
             "device_status": _lib.device_status()[0]}), flush=True)
 
 
+def run_c4(args, rank, world, local_rank):
+    """configs[4]: E1 forward only (inference), bf16, d=2048, B=256, T=2048: the large-batch
+    shape, where the recurrence pipelines several batch groups through each resident tile of
+    W_h.  x, z ~ N(0,1)/2, W_x Xavier-scaled, W_h at spectral radius about 0.5.
+    `--impl reference_cuda` runs the reference's forward kernels on the same inputs."""
+    from elman_b200 import _lib
+    from elman_b200 import hasty_pytorch_lib as H
+    Td, Bd, d = 2048, 256, 2048
+    torch.cuda.set_device(local_rank)
+    g = torch.Generator().manual_seed(1239 + rank)
+    x = torch.empty(Td, Bd, d, dtype=torch.bfloat16, device="cuda")
+    z = torch.empty(Td, Bd, d, dtype=torch.bfloat16, device="cuda")
+    for t0 in range(0, Td, 256):  # generated in slices: the fp32 host copy stays small
+        x[t0:t0 + 256] = (torch.randn(256, Bd, d, generator=g) * 0.5).to(torch.bfloat16).cuda()
+        z[t0:t0 + 256] = (torch.randn(256, Bd, d, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    W_x = (torch.randn(d, d, generator=g) / math.sqrt(d)).to(torch.bfloat16).cuda()
+    W_h = (torch.randn(d, d, generator=g) * 0.5 / math.sqrt(d)).to(torch.bfloat16).cuda()
+    b = torch.zeros(d, dtype=torch.bfloat16, device="cuda")
+    h0 = torch.zeros(Bd, d, dtype=torch.bfloat16, device="cuda")
+    if args.impl == "reference_cuda":
+        from oracle import ref_cuda
+        if not ref_cuda.available():
+            if rank == 0:
+                print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref not built"}))
+            return
+
+        def step():
+            return ref_cuda.e1_forward(False, x, z, h0, W_x, W_h, b)
+    else:
+        def step():
+            return H.mamba_gated_elman_forward(False, x, z, h0, W_x, W_h, b)
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    torch.cuda.synchronize()
+    del out
+    launches0 = _lib.launch_count()
+    total = 0.0
+    for _ in range(args.steps):  # 4.3 GB of inputs per pass: far beyond L2, no flush needed
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(); out = step(); s1.record(); s1.synchronize()
+        del out
+        total += s0.elapsed_time(s1)
+    if rank == 0:
+        print(json.dumps({
+            "impl": args.impl, "metric": "E1 forward tokens/s @ d2048 B256 T2048",
+            "value": Bd * Td * args.steps / (total / 1e3), "unit": UNIT, "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total / args.steps,
+            "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[4]: E1 cell forward (inference), bf16, d=2048, B=256, "
+                                   "T=2048; inputs larger than L2"},
+            "gpu_launches": _lib.launch_count() - launches0,
+            "device_status": _lib.device_status()[0]}), flush=True)
+
+
 def run_lm(args, rank, world, local_rank):
     """configs[2]: full E1 byte-level LM (d=1280 x 6 layers, 49.5M parameters), bf16, AdamW,
     T=512, 32 sequences per GPU, seeded Zipf(1.1) token ids; one step = forward, loss,
@@ -352,17 +465,23 @@ def run_lm(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
     launches0 = _lib.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.begin()
     ev0.record()
     for _ in range(args.steps):
         loss = step()
     ev1.record()
     loss_val = float(loss.detach())  # device -> host read of the step's result
     barrier()
+    sampler.end()
+    clocks = sampler.stop() if rank == 0 else None
     ms = ev0.elapsed_time(ev1)
     t_all = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -379,7 +498,7 @@ def run_lm(args, rank, world, local_rank):
                                    "Zipf(1.1) tokens, DDP" + (" (NCCL)" if world > 1 else ""),
                        "params": model.get_num_params(),
                        "pipeline_chunks": chunks, "cuda_graph": bool(graphed)},
-            "final_loss": loss_val,
+            "final_loss": loss_val, "clocks": clocks,
             "gpu_launches": (gstep.library_launches_per_step * args.steps if graphed
                              else _lib.launch_count() - launches0)}), flush=True)
     if world > 1:
@@ -398,6 +517,10 @@ def main():
         return
     if args.workload == "e5":
         run_e5(args, rank, world, local_rank)
+        return
+    if args.workload == "c4":
+        if rank == 0:
+            run_c4(args, rank, world, local_rank)
         return
     if args.impl == "reference":
         run_reference(args, rank)
@@ -469,27 +592,31 @@ def main():
         total_ms = sum(s.elapsed_time(e) for s, e in ev)
         return total_ms, wall, phase_ms
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step_device()
     torch.cuda.synchronize()
     if _lib.device_status()[0] != 0:
         raise SystemExit("a device-side wait timed out during warm-up: " + str(_lib.device_status()))
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     _lib.set_option("time_kernels", 1)
     launches0, tc0 = _lib.launch_count(), _lib.tc_launch_count()
+    sampler.begin()
     total_ms, wall, phase_ms = timed(step_device, args.steps, phases=True)
+    sampler.end()
     launches = _lib.launch_count() - launches0
     tc_launches = _lib.tc_launch_count() - tc0
     _lib.set_option("time_kernels", 0)
-    clocks = sampler.stop() if rank == 0 else None
 
     for _ in range(3):
         step_e2e()
     torch.cuda.synchronize()
+    sampler.begin()
     e2e_ms, _, _ = timed(step_e2e, args.steps)
+    sampler.end()
+    clocks = sampler.stop() if rank == 0 else None
     if _lib.device_status()[0] != 0:
         raise SystemExit("a device-side wait timed out: " + str(_lib.device_status()))
 
