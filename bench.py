@@ -58,8 +58,9 @@ def parse_args():
                          "over CUDA streams; 0 or 1 = layers one after another as the reference")
     ap.add_argument("--pipeline-streams", type=int, default=0, help="0 = from the SM count")
     ap.add_argument("--cuda-graph", type=int, default=-1,
-                    help="lm workload, our arm: 1 = capture the training step into a CUDA graph; "
-                         "-1 = on for one GPU, off under DDP")
+                    help="lm workload, our arm: capture the training step (with the gradient "
+                         "all-reduce for N > 1) into a CUDA graph (default); 0 = eager step, "
+                         "DistributedDataParallel for N > 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=128,
                     help="time steps of the workload the CPU baseline runs")
@@ -422,6 +423,7 @@ def run_lm(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")  # required to capture NCCL
         dist.init_process_group(backend="nccl", device_id=dev)
     if args.impl == "reference_cuda":
         from oracle import ref_cuda
@@ -436,17 +438,22 @@ def run_lm(args, rank, world, local_rank):
                                pipeline_chunks=chunks, pipeline_streams=args.pipeline_streams)
     model = model.to(dev).bfloat16()
     net = model
-    if world > 1:
+    graphed = args.impl == "ours" and args.cuda_graph != 0
+    if world > 1 and not graphed:
         net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank],
                                                         find_unused_parameters=False)
-    graphed = args.impl == "ours" and (args.cuda_graph == 1 or (args.cuda_graph < 0 and world == 1))
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
                             capturable=graphed)
     host_tokens = ladder_lm.zipf_tokens(B, T + 1, seed=1234 + rank).pin_memory()
     if graphed:
         from elman_b200.train_step import GraphedTrainStep
+        from elman_b200.train_step import allreduce_gradients
+        if world > 1:  # same initial weights on every rank; gradients averaged inside the graph
+            for p_ in model.parameters():
+                dist.broadcast(p_.data, src=0)
         gstep = GraphedTrainStep(net, opt, host_tokens.to(dev), max_grad_norm=1.0,
-                                 autocast_dtype=torch.bfloat16)
+                                 autocast_dtype=torch.bfloat16,
+                                 after_backward=allreduce_gradients if world > 1 else None)
 
     def step():
         if graphed:
@@ -495,15 +502,40 @@ def run_lm(args, rank, world, local_rank):
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "configs[2]: LadderLM level 1, d=1280, depth 6, AdamW, "
-                                   "Zipf(1.1) tokens, DDP" + (" (NCCL)" if world > 1 else ""),
+                                   "Zipf(1.1) tokens, data parallel" +
+                                   ("" if world == 1 else
+                                    " (NCCL gradient all-reduce inside the step graph)" if graphed
+                                    else " (DistributedDataParallel over NCCL)"),
                        "params": model.get_num_params(),
                        "pipeline_chunks": chunks, "cuda_graph": bool(graphed)},
             "final_loss": loss_val, "clocks": clocks,
             "gpu_launches": (gstep.library_launches_per_step * args.steps if graphed
                              else _lib.launch_count() - launches0)}), flush=True)
     if world > 1:
+        if graphed:
+            # NCCL cannot tear a communicator down while a CUDA graph that captured its
+            # kernels is alive: release the graph first, and never let teardown hang the run
+            gstep.graph = None
+            gstep = None
+            import gc
+            gc.collect()
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        _destroy_process_group_bounded(20.0)
+
+
+def _destroy_process_group_bounded(seconds):
+    """destroy_process_group in a helper thread; if it has not returned in time the process
+    exits directly (all results are printed by then)."""
+    import threading
+    import torch.distributed as dist
+    t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+    t.start()
+    t.join(seconds)
+    if t.is_alive():
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():

@@ -15,8 +15,11 @@ import torch
 
 class GraphedTrainStep:
     def __init__(self, net, optimizer, example_tokens, max_grad_norm=1.0, autocast_dtype=None,
-                 warmup_steps=3):
+                 warmup_steps=3, after_backward=None):
+        """`after_backward(params)`, if given, runs between backward and clipping, inside
+        the captured step: the place for a data-parallel gradient all-reduce."""
         self.net, self.opt = net, optimizer
+        self.after_backward = after_backward
         self.max_grad_norm = max_grad_norm
         self.autocast_dtype = autocast_dtype
         self.tokens = example_tokens.clone()
@@ -46,6 +49,8 @@ class GraphedTrainStep:
         else:
             loss = self.net(self.tokens, return_loss=True)
         loss.backward()
+        if self.after_backward is not None:
+            self.after_backward(self.params)
         if self.max_grad_norm:
             torch.nn.utils.clip_grad_norm_(self.params, self.max_grad_norm)
         self.opt.step()
@@ -57,3 +62,20 @@ class GraphedTrainStep:
         self.tokens.copy_(tokens, non_blocking=True)
         self.graph.replay()
         return self.loss
+
+
+def allreduce_gradients(params, group=None):
+    """Mean of the gradients over the ranks of `group` with one NCCL all-reduce over a
+    flat buffer (capturable: no host synchronisation, fixed shapes)."""
+    import torch.distributed as dist
+    grads = [p.grad for p in params if p.grad is not None]
+    if not grads:
+        return
+    flat = torch.cat([g.reshape(-1) for g in grads])
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+    flat.div_(dist.get_world_size(group))
+    offset = 0
+    for g in grads:
+        n = g.numel()
+        g.copy_(flat[offset:offset + n].view_as(g))
+        offset += n
