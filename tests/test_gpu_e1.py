@@ -203,3 +203,30 @@ def test_weights_in_tensor_memory_variant_is_bit_identical():
         b, _ = run_e1(inp, torch.bfloat16)
     for k in FWD_BWD_KEYS:
         assert torch.equal(a[k], b[k]), k
+
+
+def test_host_pipeline_delivers_the_device_results():
+    """E1HostPipeline (pinned host buffers in and out, three overlapping streams) returns bit
+    for bit what the device-tensor functions return, for several calls in flight."""
+    from elman_b200.host_io import E1HostPipeline
+    T, B, d = 24, 32, 256
+    calls = []
+    for k in range(5):
+        inp = orc.make_e1_inputs(T, B, d, seed=300 + k)
+        calls.append({n: v.to(torch.bfloat16).contiguous().pin_memory() for n, v in inp.items()})
+    w = {n: calls[0][n].cuda() for n in ("W_x", "W_h", "b", "h0")}
+    pipe = E1HostPipeline(T, B, d, w["W_x"], w["W_h"], w["b"], w["h0"], depth=2)
+    got = []
+    for c in calls:
+        res = pipe.submit(c["x"], c["z"], c["d_output"])
+        res["done"].synchronize()          # results of a slot are reused two calls later
+        got.append({n: res[n].clone() for n in ("output", "dx", "dz", "dW_x", "dW_h", "db")})
+    pipe.wait()
+    for c, g in zip(calls, got):
+        x, z, r = (c[n].cuda() for n in ("x", "z", "d_output"))
+        h, out, v = H.mamba_gated_elman_forward(True, x, z, w["h0"], w["W_x"], w["W_h"], w["b"])
+        dx, dz, dWx, dWh, db = H.mamba_gated_elman_backward(w["W_x"], w["W_h"], x, z, h, v, r)
+        for n, t in (("output", out), ("dx", dx), ("dz", dz), ("dW_x", dWx), ("dW_h", dWh), ("db", db)):
+            assert torch.equal(g[n], t.cpu()), n
+    with pytest.raises(RuntimeError, match="pinned"):
+        pipe.submit(calls[0]["x"].cuda(), calls[0]["z"], calls[0]["d_output"])

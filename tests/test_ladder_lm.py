@@ -94,3 +94,38 @@ def test_data_parallel_step_on_two_gloo_ranks_averages_shard_gradients(tmp_path,
             ref[k] = ref.get(k, 0) + p.grad / 2
     for k in ref:
         assert orc.rel_err(got[k], ref[k]) < 1e-5, k
+
+
+def _allreduce_worker(rank, world, port, out):
+    import torch.distributed as dist
+    from elman_b200.train_step import allreduce_gradients
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank,
+                            world_size=world)
+    a = torch.nn.Parameter(torch.zeros(3, 2))
+    b = torch.nn.Parameter(torch.zeros(5))
+    c = torch.nn.Parameter(torch.zeros(2))          # never gets a gradient
+    a.grad = torch.full((3, 2), float(rank + 1))
+    b.grad = torch.arange(5.0) * (rank + 1)
+    allreduce_gradients([a, b, c])
+    out.put((rank, a.grad.clone(), b.grad.clone(), c.grad is None))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_allreduce_gradients_averages_over_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29650 + os.getpid() % 200
+    procs = [ctx.Process(target=_allreduce_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=120) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ga, gb, none_c in got:
+        assert torch.allclose(ga, torch.full((3, 2), 1.5))
+        assert torch.allclose(gb, torch.arange(5.0) * 1.5)
+        assert none_c
