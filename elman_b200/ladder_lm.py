@@ -72,8 +72,10 @@ class LadderLM(nn.Module):
         h = self.embedding(inp)
         if prev_hiddens is None:
             prev_hiddens = [None] * self.depth
+        time_major = False
         if self._can_pipeline(h):
             h, residual, new_hiddens = self._pipelined_layers(h, prev_hiddens)
+            time_major = True
         else:
             new_hiddens = []
             residual = None
@@ -85,6 +87,9 @@ class LadderLM(nn.Module):
                 h, h_final = layer(h, prev_hiddens[i])
                 new_hiddens.append(h_final)
         h = self.norm((h + residual).to(dtype=self.norm.weight.dtype))
+        if time_major and (not return_loss or self.loss_chunk_size > 0):
+            h = h.transpose(0, 1).contiguous()   # back to [B,T,D] for the callers below
+            time_major = False
         if not return_loss:
             logits = self.lm_head(h)
             return (logits, (new_hiddens, None)) if return_prev_hiddens else logits
@@ -92,6 +97,10 @@ class LadderLM(nn.Module):
             positions = torch.arange(target.size(1), device=h.device).unsqueeze(0)
             target = target.clone()
             target[~(positions < (actual_length.unsqueeze(1) - 1))] = -100
+        if time_major:
+            # the mean over tokens does not care about their order: transpose the small
+            # integer targets instead of the activations
+            target = target.transpose(0, 1)
         T_total = h.size(1)
         if self.loss_chunk_size > 0 and T_total > self.loss_chunk_size:
             total, count = h.new_zeros(()), 0
@@ -153,11 +162,12 @@ class LadderLM(nn.Module):
         main = torch.cuda.current_stream(h.device)
         streams = self._pipeline_streams(h.device, self._stream_count(h, edges[1] - edges[0]))
         shared = [layer.chunk_weights() for layer in self.layers]
-        start = torch.cuda.Event()
+        # time-major chunks [Tc,B,D]: the cell's own layout, so no layer transposes anything
+        h_chunks = [h[:, edges[c]:edges[c + 1]].transpose(0, 1).contiguous() for c in range(C)]
+        start = torch.cuda.Event()   # everything the side streams read is enqueued before this
         start.record(main)
         for s in streams:
             s.wait_event(start)
-        h_chunks = [h[:, edges[c]:edges[c + 1]] for c in range(C)]
         res_chunks = [None] * C
         states = []
         done = [[None] * C for _ in range(self.depth)]
@@ -181,7 +191,8 @@ class LadderLM(nn.Module):
                     hn = ln(residual.to(dtype=ln.weight.dtype))
                     if self.residual_in_fp32:
                         residual = residual.to(torch.float32)
-                    out, state = layer.forward_chunk(hn, state, shared[i], self.pipeline_flags)
+                    out, state = layer.forward_chunk(hn, state, shared[i], self.pipeline_flags,
+                                                     time_major=True)
                     h_chunks[c], res_chunks[c] = out, residual
                     done[i][c] = torch.cuda.Event()
                     done[i][c].record(s)
@@ -196,8 +207,8 @@ class LadderLM(nn.Module):
             joined = torch.cuda.Event()
             joined.record(s)
             main.wait_event(joined)
-        return (torch.cat(h_chunks, dim=1), torch.cat(res_chunks, dim=1),
-                [st.detach() for st in states])
+        # both still time-major [T,B,D]
+        return torch.cat(h_chunks, dim=0), torch.cat(res_chunks, dim=0), [st.detach() for st in states]
 
     def get_num_params(self):
         return sum(p.numel() for p in self.parameters())

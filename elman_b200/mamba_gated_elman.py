@@ -176,18 +176,22 @@ class MambaGatedElman(nn.Module):
         (the spectral-norm power iteration advances once per pass, as in forward())."""
         return self.cell.get_W_h().contiguous()
 
-    def forward_chunk(self, x, h0, W_h, flags=0):
-        """x: [B,Tc,dim], h0: [B,d_inner] (last state of the preceding chunk) ->
-        (output [B,Tc,dim], h_last).  Chained over the chunks of a sequence this equals
-        forward() on the whole sequence."""
+    def forward_chunk(self, x, h0, W_h, flags=0, time_major=False):
+        """x: [B,Tc,dim] ([Tc,B,dim] with time_major), h0: [B,d_inner] (last state of the
+        preceding chunk) -> (output in the layout of x, h_last).  Chained over the chunks of
+        a sequence this equals forward() on the whole sequence.  Time-major callers skip the
+        three layout copies around the cell: every other op of the layer is per token."""
         x_proj, z = self.in_proj(x).chunk(2, dim=-1)
-        x_rnn = F.silu(x_proj).permute(1, 0, 2).contiguous()
-        z_rnn = z.permute(1, 0, 2).contiguous()
+        if time_major:
+            x_rnn, z_rnn = F.silu(x_proj).contiguous(), z.contiguous()
+        else:
+            x_rnn = F.silu(x_proj).permute(1, 0, 2).contiguous()
+            z_rnn = z.permute(1, 0, 2).contiguous()
         cell = self.cell
         cell_out, h_last = MambaGatedElmanChunkFunction.apply(
             x_rnn, z_rnn, h0.contiguous(), cell.W_x.contiguous(), W_h, cell.b.contiguous(), flags)
-        y = self.dropout(cell_out.permute(1, 0, 2).contiguous())
-        return self.out_proj(y), h_last
+        y = cell_out if time_major else cell_out.permute(1, 0, 2).contiguous()
+        return self.out_proj(self.dropout(y)), h_last
 
     def extra_repr(self):
         return f"dim={self.dim}, d_inner={self.d_inner}, use_conv={self.use_conv}, LEVEL=1_MAMBA_GATED"
