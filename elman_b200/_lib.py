@@ -45,6 +45,12 @@ SIGNATURES = {
     "elman_e1_forward_flags": (_I, [_I, _I, _I, _I, _I, _I] + [_P] * 6 + [_P] * 3 + [_P, _Z, _P]),
     "elman_e1_backward_carry": (_I, [_I, _I, _I, _I, _I] + [_P] * 8 + [_P] * 6 + [_P, _Z, _P]),
     "elman_b200_recurrence_blocks": (_I, [_I, _I, _I, _I, _I]),
+    "elman_gemm": (_I, [_I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
+    "elman_column_sum_workspace": (_Z, [_I]),
+    "elman_column_sum": (_I, [_I, _L, _I, _P, _P, _P, _Z, _P]),
+    "elman_e1_recurrence_workspace": (_Z, [_I, _I]),
+    "elman_e1_recurrence_forward": (_I, [_I] * 6 + [_P] * 4 + [_P] * 3 + [_P, _Z, _P]),
+    "elman_e1_recurrence_backward": (_I, [_I] * 5 + [_P] * 6 + [_P] * 3 + [_P, _Z, _P]),
     "elman_e0_forward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e0_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 7 + [_P] * 4 + [_P, _Z, _P]),
     "elman_e0_backward_workspace": (_Z, [_I, _I, _I, _I]),

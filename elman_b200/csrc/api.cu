@@ -823,4 +823,114 @@ int elman_projection(int dtype, int M, int N, int K, const void* A, int lda, con
   return proj_nt(dtype, M, N, K, A, lda, W, ldw, bias, C, ldc, accumulate, (cudaStream_t)stream);
 }
 
+// ------------------- the phases of an E1 call, one by one --------------------
+
+int elman_gemm(int dtype, int op, int M, int N, int K, const void* A, const void* B,
+               const void* bias, void* C, int accumulate, void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(M >= 0 && N >= 0 && K >= 0, "negative size");
+  ELMAN_ARG_CHECK(op == ELMAN_GEMM_NT || op == ELMAN_GEMM_NN || op == ELMAN_GEMM_TN,
+                  "unknown GEMM form %d", op);
+  ELMAN_ARG_CHECK(bias == nullptr || op == ELMAN_GEMM_NT, "bias only with ELMAN_GEMM_NT");
+  ELMAN_ARG_CHECK(!accumulate || op != ELMAN_GEMM_TN, "ELMAN_GEMM_TN overwrites C");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (M == 0 || N == 0) return ELMAN_OK;
+  REQUIRE_PTR(C);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (K == 0) {
+    if (!accumulate)
+      ELMAN_CUDA_CHECK(cudaMemsetAsync(C, 0, (size_t)M * N * esize(dtype), st));
+    return ELMAN_OK;
+  }
+  REQUIRE_PTR(A); REQUIRE_PTR(B);
+  if (op == ELMAN_GEMM_NT) return proj_nt(dtype, M, N, K, A, K, B, K, bias, C, N, accumulate, st);
+  if (op == ELMAN_GEMM_NN) return gemm_nn(dtype, M, N, K, A, K, B, N, nullptr, C, N, accumulate, st);
+  return gemm_tn(dtype, M, N, K, A, B, nullptr, false, nullptr, false, C, st);
+}
+
+size_t elman_column_sum_workspace(int N) { return column_sum_scratch_bytes(N < 0 ? 0 : N); }
+
+int elman_column_sum(int dtype, long M, int N, const void* in, void* out, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(M >= 0 && N >= 0, "negative size");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (N == 0) return ELMAN_OK;
+  REQUIRE_PTR(out); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(M == 0 || in != nullptr, "argument in is NULL");
+  if (workspace_bytes < column_sum_scratch_bytes(N))
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes,
+                     column_sum_scratch_bytes(N));
+  return column_sum(dtype, M, N, in, out, (float*)workspace, (cudaStream_t)stream);
+}
+
+struct E1RecWs { void* Wt; float* db; int* sync; };
+static size_t carve_e1_rec(int dtype, int d, void* ws, E1RecWs* o) {
+  Carver c(ws);
+  o->Wt = c.take((size_t)d * d * esize(dtype));
+  o->db = (float*)c.take((size_t)d * sizeof(float));
+  size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
+  o->sync = (int*)c.take(sb);
+  return c.total();
+}
+
+size_t elman_e1_recurrence_workspace(int dtype, int d) {
+  E1RecWs w;
+  return carve_e1_rec(dtype, d < 0 ? 0 : d, nullptr, &w);
+}
+
+int elman_e1_recurrence_forward(int dtype, int flags, int training, int T, int B, int d,
+                                const void* pre, const void* z, const void* h0, const void* W_h,
+                                void* h, void* output, void* v, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  ELMAN_ARG_CHECK((flags & ~ELMAN_FLAG_COMPACT) == 0, "unknown flags 0x%x", flags);
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (B == 0 || d == 0) return ELMAN_OK;
+  REQUIRE_PTR(h0); REQUIRE_PTR(h);
+  cudaStream_t st = (cudaStream_t)stream;
+  ELMAN_RETURN_IF(copy_rows(dtype, h0, h, (long)B * d, st));
+  if (T == 0) return ELMAN_OK;
+  REQUIRE_PTR(pre); REQUIRE_PTR(z); REQUIRE_PTR(W_h); REQUIRE_PTR(output); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(!training || v != nullptr, "v must be provided when training");
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E1RecWs w;
+  size_t need = carve_e1_rec(dtype, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  return run_rec_fwd(dtype, T, B, d, W_h, pre, z, h, output, training ? v : nullptr, w.sync, st,
+                     (flags & ELMAN_FLAG_COMPACT) ? 1 : 0);
+}
+
+int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d, const void* W_h,
+                                 const void* z, const void* h, const void* v,
+                                 const void* d_output, const void* dv_in, void* dv, void* dz,
+                                 void* db, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+  ELMAN_ARG_CHECK((flags & ~ELMAN_FLAG_COMPACT) == 0, "unknown flags 0x%x", flags);
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (d == 0 || B == 0) return ELMAN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  REQUIRE_PTR(dv); REQUIRE_PTR(db);
+  const size_t es = esize(dtype);
+  if (T == 0) {  // no steps: the carried gradient passes through, nothing adds to the bias
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    if (dv_in != nullptr)
+      ELMAN_CUDA_CHECK(cudaMemcpyAsync(dv, dv_in, (size_t)B * d * es, cudaMemcpyDeviceToDevice, st));
+    else
+      ELMAN_CUDA_CHECK(cudaMemsetAsync(dv, 0, (size_t)B * d * es, st));
+    return ELMAN_OK;
+  }
+  REQUIRE_PTR(W_h); REQUIRE_PTR(z); REQUIRE_PTR(h); REQUIRE_PTR(v); REQUIRE_PTR(d_output);
+  REQUIRE_PTR(dz); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E1RecWs w;
+  size_t need = carve_e1_rec(dtype, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
+  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, z, d_output, dv, dz, w.db, w.sync, dv_in,
+                              st, (flags & ELMAN_FLAG_COMPACT) ? 1 : 0));
+  return float_to_dtype(dtype, w.db, db, d, st);
+}
+
 }  // extern "C"

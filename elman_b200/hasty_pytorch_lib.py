@@ -158,6 +158,110 @@ def recurrence_blocks(dtype, T, B, d, flags=0):
                                                         int(d)))
 
 
+# ------------------------------------------- the phases of an E1 call, one by one
+# (extensions of the C ABI: elman_gemm, elman_column_sum, elman_e1_recurrence_*)
+
+GEMM_NT, GEMM_NN, GEMM_TN = 0, 1, 2
+
+
+def gemm(op, A, B, bias=None, out=None, accumulate=False):
+    """Dense row-major GEMM through elman_gemm:
+    GEMM_NT out[M,N] = A[M,K] B[N,K]^T (+bias), GEMM_NN A[M,K] B[K,N], GEMM_TN A[K,M]^T B[K,N]."""
+    fn = "gemm"
+    tensors = dict(A=A, B=B)
+    if bias is not None:
+        tensors["bias"] = bias
+    dt = _check_inputs(fn, A, **tensors)
+    if A.dim() != 2 or B.dim() != 2:
+        raise RuntimeError(f"{fn}: A and B must be matrices")
+    if op == GEMM_NT:
+        (M, K), (N, K2) = A.shape, B.shape
+    elif op == GEMM_NN:
+        (M, K), (K2, N) = A.shape, B.shape
+    elif op == GEMM_TN:
+        (K, M), (K2, N) = A.shape, B.shape
+    else:
+        raise RuntimeError(f"{fn}: unknown form {op}")
+    if K != K2:
+        raise RuntimeError(f"{fn}: inner extents differ ({K} vs {K2})")
+    if out is None:
+        out = torch.empty(M, N, dtype=A.dtype, device=A.device)
+        accumulate = False
+    else:
+        _shape(fn, out, (M, N), "out")
+    with torch.cuda.device(A.device):
+        rc = _lib.load().elman_gemm(dt, op, M, N, K, _ptr(A), _ptr(B), _ptr(bias), _ptr(out),
+                                    1 if accumulate else 0, _stream(A.device))
+        _lib.check(rc, fn)
+    return out
+
+
+def column_sum(x):
+    """out[N] = sum over the rows of x[M,N] (deterministic) through elman_column_sum."""
+    fn = "column_sum"
+    dt = _check_inputs(fn, x, x=x)
+    M, N = x.shape
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        out = torch.empty(N, dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_column_sum_workspace(N), x.device)
+        rc = lib.elman_column_sum(dt, M, N, _ptr(x), _ptr(out), ws.data_ptr(), ws.numel(),
+                                  _stream(x.device))
+        _lib.check(rc, fn)
+    return out
+
+
+def e1_recurrence_forward(training, pre, z, h0, W_h, flags=0):
+    """The recurrence of the E1 cell alone, on already projected inputs pre = W_x x + b:
+    -> [h[T+1,B,d], output[T,B,d], v[T,B,d] (empty if not training)]."""
+    fn = "e1_recurrence_forward"
+    dt = _check_inputs(fn, pre, pre=pre, z=z, h0=h0, W_h=W_h)
+    if pre.dim() != 3:
+        raise RuntimeError(f"{fn}: pre must be [T, B, dim]")
+    T, B, d = pre.shape
+    _shape(fn, z, (T, B, d), "z"); _shape(fn, h0, (B, d), "h0"); _shape(fn, W_h, (d, d), "W_h")
+    lib = _lib.load()
+    with torch.cuda.device(pre.device):
+        h = torch.empty(T + 1, B, d, dtype=pre.dtype, device=pre.device)
+        out = torch.empty(T, B, d, dtype=pre.dtype, device=pre.device)
+        v = torch.empty((T, B, d) if training else (0,), dtype=pre.dtype, device=pre.device)
+        ws = _workspace(lib.elman_e1_recurrence_workspace(dt, d), pre.device)
+        rc = lib.elman_e1_recurrence_forward(dt, int(flags), 1 if training else 0, T, B, d,
+                                             _ptr(pre), _ptr(z), _ptr(h0), _ptr(W_h), _ptr(h),
+                                             _ptr(out), _ptr(v), ws.data_ptr(), ws.numel(),
+                                             _stream(pre.device))
+        _lib.check(rc, fn)
+    return [h, out, v]
+
+
+def e1_recurrence_backward(W_h, z, h, v, d_output, dv_in=None, flags=0):
+    """BPTT of the recurrence alone -> [dv[T+1,B,d], dz[T,B,d], db[d]].  dv[:T] is the
+    gradient of `pre`; dv[0] is what the preceding time chunk takes as its dv_in; slot T
+    holds a copy of this call's dv_in (zeros if None)."""
+    fn = "e1_recurrence_backward"
+    tensors = dict(W_h=W_h, z=z, h=h, v=v, d_output=d_output)
+    if dv_in is not None:
+        tensors["dv_in"] = dv_in
+    dt = _check_inputs(fn, z, **tensors)
+    T, B, d = z.shape
+    _shape(fn, h, (T + 1, B, d), "h"); _shape(fn, v, (T, B, d), "v")
+    _shape(fn, d_output, (T, B, d), "d_output"); _shape(fn, W_h, (d, d), "W_h")
+    if dv_in is not None:
+        _shape(fn, dv_in, (B, d), "dv_in")
+    lib = _lib.load()
+    with torch.cuda.device(z.device):
+        dv = torch.empty(T + 1, B, d, dtype=z.dtype, device=z.device)
+        dz = torch.empty_like(z)
+        db = torch.empty(d, dtype=z.dtype, device=z.device)
+        ws = _workspace(lib.elman_e1_recurrence_workspace(dt, d), z.device)
+        rc = lib.elman_e1_recurrence_backward(dt, int(flags), T, B, d, _ptr(W_h), _ptr(z), _ptr(h),
+                                              _ptr(v), _ptr(d_output), _ptr(dv_in), _ptr(dv),
+                                              _ptr(dz), _ptr(db), ws.data_ptr(), ws.numel(),
+                                              _stream(z.device))
+        _lib.check(rc, fn)
+    return [dv, dz, db]
+
+
 # --------------------------------------------------------------------------- E0
 
 def stock_elman_forward(training, x, h0, W_x, W_h, W_gate, b, b_gate):

@@ -122,9 +122,10 @@ class LadderLM(nn.Module):
     # fraction of the GPU's SMs busy, and layer l+1 at time t needs layer l only
     # up to time t.  Cutting the sequence into C time chunks turns the depth x C
     # (layer, chunk) units into a wavefront: unit (l, c) needs (l-1, c) for its
-    # input and (l, c-1) for its initial state.  Layers are dealt round-robin to a
-    # few CUDA streams, so up to that many recurrences (and the projections, norms
-    # and copies around them) run side by side.  Autograd runs every backward op on
+    # input and (l, c-1) for its initial state.  Each layer's recurrences run back to
+    # back on a stream of their own while the time-parallel ops before and after them
+    # (norms, projections, weight-gradient GEMMs) run on two further streams per layer,
+    # so up to `depth` recurrences overlap each other and everything else.  Autograd runs every backward op on
     # the stream of its forward op, so the backward pass forms the mirrored
     # wavefront by itself.  Chained chunks reproduce the unchunked layer exactly
     # (state carried forward, pre-activation gradient carried backward).
@@ -133,16 +134,19 @@ class LadderLM(nn.Module):
         return (self.pipeline_chunks > 1 and h.is_cuda and h.size(1) >= 2 * self.pipeline_chunks
                 and all(getattr(layer, "supports_time_chunks", False) for layer in self.layers))
 
-    def _pipeline_streams(self, device, n):
-        key = (device, n)
+    def _pipeline_streams(self, device, n_rec):
+        """Per layer one stream for the ops before the recurrence and one for those after it;
+        `n_rec` streams for the recurrences themselves, dealt to the layers round-robin."""
+        key = (device, n_rec)
         if key not in self._streams:
-            self._streams[key] = [torch.cuda.Stream(device=device) for _ in range(n)]
+            mk = lambda n: [torch.cuda.Stream(device=device) for _ in range(n)]
+            self._streams[key] = (mk(self.depth), mk(n_rec), mk(self.depth))
         return self._streams[key]
 
-    def _stream_count(self, h, chunk_len):
-        """Streams = recurrences that may run at once.  The thread blocks of one
-        recurrence launch wait for one another, so all launches that can be in
-        flight together must fit on the device at the same time."""
+    def _recurrence_stream_count(self, h, chunk_len):
+        """Recurrence launches that may be in flight at once.  The thread blocks of one
+        launch wait for one another, so every set of launches that can run together must
+        fit on the device together: one stream per layer while that holds."""
         if self.pipeline_streams > 0:
             return self.pipeline_streams
         from . import hasty_pytorch_lib
@@ -151,62 +155,86 @@ class LadderLM(nn.Module):
         blocks = hasty_pytorch_lib.recurrence_blocks(h.dtype, chunk_len, h.size(0), d_inner,
                                                      self.pipeline_flags)
         sms = torch.cuda.get_device_properties(h.device).multi_processor_count
-        # one stream per layer while all their recurrences fit on the device together
         n = sms // blocks if blocks > 0 else 2
         return max(1, min(n, self.depth))
 
     def _pipelined_layers(self, h, prev_hiddens):
+        from .mamba_gated_elman import ChunkLink
         B, T, _ = h.shape
         C = self.pipeline_chunks
         edges = [(T * c) // C for c in range(C + 1)]
         main = torch.cuda.current_stream(h.device)
-        streams = self._pipeline_streams(h.device, self._stream_count(h, edges[1] - edges[0]))
+        pre_streams, rec_streams, post_streams = self._pipeline_streams(
+            h.device, self._recurrence_stream_count(h, edges[1] - edges[0]))
         shared = [layer.chunk_weights() for layer in self.layers]
         # time-major chunks [Tc,B,D]: the cell's own layout, so no layer transposes anything
         h_chunks = [h[:, edges[c]:edges[c + 1]].transpose(0, 1).contiguous() for c in range(C)]
         start = torch.cuda.Event()   # everything the side streams read is enqueued before this
         start.record(main)
-        for s in streams:
+        for s in pre_streams + rec_streams + post_streams:
             s.wait_event(start)
         res_chunks = [None] * C
         states = []
-        done = [[None] * C for _ in range(self.depth)]
+        post_done = [[None] * C for _ in range(self.depth)]
+
+        def record(stream):
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            return ev
+
         for i, (ln, layer) in enumerate(zip(self.layer_norms, self.layers)):
-            s = streams[i % len(streams)]
+            sp, sr, sq = pre_streams[i], rec_streams[i % len(rec_streams)], post_streams[i]
             d_inner = getattr(layer, "d_inner", self.dim)
             state = prev_hiddens[i]
             state = (torch.zeros(B, d_inner, device=h.device, dtype=h.dtype) if state is None
                      else state.detach())
-            state.record_stream(s)
-            shared[i].record_stream(s)
-            with torch.cuda.stream(s):
-                for c in range(C):
+            state.record_stream(sr)
+            shared[i].record_stream(sr)
+
+            def issue_pre(c):
+                # residual add, norm, input projections: everything up to the recurrence
+                with torch.cuda.stream(sp):
                     if i > 0:
-                        s.wait_event(done[i - 1][c])
+                        sp.wait_event(post_done[i - 1][c])
                     hin, rin = h_chunks[c], res_chunks[c]
-                    hin.record_stream(s)
+                    hin.record_stream(sp)
                     if rin is not None:
-                        rin.record_stream(s)
+                        rin.record_stream(sp)
                     residual = (hin + rin) if rin is not None else hin
                     hn = ln(residual.to(dtype=ln.weight.dtype))
                     if self.residual_in_fp32:
                         residual = residual.to(torch.float32)
-                    out, state = layer.forward_chunk(hn, state, shared[i], self.pipeline_flags,
-                                                     time_major=True)
-                    h_chunks[c], res_chunks[c] = out, residual
-                    done[i][c] = torch.cuda.Event()
-                    done[i][c].record(s)
+                    link = ChunkLink()
+                    pre, z = layer.chunk_pre(hn, shared[i], link)
+                    return pre, z, link, residual, record(sp)
+
+            ahead = issue_pre(0)
+            for c in range(C):
+                pre, z, link, residual, pre_ev = ahead
+                with torch.cuda.stream(sr):
+                    sr.wait_event(pre_ev)
+                    pre.record_stream(sr)
+                    z.record_stream(sr)
+                    cell_out, state = layer.chunk_rec(pre, z, state, shared[i], link,
+                                                      self.pipeline_flags)
+                    rec_ev = record(sr)
+                if c + 1 < C:   # enqueued before this chunk's post ops: the next recurrence
+                    ahead = issue_pre(c + 1)    # of this layer never waits behind them
+                with torch.cuda.stream(sq):
+                    sq.wait_event(rec_ev)
+                    cell_out.record_stream(sq)
+                    out = layer.chunk_post(cell_out)
+                    post_done[i][c] = record(sq)
+                h_chunks[c], res_chunks[c] = out, residual
             states.append(state)
         for c in range(C):
-            main.wait_event(done[-1][c])
+            main.wait_event(post_done[-1][c])
             h_chunks[c].record_stream(main)
             res_chunks[c].record_stream(main)
         for st in states:
             st.record_stream(main)
-        for s in streams:  # every stream rejoins the caller's (required under graph capture)
-            joined = torch.cuda.Event()
-            joined.record(s)
-            main.wait_event(joined)
+        for s in pre_streams + rec_streams + post_streams:
+            main.wait_event(record(s))   # every stream rejoins (required under graph capture)
         # both still time-major [T,B,D]
         return torch.cat(h_chunks, dim=0), torch.cat(res_chunks, dim=0), [st.detach() for st in states]
 

@@ -73,6 +73,89 @@ class MambaGatedElmanChunkFunction(torch.autograd.Function):
         return dx, dz, dv_out, dW_x, dW_h, db, None
 
 
+class ChunkLink:
+    """Carries the hidden states (and the bias gradient) of one chunk from its recurrence
+    node to its projection node, whose backward pass needs them for dW_h."""
+    __slots__ = ("h", "db")
+
+    def __init__(self):
+        self.h = None
+        self.db = None
+
+
+class E1ChunkProjectionFunction(torch.autograd.Function):
+    """The time-parallel half of one chunk: forward(x, W_x, b, W_h, link) -> pre = x W_x^T + b.
+
+    Its backward receives d(pre), which is the pre-activation gradient dv of the chunk's
+    recurrence, and computes every GEMM of the cell's backward pass from it: dx = dv W_x,
+    dW_x = dv^T x and — with the hidden states the recurrence node left in `link` —
+    dW_h = dv^T h[0:T].  W_h is an input only so that this node can return that gradient;
+    the forward pass does not read it.  Split from E1ChunkRecurrenceFunction so that the two
+    halves can run on different CUDA streams (no counterpart in the reference).
+    """
+
+    @staticmethod
+    def forward(ctx, x, W_x, b, W_h, link):
+        T, B, d = x.shape
+        pre = hasty_pytorch_lib.gemm(hasty_pytorch_lib.GEMM_NT, x.view(T * B, d), W_x, b)
+        ctx.save_for_backward(x, W_x)
+        ctx.link = link
+        return pre.view(T, B, d)
+
+    @staticmethod
+    def backward(ctx, dpre):
+        x, W_x = ctx.saved_tensors
+        T, B, d = x.shape
+        link, ctx.link = ctx.link, None
+        here = torch.cuda.current_stream(x.device) if x.is_cuda else None
+        dv = dpre.contiguous().view(T * B, d)
+        h, db = link.h, link.db
+        if here is not None:   # produced on the recurrence's stream, read on this one
+            for t in (dpre, h, db):
+                t.record_stream(here)
+        G = hasty_pytorch_lib
+        dx = G.gemm(G.GEMM_NN, dv, W_x).view(T, B, d)
+        dW_x = G.gemm(G.GEMM_TN, dv, x.view(T * B, d))
+        dW_h = G.gemm(G.GEMM_TN, dv, h[:T].view(T * B, d))
+        link.h = link.db = None
+        return dx, dW_x, db, dW_h, None
+
+
+class E1ChunkRecurrenceFunction(torch.autograd.Function):
+    """The sequential half of one chunk: forward(pre, z, h0, W_h, link, flags) ->
+    (output [T,B,d], h_last [B,d]).  The h_last -> next chunk's h0 edge carries the
+    pre-activation gradient backward, exactly as in MambaGatedElmanChunkFunction; the
+    gradient of W_h is produced by the projection node."""
+
+    @staticmethod
+    def forward(ctx, pre, z, h0, W_h, link, flags=0):
+        h, output, v = hasty_pytorch_lib.e1_recurrence_forward(True, pre, z, h0, W_h, flags)
+        link.h = h
+        ctx.link = link
+        ctx.save_for_backward(W_h, z, h, v)
+        ctx.set_materialize_grads(False)
+        ctx.flags = flags
+        return output, h[-1].clone()
+
+    @staticmethod
+    def backward(ctx, d_output, dv_in):
+        W_h, z, h, v = ctx.saved_tensors
+        T = z.shape[0]
+        if d_output is None:
+            d_output = torch.zeros_like(z)
+        if z.is_cuda:
+            here = torch.cuda.current_stream(z.device)
+            d_output.record_stream(here)
+            if dv_in is not None:
+                dv_in.record_stream(here)
+        dv, dz, db = hasty_pytorch_lib.e1_recurrence_backward(
+            W_h, z, h, v, d_output.contiguous(), None if dv_in is None else dv_in.contiguous(),
+            ctx.flags)
+        ctx.link.db = db
+        ctx.link = None
+        return dv[:T], dz, dv[0], None, None, None
+
+
 class MambaGatedElmanCell(nn.Module):
     """Weights of the recurrence and the dispatch into the CUDA library."""
 
@@ -192,6 +275,22 @@ class MambaGatedElman(nn.Module):
             x_rnn, z_rnn, h0.contiguous(), cell.W_x.contiguous(), W_h, cell.b.contiguous(), flags)
         y = cell_out if time_major else cell_out.permute(1, 0, 2).contiguous()
         return self.out_proj(self.dropout(y)), h_last
+
+    # The same chunk in three pieces, for callers that put them on different streams:
+    # chunk_pre (time-parallel, up to the projected inputs), chunk_rec (the recurrence
+    # alone) and chunk_post (output projection).  All time-major [Tc,B,*].
+    def chunk_pre(self, x, W_h, link):
+        x_proj, z = self.in_proj(x).chunk(2, dim=-1)
+        cell = self.cell
+        pre = E1ChunkProjectionFunction.apply(F.silu(x_proj).contiguous(), cell.W_x.contiguous(),
+                                              cell.b.contiguous(), W_h, link)
+        return pre, z.contiguous()
+
+    def chunk_rec(self, pre, z, h0, W_h, link, flags=0):
+        return E1ChunkRecurrenceFunction.apply(pre, z, h0.contiguous(), W_h, link, flags)
+
+    def chunk_post(self, cell_out):
+        return self.out_proj(self.dropout(cell_out))
 
     def extra_repr(self):
         return f"dim={self.dim}, d_inner={self.d_inner}, use_conv={self.use_conv}, LEVEL=1_MAMBA_GATED"

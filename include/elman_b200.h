@@ -291,6 +291,50 @@ int elman_projection(int dtype, int M, int N, int K,
                      const void* A, int lda, const void* W, int ldw,
                      const void* bias, void* C, int ldc, int accumulate, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * The phases of an E1 call as separate entry points (an extension; the reference
+ * only has the whole-call functions above).  elman_e1_forward is
+ *   elman_gemm(NT: pre = x W_x^T + b)  ->  elman_e1_recurrence_forward
+ * and elman_e1_backward(_carry) is
+ *   elman_e1_recurrence_backward  ->  elman_gemm(NN: dx = dv W_x),
+ *   elman_gemm(TN: dW_x = dv^T x), elman_gemm(TN: dW_h = dv^T h[0:T]).
+ * A caller that overlaps work on several streams can keep the latency-bound
+ * recurrence launches back to back on one stream and run the time-parallel GEMMs
+ * of other chunks or layers beside them on another.
+ *
+ * elman_gemm: dense row-major operands, C[M,N] overwritten unless accumulate.
+ *   ELMAN_GEMM_NT  C = A[M,K] B[N,K]^T (+ bias[N])     (blas<T>::gemm call sites of the
+ *   ELMAN_GEMM_NN  C = A[M,K] B[K,N]                     reference: elman/cuda/lib/
+ *   ELMAN_GEMM_TN  C = A[K,M]^T B[K,N]                   mamba_gated_elman_gpu.cu.cc:440-448,
+ *                                                        :560-592)
+ * elman_column_sum: out[N] = sum over the M rows of in[M,N], deterministic (the bias
+ *   gradient; the reference accumulates it with float atomics, :318-322).
+ * elman_e1_recurrence_forward: h_t = tanh(pre_t + W_h h_{t-1}), y_t = h_t silu(z_t);
+ *   pre,z,output,v : [T,B,d], h : [T+1,B,d], h0 : [B,d].
+ * elman_e1_recurrence_backward: dv : [T+1,B,d] — slots 0..T-1 receive the gradient of
+ *   pre (= of the pre-activations), slot T is scratch for the carried-in gradient;
+ *   dv_in as for elman_e1_backward_carry (dv[0:1] of this call is the next dv_in);
+ *   dz : [T,B,d]; db : [d] = sum over t,b of dv.
+ * ------------------------------------------------------------------------- */
+#define ELMAN_GEMM_NT 0
+#define ELMAN_GEMM_NN 1
+#define ELMAN_GEMM_TN 2
+int elman_gemm(int dtype, int op, int M, int N, int K, const void* A, const void* B,
+               const void* bias, void* C, int accumulate, void* stream);
+size_t elman_column_sum_workspace(int N);
+int elman_column_sum(int dtype, long M, int N, const void* in, void* out,
+                     void* workspace, size_t workspace_bytes, void* stream);
+size_t elman_e1_recurrence_workspace(int dtype, int d);
+int elman_e1_recurrence_forward(int dtype, int flags, int training, int T, int B, int d,
+                                const void* pre, const void* z, const void* h0, const void* W_h,
+                                void* h, void* output, void* v,
+                                void* workspace, size_t workspace_bytes, void* stream);
+int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d,
+                                 const void* W_h, const void* z, const void* h, const void* v,
+                                 const void* d_output, const void* dv_in,
+                                 void* dv, void* dz, void* db,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

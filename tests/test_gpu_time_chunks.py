@@ -170,3 +170,33 @@ def test_graphed_train_step_matches_eager_steps():
     graphed = [step(tok).item() for tok in batches]
     for a, b in zip(eager[3:], graphed):
         assert abs(a - b) < 3e-2 * abs(a), (eager, graphed)
+
+
+@pytest.mark.parametrize("dtype,T,B,d", [(torch.float32, 7, 3, 40), (torch.bfloat16, 16, 32, 256),
+                                         (torch.bfloat16, 9, 5, 72)])
+def test_phase_entry_points_compose_to_the_whole_call(dtype, T, B, d):
+    """elman_gemm + elman_e1_recurrence_forward/backward + elman_column_sum, chained by
+    hand, give bit for bit what elman_e1_forward / elman_e1_backward give."""
+    inp = orc.make_e1_inputs(T, B, d, seed=41)
+    dev, ref = round_inputs(inp, dtype)
+    whole, _ = run_e1(inp, dtype)
+    x2 = dev["x"].view(T * B, d)
+    pre = H.gemm(H.GEMM_NT, x2, dev["W_x"], dev["b"]).view(T, B, d)
+    h, out, v = H.e1_recurrence_forward(True, pre, dev["z"], dev["h0"], dev["W_h"])
+    dv, dz, db = H.e1_recurrence_backward(dev["W_h"], dev["z"], h, v, dev["d_output"])
+    dv2 = dv[:T].view(T * B, d)
+    got = {"h": h, "output": out, "v": v, "dz": dz, "db": db,
+           "dx": H.gemm(H.GEMM_NN, dv2, dev["W_x"]).view(T, B, d),
+           "dW_x": H.gemm(H.GEMM_TN, dv2, x2),
+           "dW_h": H.gemm(H.GEMM_TN, dv2, h[:T].view(T * B, d))}
+    torch.cuda.synchronize()
+    for k, t in got.items():
+        assert torch.equal(t, whole[k]), k
+    assert_close(errors(got, oracle_e1(ref)), TOL[dtype], "phases vs oracle")
+    cs = H.column_sum(dv2)
+    assert orc.rel_err(cs.float().cpu(), whole["db"].float().cpu()) < TOL[dtype]
+    # accumulate and the carried gradient
+    acc = H.gemm(H.GEMM_NN, dv2, dev["W_x"], out=got["dx"].view(T * B, d).clone(), accumulate=True)
+    assert orc.rel_err(acc.float().cpu(), 2 * got["dx"].view(T * B, d).float().cpu()) < 1e-2
+    with pytest.raises(Exception):
+        H.gemm(7, dv2, dev["W_x"])

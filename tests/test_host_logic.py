@@ -36,6 +36,31 @@ class OracleBackend:
         g = orc.e1_backward(W_x, W_h, x, z, h, v, d_output, dv_in)
         return [g["dx"], g["dz"], g["dW_x"], g["dW_h"], g["db"], g["dv0"]]
 
+    GEMM_NT, GEMM_NN, GEMM_TN = 0, 1, 2
+
+    @staticmethod
+    def gemm(op, A, B, bias=None, out=None, accumulate=False):
+        r = {0: lambda: A @ B.T, 1: lambda: A @ B, 2: lambda: A.T @ B}[op]()
+        return r if bias is None else r + bias
+
+    @staticmethod
+    def column_sum(x):
+        return x.sum(0)
+
+    @staticmethod
+    def e1_recurrence_forward(training, pre, z, h0, W_h, flags=0):
+        d = pre.shape[-1]   # the recurrence alone = the cell with W_x = I, b = 0
+        o = orc.e1_forward(pre, z, h0, torch.eye(d, dtype=pre.dtype), W_h, torch.zeros(d, dtype=pre.dtype))
+        return [o["h"], o["output"], o["v"] if training else pre.new_empty(0)]
+
+    @staticmethod
+    def e1_recurrence_backward(W_h, z, h, v, d_output, dv_in=None, flags=0):
+        T, B, d = z.shape
+        g = orc.e1_backward(torch.eye(d, dtype=z.dtype), W_h, torch.zeros_like(z), z, h, v,
+                            d_output, dv_in)
+        carry = torch.zeros(1, B, d, dtype=z.dtype) if dv_in is None else dv_in[None]
+        return [torch.cat([g["dx"], carry]), g["dz"], g["db"]]
+
     @staticmethod
     def stock_elman_forward(training, x, h0, W_x, W_h, W_gate, b, b_gate):
         o = orc.e0_forward(x, h0, W_x, W_h, W_gate, b, b_gate)
@@ -199,3 +224,35 @@ def test_e1_layer_in_time_chunks_equals_reference_fixture(golden_dir, oracle_bac
             assert orc.rel_err(got[k], vref) < 2e-5, k
             checked += 1
     assert checked >= 4
+
+
+@pytest.mark.parametrize("cuts", [(0, 3, 5), (0,)])
+def test_e1_layer_split_chunk_pieces_equal_reference_fixture(golden_dir, oracle_backend, cuts):
+    """chunk_pre / chunk_rec / chunk_post (time-major, the projection node returning dW_h
+    from the states the recurrence node leaves in the link) reproduce the reference layer."""
+    inp, want = load(golden_dir, "e1_layer")
+    dim = inp["x"].shape[-1]
+    layer = e1mod.MambaGatedElman(dim, expansion=1.0)
+    layer.load_state_dict({k[2:]: v for k, v in inp.items() if k.startswith("p_")})
+    x = inp["x"].clone().requires_grad_(True)
+    B, T, _ = x.shape
+    edges = list(cuts) + [T]
+    W_h = layer.chunk_weights()
+    state = torch.zeros(B, layer.d_inner)
+    outs = []
+    for t0, t1 in zip(edges[:-1], edges[1:]):
+        link = e1mod.ChunkLink()
+        pre, z = layer.chunk_pre(x[:, t0:t1].transpose(0, 1).contiguous(), W_h, link)
+        cell_out, state = layer.chunk_rec(pre, z, state, W_h, link)
+        outs.append(layer.chunk_post(cell_out).transpose(0, 1))
+    out = torch.cat(outs, dim=1)
+    (out * inp["d_output"]).sum().backward()
+    got = {"output": out, "h_final": state, "dx": x.grad}
+    for n, p_ in layer.named_parameters():
+        got["g_" + n] = p_.grad
+    checked = 0
+    for k, vref in want.items():
+        if k in got:
+            assert orc.rel_err(got[k], vref) < 2e-5, k
+            checked += 1
+    assert checked >= 7
