@@ -50,7 +50,7 @@ SIGNATURES = {
     "elman_column_sum": (_I, [_I, _L, _I, _P, _P, _P, _Z, _P]),
     "elman_e1_recurrence_workspace": (_Z, [_I, _I]),
     "elman_e1_recurrence_forward": (_I, [_I] * 6 + [_P] * 4 + [_P] * 3 + [_P, _Z, _P]),
-    "elman_e1_recurrence_backward": (_I, [_I] * 5 + [_P] * 6 + [_P] * 3 + [_P, _Z, _P]),
+    "elman_e1_recurrence_backward": (_I, [_I] * 5 + [_P] * 7 + [_P] * 3 + [_P, _Z, _P]),
     "elman_e0_forward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e0_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 7 + [_P] * 4 + [_P, _Z, _P]),
     "elman_e0_backward_workspace": (_Z, [_I, _I, _I, _I]),

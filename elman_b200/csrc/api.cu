@@ -903,9 +903,9 @@ int elman_e1_recurrence_forward(int dtype, int flags, int training, int T, int B
 
 int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d, const void* W_h,
                                  const void* z, const void* h, const void* v,
-                                 const void* d_output, const void* dv_in, void* dv, void* dz,
-                                 void* db, void* workspace, size_t workspace_bytes,
-                                 void* stream) {
+                                 const void* d_output, const void* dv_in, const void* W_h_T,
+                                 void* dv, void* dz, void* db, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
   ELMAN_ARG_CHECK((flags & ~ELMAN_FLAG_COMPACT) == 0, "unknown flags 0x%x", flags);
   ELMAN_RETURN_IF(check_common(dtype, T, B, d));
   if (d == 0 || B == 0) return ELMAN_OK;
@@ -920,15 +920,20 @@ int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d, cons
       ELMAN_CUDA_CHECK(cudaMemsetAsync(dv, 0, (size_t)B * d * es, st));
     return ELMAN_OK;
   }
-  REQUIRE_PTR(W_h); REQUIRE_PTR(z); REQUIRE_PTR(h); REQUIRE_PTR(v); REQUIRE_PTR(d_output);
+  ELMAN_ARG_CHECK(W_h != nullptr || W_h_T != nullptr, "W_h and W_h_T are both NULL");
+  REQUIRE_PTR(z); REQUIRE_PTR(h); REQUIRE_PTR(v); REQUIRE_PTR(d_output);
   REQUIRE_PTR(dz); REQUIRE_PTR(workspace);
   ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
   E1RecWs w;
   size_t need = carve_e1_rec(dtype, d, workspace, &w);
   if (workspace_bytes < need)
     return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
-  ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
-  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, z, d_output, dv, dz, w.db, w.sync, dv_in,
+  const void* Wt = W_h_T;
+  if (Wt == nullptr) {
+    ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
+    Wt = w.Wt;
+  }
+  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, Wt, h, v, z, d_output, dv, dz, w.db, w.sync, dv_in,
                               st, (flags & ELMAN_FLAG_COMPACT) ? 1 : 0));
   return float_to_dtype(dtype, w.db, db, d, st);
 }

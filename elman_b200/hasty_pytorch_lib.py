@@ -234,7 +234,7 @@ def e1_recurrence_forward(training, pre, z, h0, W_h, flags=0):
     return [h, out, v]
 
 
-def e1_recurrence_backward(W_h, z, h, v, d_output, dv_in=None, flags=0):
+def e1_recurrence_backward(W_h, z, h, v, d_output, dv_in=None, flags=0, W_h_T=None):
     """BPTT of the recurrence alone -> [dv[T+1,B,d], dz[T,B,d], db[d]].  dv[:T] is the
     gradient of `pre`; dv[0] is what the preceding time chunk takes as its dv_in; slot T
     holds a copy of this call's dv_in (zeros if None)."""
@@ -248,6 +248,9 @@ def e1_recurrence_backward(W_h, z, h, v, d_output, dv_in=None, flags=0):
     _shape(fn, d_output, (T, B, d), "d_output"); _shape(fn, W_h, (d, d), "W_h")
     if dv_in is not None:
         _shape(fn, dv_in, (B, d), "dv_in")
+    if W_h_T is not None:
+        _check_inputs(fn, z, W_h_T=W_h_T)
+        _shape(fn, W_h_T, (d, d), "W_h_T")
     lib = _lib.load()
     with torch.cuda.device(z.device):
         dv = torch.empty(T + 1, B, d, dtype=z.dtype, device=z.device)
@@ -255,7 +258,8 @@ def e1_recurrence_backward(W_h, z, h, v, d_output, dv_in=None, flags=0):
         db = torch.empty(d, dtype=z.dtype, device=z.device)
         ws = _workspace(lib.elman_e1_recurrence_workspace(dt, d), z.device)
         rc = lib.elman_e1_recurrence_backward(dt, int(flags), T, B, d, _ptr(W_h), _ptr(z), _ptr(h),
-                                              _ptr(v), _ptr(d_output), _ptr(dv_in), _ptr(dv),
+                                              _ptr(v), _ptr(d_output), _ptr(dv_in), _ptr(W_h_T),
+                                              _ptr(dv),
                                               _ptr(dz), _ptr(db), ws.data_ptr(), ws.numel(),
                                               _stream(z.device))
         _lib.check(rc, fn)

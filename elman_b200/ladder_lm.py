@@ -167,6 +167,9 @@ class LadderLM(nn.Module):
         pre_streams, rec_streams, post_streams = self._pipeline_streams(
             h.device, self._recurrence_stream_count(h, edges[1] - edges[0]))
         shared = [layer.chunk_weights() for layer in self.layers]
+        # one transposed copy per layer and pass for the backward recurrences of all chunks
+        shared_t = [w.detach().t().contiguous() if torch.is_grad_enabled() else None
+                    for w in shared]
         # time-major chunks [Tc,B,D]: the cell's own layout, so no layer transposes anything
         h_chunks = [h[:, edges[c]:edges[c + 1]].transpose(0, 1).contiguous() for c in range(C)]
         start = torch.cuda.Event()   # everything the side streams read is enqueued before this
@@ -190,6 +193,8 @@ class LadderLM(nn.Module):
                      else state.detach())
             state.record_stream(sr)
             shared[i].record_stream(sr)
+            if shared_t[i] is not None:
+                shared_t[i].record_stream(sr)
 
             def issue_pre(c):
                 # residual add, norm, input projections: everything up to the recurrence
@@ -216,7 +221,7 @@ class LadderLM(nn.Module):
                     pre.record_stream(sr)
                     z.record_stream(sr)
                     cell_out, state = layer.chunk_rec(pre, z, state, shared[i], link,
-                                                      self.pipeline_flags)
+                                                      self.pipeline_flags, shared_t[i])
                     rec_ev = record(sr)
                 if c + 1 < C:   # enqueued before this chunk's post ops: the next recurrence
                     ahead = issue_pre(c + 1)    # of this layer never waits behind them

@@ -128,10 +128,11 @@ class E1ChunkRecurrenceFunction(torch.autograd.Function):
     gradient of W_h is produced by the projection node."""
 
     @staticmethod
-    def forward(ctx, pre, z, h0, W_h, link, flags=0):
+    def forward(ctx, pre, z, h0, W_h, link, flags=0, W_h_T=None):
         h, output, v = hasty_pytorch_lib.e1_recurrence_forward(True, pre, z, h0, W_h, flags)
         link.h = h
         ctx.link = link
+        ctx.W_h_T = W_h_T    # optional transposed copy shared by all chunks of a pass
         ctx.save_for_backward(W_h, z, h, v)
         ctx.set_materialize_grads(False)
         ctx.flags = flags
@@ -150,10 +151,10 @@ class E1ChunkRecurrenceFunction(torch.autograd.Function):
                 dv_in.record_stream(here)
         dv, dz, db = hasty_pytorch_lib.e1_recurrence_backward(
             W_h, z, h, v, d_output.contiguous(), None if dv_in is None else dv_in.contiguous(),
-            ctx.flags)
+            ctx.flags, ctx.W_h_T)
         ctx.link.db = db
-        ctx.link = None
-        return dv[:T], dz, dv[0], None, None, None
+        ctx.link = ctx.W_h_T = None
+        return dv[:T], dz, dv[0], None, None, None, None
 
 
 class MambaGatedElmanCell(nn.Module):
@@ -286,8 +287,8 @@ class MambaGatedElman(nn.Module):
                                               cell.b.contiguous(), W_h, link)
         return pre, z.contiguous()
 
-    def chunk_rec(self, pre, z, h0, W_h, link, flags=0):
-        return E1ChunkRecurrenceFunction.apply(pre, z, h0.contiguous(), W_h, link, flags)
+    def chunk_rec(self, pre, z, h0, W_h, link, flags=0, W_h_T=None):
+        return E1ChunkRecurrenceFunction.apply(pre, z, h0.contiguous(), W_h, link, flags, W_h_T)
 
     def chunk_post(self, cell_out):
         return self.out_proj(self.dropout(cell_out))

@@ -314,7 +314,9 @@ int elman_projection(int dtype, int M, int N, int K,
  * elman_e1_recurrence_backward: dv : [T+1,B,d] — slots 0..T-1 receive the gradient of
  *   pre (= of the pre-activations), slot T is scratch for the carried-in gradient;
  *   dv_in as for elman_e1_backward_carry (dv[0:1] of this call is the next dv_in);
- *   dz : [T,B,d]; db : [d] = sum over t,b of dv.
+ *   dz : [T,B,d]; db : [d] = sum over t,b of dv.  W_h_T, if not NULL, is W_h transposed
+ *   ([in,out], dense): a caller that runs many chunks with the same weights passes it to
+ *   save the transpose each call would otherwise do (W_h may then be NULL).
  * ------------------------------------------------------------------------- */
 #define ELMAN_GEMM_NT 0
 #define ELMAN_GEMM_NN 1
@@ -331,7 +333,7 @@ int elman_e1_recurrence_forward(int dtype, int flags, int training, int T, int B
                                 void* workspace, size_t workspace_bytes, void* stream);
 int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d,
                                  const void* W_h, const void* z, const void* h, const void* v,
-                                 const void* d_output, const void* dv_in,
+                                 const void* d_output, const void* dv_in, const void* W_h_T,
                                  void* dv, void* dz, void* db,
                                  void* workspace, size_t workspace_bytes, void* stream);
 

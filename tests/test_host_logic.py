@@ -54,7 +54,7 @@ class OracleBackend:
         return [o["h"], o["output"], o["v"] if training else pre.new_empty(0)]
 
     @staticmethod
-    def e1_recurrence_backward(W_h, z, h, v, d_output, dv_in=None, flags=0):
+    def e1_recurrence_backward(W_h, z, h, v, d_output, dv_in=None, flags=0, W_h_T=None):
         T, B, d = z.shape
         g = orc.e1_backward(torch.eye(d, dtype=z.dtype), W_h, torch.zeros_like(z), z, h, v,
                             d_output, dv_in)
