@@ -61,6 +61,8 @@ def parse_args():
                     help="lm workload, our arm: capture the training step (with the gradient "
                          "all-reduce for N > 1) into a CUDA graph (default); 0 = eager step, "
                          "DistributedDataParallel for N > 1")
+    ap.add_argument("--time-steps", type=int, default=0,
+                    help="c4 workload: sequence length instead of 2048 (small captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-steps", type=int, default=128,
                     help="time steps of the workload the CPU baseline runs")
@@ -365,14 +367,15 @@ def run_c4(args, rank, world, local_rank):
     `--impl reference_cuda` runs the reference's forward kernels on the same inputs."""
     from elman_b200 import _lib
     from elman_b200 import hasty_pytorch_lib as H
-    Td, Bd, d = 2048, 256, 2048
+    Td, Bd, d = (args.time_steps if args.time_steps > 0 else 2048), 256, 2048
     torch.cuda.set_device(local_rank)
     g = torch.Generator().manual_seed(1239 + rank)
     x = torch.empty(Td, Bd, d, dtype=torch.bfloat16, device="cuda")
     z = torch.empty(Td, Bd, d, dtype=torch.bfloat16, device="cuda")
     for t0 in range(0, Td, 256):  # generated in slices: the fp32 host copy stays small
-        x[t0:t0 + 256] = (torch.randn(256, Bd, d, generator=g) * 0.5).to(torch.bfloat16).cuda()
-        z[t0:t0 + 256] = (torch.randn(256, Bd, d, generator=g) * 0.5).to(torch.bfloat16).cuda()
+        n = min(256, Td - t0)
+        x[t0:t0 + n] = (torch.randn(n, Bd, d, generator=g) * 0.5).to(torch.bfloat16).cuda()
+        z[t0:t0 + n] = (torch.randn(n, Bd, d, generator=g) * 0.5).to(torch.bfloat16).cuda()
     W_x = (torch.randn(d, d, generator=g) / math.sqrt(d)).to(torch.bfloat16).cuda()
     W_h = (torch.randn(d, d, generator=g) * 0.5 / math.sqrt(d)).to(torch.bfloat16).cuda()
     b = torch.zeros(d, dtype=torch.bfloat16, device="cuda")
@@ -407,7 +410,7 @@ def run_c4(args, rank, world, local_rank):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total / args.steps,
             "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "configs[4]: E1 cell forward (inference), bf16, d=2048, B=256, "
-                                   "T=2048; inputs larger than L2"},
+                                   f"T={Td}; inputs larger than L2"},
             "gpu_launches": _lib.launch_count() - launches0,
             "device_status": _lib.device_status()[0]}), flush=True)
 
