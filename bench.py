@@ -39,7 +39,7 @@ T, B, D = 512, 32, 1280
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes per launch of the dominant kernel from the committed ncu capture
 # (profiles/), or None while no capture of the current kernel exists.
-NCU_TRAFFIC_BYTES = {"rec_tc_kernel<fwd>": 170.6e6, "rec_tc_kernel<bwd>": 232.3e6}  # profiles/rec_tc_kernel_e1_c1.md
+NCU_TRAFFIC_BYTES = {"rec_tc_kernel<fwd>": 170.1e6, "rec_tc_kernel<bwd>": 231.1e6}  # profiles/rec_tc_kernel_e1_c1.md
 
 
 def parse_args():

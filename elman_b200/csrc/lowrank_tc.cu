@@ -25,6 +25,7 @@
 //
 // All waits are bounded; named barriers are only ever reached by all of their threads
 // (a reducing barrier carries the stop decision).  No TMA multicast.
+#include <mutex>
 #include "tc_helpers.cuh"
 
 namespace elman {
@@ -523,6 +524,8 @@ int lr_configure(const LrPlan& pl, cudaLaunchConfig_t* cfg, cudaLaunchAttribute*
 template <bool BWD>
 bool lr_launchable(const LrPlan& pl) {
   static int cache_nc[8], cache_smem[8], cache_ok[8], ncache = 0;
+  static std::mutex cache_mutex;
+  std::lock_guard<std::mutex> lock(cache_mutex);
   for (int i = 0; i < ncache; ++i)
     if (cache_nc[i] == pl.NC && cache_smem[i] == (int)pl.smem) return cache_ok[i] != 0;
   cudaLaunchConfig_t cfg;

@@ -31,6 +31,8 @@
 // returns with tensor memory freed.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -919,6 +921,8 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
   struct Entry { Key k; RecPlan pl; };
   static Entry cache[32];
   static int ncache = 0;
+  static std::mutex cache_mutex;   // callers may come from several host threads (autograd's)
+  std::lock_guard<std::mutex> lock(cache_mutex);
   const Key key{B, d, compact, options().rec_ksplit, options().rec_groups, options().rec_mma_warps,
                 options().rec_w_tmem, options().rec_large_batch};
   for (int i = 0; i < ncache; ++i) {
