@@ -64,7 +64,9 @@ def parse_args():
     ap.add_argument("--time-steps", type=int, default=0,
                     help="c4 workload: sequence length instead of 2048 (small captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-sample-steps", type=int, default=128,
+    ap.add_argument("--cpu-seconds", type=float, default=12.0,
+                    help="CPU work to spend on the cpu_baseline leg (whole passes, at least 2)")
+    ap.add_argument("--cpu-sample-steps", type=int, default=0,
                     help="time steps of the workload the CPU baseline runs")
     return ap.parse_args()
 
@@ -223,7 +225,13 @@ def run_reference(args, rank):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     inp = make_inputs(1234)
-    sample = min(T, 32)
+    # one step = one pass over the workload; whole T when the run then stays near 90 s of
+    # CPU work (about a second per pass on 16 cores), else a prefix of the time steps
+    cpu_reference_pass(inp, 32)
+    probe = cpu_reference_pass(inp, 128)
+    budget = 90.0 / max(1, args.steps + max(1, min(args.warmup, 2)))
+    sample = T if probe * (T / 128) <= budget else max(32, int(budget / probe * 128) // 32 * 32)
+    sample = min(T, sample)
     for _ in range(max(1, min(args.warmup, 2))):
         cpu_reference_pass(inp, sample)
     times = [cpu_reference_pass(inp, sample) for _ in range(args.steps)]
@@ -236,7 +244,8 @@ def run_reference(args, rank):
         "data": "synthetic",
         "config": {"workload": "configs[1]: E1 cell fwd+bwd, d=1280, B=32, T=512 (fp32 on CPU)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"first {sample} of {T} time steps per step, full B and d; "
+                         "sample": f"each step is one pass over the first {sample} of {T} time "
+                                   "steps, full B and d, fp32, forward + autograd backward; "
                                    "ms_per_step is scaled to T=512"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -736,12 +745,16 @@ def main():
             torch.set_num_threads(cores)
             fp32 = {k: v.float() for k, v in host.items()}
             cpu_reference_pass(fp32, 8)
-            sec = cpu_reference_pass(fp32, args.cpu_sample_steps)
+            n_t = T if args.cpu_sample_steps <= 0 else min(T, args.cpu_sample_steps)
+            passes, spent = 0, 0.0
+            while passes < 2 or (spent < args.cpu_seconds and passes < 64):
+                spent += cpu_reference_pass(fp32, n_t)
+                passes += 1
             line["cpu_baseline"] = {
-                "value": B * args.cpu_sample_steps / sec, "unit": UNIT, "cores": cores,
+                "value": B * n_t * passes / spent, "unit": UNIT, "cores": cores,
                 "kind": "port",
-                "sample": f"first {args.cpu_sample_steps} of {T} time steps, full B and d, fp32, "
-                          f"one pass ({sec:.1f} s)"}
+                "sample": f"{passes} passes over the first {n_t} of {T} time steps, full B and d, "
+                          f"fp32, forward + autograd backward ({spent:.1f} s of CPU work)"}
         else:
             line["cpu_baseline"] = None
         print(json.dumps(line), flush=True)
