@@ -200,3 +200,20 @@ def test_phase_entry_points_compose_to_the_whole_call(dtype, T, B, d):
     assert orc.rel_err(acc.float().cpu(), 2 * got["dx"].view(T * B, d).float().cpu()) < 1e-2
     with pytest.raises(Exception):
         H.gemm(7, dv2, dev["W_x"])
+
+
+@pytest.mark.parametrize("dtype,batch,dim", [(torch.float32, 3, 72), (torch.bfloat16, 5, 136)])
+def test_pipelined_ladder_lm_on_the_cuda_core_kernels(dtype, batch, dim):
+    """Shapes the tensor-core recurrence does not take (fp32; odd sizes) run the pipeline on
+    the cooperative CUDA-core kernels: same results as layer by layer."""
+    from elman_b200.ladder_lm import LadderLM, zipf_tokens
+    torch.manual_seed(5)
+    model = LadderLM(vocab_size=256, dim=dim, depth=3, level=1, r_h_mode="none").cuda().to(dtype)
+    tokens = zipf_tokens(batch, 41, seed=9).cuda()
+    loss_seq, g_seq = _lm_step(model, tokens)
+    model.pipeline_chunks = 3
+    loss_pipe, g_pipe = _lm_step(model, tokens)
+    tol = TOL[dtype] * (50 if dtype == torch.float32 else 1)   # fp32: sums reordered over chunks
+    assert abs(loss_pipe - loss_seq) < tol * abs(loss_seq)
+    for n in g_seq:
+        assert orc.rel_err(g_pipe[n].cpu(), g_seq[n].cpu()) < tol, n
