@@ -121,6 +121,27 @@ class E1ChunkProjectionFunction(torch.autograd.Function):
         return dx, dW_x, db, dW_h, None
 
 
+class LinearFunction(torch.autograd.Function):
+    """y = x W^T + b over the last dimension through the library's GEMMs (elman_gemm);
+    backward: dx = dy W, dW = dy^T x, db = column sums of dy."""
+
+    @staticmethod
+    def forward(ctx, x, W, b):
+        ctx.save_for_backward(x, W)
+        x2 = x.reshape(-1, x.shape[-1])
+        return hasty_pytorch_lib.gemm(hasty_pytorch_lib.GEMM_NT, x2, W, b).view(*x.shape[:-1],
+                                                                              W.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, W = ctx.saved_tensors
+        G = hasty_pytorch_lib
+        dy2 = dy.contiguous().view(-1, W.shape[0])
+        dx = G.gemm(G.GEMM_NN, dy2, W).view(x.shape)
+        dW = G.gemm(G.GEMM_TN, dy2, x.reshape(-1, x.shape[-1]))
+        return dx, dW, G.column_sum(dy2)
+
+
 class E1ChunkRecurrenceFunction(torch.autograd.Function):
     """The sequential half of one chunk: forward(pre, z, h0, W_h, link, flags) ->
     (output [T,B,d], h_last [B,d]).  The h_last -> next chunk's h0 edge carries the

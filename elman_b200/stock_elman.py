@@ -108,5 +108,33 @@ class StockElman(nn.Module):
         y = self.dropout(cell_out.permute(1, 0, 2).contiguous())
         return self.out_proj(y), h_all[-1]
 
+    # ---- time-chunked execution (LadderLM's layer/time pipeline), time-major [Tc,B,*] ----
+    # E0 differs from E1 only in where the gate pre-activation comes from, so the chunk
+    # pieces reuse E1's projection and recurrence nodes: pre = W_x x + b and the gate
+    # g = W_gate x + b_gate are both time-parallel projections, and the recurrence
+    # h_t = tanh(pre_t + W_h h_{t-1}), y_t = h_t silu(g_t) is the same kernel.
+    @property
+    def supports_time_chunks(self):
+        return not self.use_conv
+
+    def chunk_weights(self):
+        return self.cell.get_W_h().contiguous()
+
+    def chunk_pre(self, x, W_h, link):
+        from .mamba_gated_elman import E1ChunkProjectionFunction, LinearFunction
+        cell = self.cell
+        x_proj = self.in_proj(x).contiguous()
+        pre = E1ChunkProjectionFunction.apply(x_proj, cell.W_x.contiguous(), cell.b.contiguous(),
+                                              W_h, link)
+        gate = LinearFunction.apply(x_proj, cell.W_gate.contiguous(), cell.b_gate.contiguous())
+        return pre, gate
+
+    def chunk_rec(self, pre, gate, h0, W_h, link, flags=0, W_h_T=None):
+        from .mamba_gated_elman import E1ChunkRecurrenceFunction
+        return E1ChunkRecurrenceFunction.apply(pre, gate, h0.contiguous(), W_h, link, flags, W_h_T)
+
+    def chunk_post(self, cell_out):
+        return self.out_proj(self.dropout(cell_out))
+
     def extra_repr(self):
         return f"dim={self.dim}, d_inner={self.d_inner}, LEVEL=0_STOCK"

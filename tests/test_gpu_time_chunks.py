@@ -217,3 +217,22 @@ def test_pipelined_ladder_lm_on_the_cuda_core_kernels(dtype, batch, dim):
     assert abs(loss_pipe - loss_seq) < tol * abs(loss_seq)
     for n in g_seq:
         assert orc.rel_err(g_pipe[n].cpu(), g_seq[n].cpu()) < tol, n
+
+
+def test_pipelined_ladder_lm_level0_matches_sequential():
+    """The E0 layer runs the same pipeline (E1's projection/recurrence nodes, gate from a
+    second projection)."""
+    from elman_b200.ladder_lm import LadderLM, zipf_tokens
+    torch.manual_seed(8)
+    model = LadderLM(vocab_size=256, dim=256, depth=3, level=0, r_h_mode="free").cuda().bfloat16()
+    with torch.no_grad():       # keep the free recurrent matrices contractive
+        for layer in model.layers:
+            layer.cell.W_h.mul_(0.5)
+    tokens = zipf_tokens(8, 65, seed=4).cuda()
+    loss_seq, g_seq = _lm_step(model, tokens)
+    model.pipeline_chunks = 4
+    for _ in range(2):
+        loss_pipe, g_pipe = _lm_step(model, tokens)
+        assert abs(loss_pipe - loss_seq) < 2e-2 * abs(loss_seq)
+        for n in g_seq:
+            assert orc.rel_err(g_pipe[n].cpu(), g_seq[n].cpu()) < TOL[torch.bfloat16], n

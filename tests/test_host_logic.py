@@ -256,3 +256,34 @@ def test_e1_layer_split_chunk_pieces_equal_reference_fixture(golden_dir, oracle_
             assert orc.rel_err(got[k], vref) < 2e-5, k
             checked += 1
     assert checked >= 7
+
+
+def test_e0_layer_chunk_pieces_equal_whole_layer(oracle_backend):
+    """StockElman's chunk_pre / chunk_rec / chunk_post (E1's projection and recurrence nodes
+    with the gate from a second projection) reproduce its own whole-sequence forward()."""
+    torch.manual_seed(3)
+    dim, B, T = 24, 2, 7
+    layer = e0mod.StockElman(dim, expansion=1.0, r_h_mode="free")
+    x1 = as_fake_cuda(torch.randn(B, T, dim)).requires_grad_(True)
+    d_out = torch.randn(B, T, dim)
+    out1, h1 = layer(x1)
+    (out1 * d_out).sum().backward()
+    want = {n: p_.grad.clone() for n, p_ in layer.named_parameters()}
+    want_dx = x1.grad.clone()
+    layer.zero_grad()
+    x2 = torch.Tensor(x1.detach().clone()).requires_grad_(True)
+    W_h = layer.chunk_weights()
+    state = torch.zeros(B, layer.d_inner)
+    outs = []
+    for t0, t1 in ((0, 3), (3, 4), (4, 7)):
+        link = e1mod.ChunkLink()
+        pre, gate = layer.chunk_pre(x2[:, t0:t1].transpose(0, 1).contiguous(), W_h, link)
+        cell_out, state = layer.chunk_rec(pre, gate, state, W_h, link)
+        outs.append(layer.chunk_post(cell_out).transpose(0, 1))
+    out2 = torch.cat(outs, dim=1)
+    (out2 * d_out).sum().backward()
+    assert orc.rel_err(out2, torch.Tensor(out1.detach())) < 1e-5
+    assert orc.rel_err(state, torch.Tensor(h1.detach())) < 1e-5
+    assert orc.rel_err(x2.grad, torch.Tensor(want_dx)) < 1e-5
+    for n, p_ in layer.named_parameters():
+        assert orc.rel_err(p_.grad, want[n]) < 1e-5, n
