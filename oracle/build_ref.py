@@ -1,7 +1,7 @@
 """TEST INFRASTRUCTURE ONLY — build the REFERENCE's CUDA kernels for this path.
 
 Compiles the reference's own, unmodified sources where they lie in a checkout of
-the reference (default /root/reference) together with oracle/ref_cuda_binding.cu
+the reference (REFERENCE_DIR below, or --reference) together with oracle/ref_cuda_binding.cu
 into oracle/_ref/libelman_ref_cuda.so (sm_100; the reference's Makefile only
 lists sm_80/sm_89).  Nothing is copied out of the reference; only the built
 library lands in oracle/_ref/, which is git-ignored.
@@ -20,13 +20,16 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+# where a checkout of the reference lives on the build machine (absent on a GPU-only box)
+REFERENCE_DIR = os.environ.get("ELMAN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
 OUT = os.path.join(HERE, "_ref")
 LIB = os.path.join(OUT, "libelman_ref_cuda.so")
 REF_SOURCES = ["mamba_gated_elman_gpu.cu.cc", "stock_elman_gpu.cu.cc",
                "pure_lowrank_elman_fused_gpu.cu.cc"]
 
 
-def build(reference: str = "/root/reference", force: bool = False) -> str | None:
+def build(reference: str = None, force: bool = False) -> str | None:
+    reference = reference or REFERENCE_DIR
     libdir = os.path.join(reference, "elman", "cuda", "lib")
     if not os.path.isdir(libdir):
         return LIB if os.path.exists(LIB) else None
@@ -51,7 +54,7 @@ def build(reference: str = "/root/reference", force: bool = False) -> str | None
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=REFERENCE_DIR)
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     print(build(a.reference, a.force))

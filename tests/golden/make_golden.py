@@ -154,7 +154,8 @@ def run_ladder_lm(reference_root, seed):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference",
+                    default=os.environ.get("ELMAN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference")))
     ap.add_argument("--only-lm", action="store_true")
     args = ap.parse_args()
     if args.only_lm:
