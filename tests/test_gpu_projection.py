@@ -78,3 +78,31 @@ def test_tensor_core_and_cuda_core_paths_agree():
         b = H.projection(A, W)
     torch.cuda.synchronize()
     assert rel_err(a, b.float().cpu()) < 4e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 128), (304, 520, 136), (1280, 1280, 2048),
+                                   (2048, 1280, 1280), (384, 392, 64), (8, 16, 8)])
+def test_every_gemm_form(M, N, K):
+    """NT (+bias, +accumulate), NN and TN through elman_gemm: K-major and MN-major operands of
+    the tcgen05 kernel, ragged tile edges, against fp32 matmuls."""
+    g = torch.Generator().manual_seed(7 * M + 3 * N + K)
+    s = K ** -0.5
+    A = torch.randn(M, K, generator=g).bfloat16().cuda()
+    Bnt = (torch.randn(N, K, generator=g) * s).bfloat16().cuda()
+    Bnn = (torch.randn(K, N, generator=g) * s).bfloat16().cuda()
+    At = torch.randn(K, M, generator=g).bfloat16().cuda()
+    bias = torch.randn(N, generator=g).bfloat16().cuda()
+    C0 = torch.randn(M, N, generator=g).bfloat16().cuda()
+    f = lambda t: t.float().cpu()
+    before = _lib.tc_launch_count()
+    nt = H.gemm(H.GEMM_NT, A, Bnt, bias)
+    acc = H.gemm(H.GEMM_NT, A, Bnt, None, out=C0.clone(), accumulate=True)
+    nn = H.gemm(H.GEMM_NN, A, Bnn)
+    tn = H.gemm(H.GEMM_TN, At, Bnn)
+    torch.cuda.synchronize()
+    assert _lib.tc_launch_count() - before == 4, "all four must take the tcgen05 kernel"
+    assert _lib.device_status()[0] == 0
+    assert rel_err(f(nt), f(A) @ f(Bnt).T + f(bias)) < 1e-2
+    assert rel_err(f(acc), f(A) @ f(Bnt).T + f(C0)) < 1e-2
+    assert rel_err(f(nn), f(A) @ f(Bnn)) < 1e-2
+    assert rel_err(f(tn), f(At).T @ f(Bnn)) < 1e-2
