@@ -42,6 +42,68 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// One 32-column chunk of one output row, as it comes out of tensor memory: bias, optional
+// accumulate into C, conversion and store.  `gm` is the row, `gn0` the chunk's first column.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, int gm, int gn0,
+                                            const uint32_t (&r)[32], bool vec_ok) {
+  if (gm < p.M && gn0 < p.N) {
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+    const bool full = gn0 + 32 <= p.N;
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (full || gn0 + j < p.N) f[j] += __bfloat162float(p.bias[gn0 + j]);
+    }
+    if (p.c_is_f32) {
+      float* crow = (float*)p.C + (long)gm * p.ldc + gn0;
+      if (full && ((p.ldc & 3) == 0) && (((uintptr_t)p.C & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+          if (p.accumulate) {
+            float4 old = *reinterpret_cast<float4*>(crow + j);
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          *reinterpret_cast<float4*>(crow + j) = o;
+        }
+      } else {
+        for (int j = 0; j < 32 && gn0 + j < p.N; ++j)
+          crow[j] = p.accumulate ? crow[j] + f[j] : f[j];
+      }
+    } else {
+      bf16* crow = (bf16*)p.C + (long)gm * p.ldc + gn0;
+      if (full && vec_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          if (p.accumulate) {
+            uint4 old = *reinterpret_cast<uint4*>(crow + j);
+            const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float2 of = __bfloat1622float2(o2[q]);
+              f[j + 2 * q] += of.x;
+              f[j + 2 * q + 1] += of.y;
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16(f[j], f[j + 1]);
+          o.y = pack_bf16(f[j + 2], f[j + 3]);
+          o.z = pack_bf16(f[j + 4], f[j + 5]);
+          o.w = pack_bf16(f[j + 6], f[j + 7]);
+          *reinterpret_cast<uint4*>(crow + j) = o;
+        }
+      } else {
+        for (int j = 0; j < 32 && gn0 + j < p.N; ++j) {
+          float val = p.accumulate ? f[j] + __bfloat162float(crow[j]) : f[j];
+          crow[j] = __float2bfloat16_rn(val);
+        }
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                GemmParams p) {
@@ -159,63 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t r[32];
       ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
       ptx::tmem_ld_wait();
-      const int gn0 = n0 + c * 32;
-      if (gm < p.M && gn0 < p.N) {
-        float f[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
-        const bool full = gn0 + 32 <= p.N;
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (full || gn0 + j < p.N) f[j] += __bfloat162float(p.bias[gn0 + j]);
-        }
-        if (p.c_is_f32) {
-          float* crow = (float*)p.C + (long)gm * p.ldc + gn0;
-          if (full && ((p.ldc & 3) == 0) && (((uintptr_t)p.C & 15) == 0)) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-              if (p.accumulate) {
-                float4 old = *reinterpret_cast<float4*>(crow + j);
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(crow + j) = o;
-            }
-          } else {
-            for (int j = 0; j < 32 && gn0 + j < p.N; ++j)
-              crow[j] = p.accumulate ? crow[j] + f[j] : f[j];
-          }
-        } else {
-          bf16* crow = (bf16*)p.C + (long)gm * p.ldc + gn0;
-          if (full && vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (p.accumulate) {
-                uint4 old = *reinterpret_cast<uint4*>(crow + j);
-                const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  float2 of = __bfloat1622float2(o2[q]);
-                  f[j + 2 * q] += of.x;
-                  f[j + 2 * q + 1] += of.y;
-                }
-              }
-              uint4 o;
-              o.x = pack_bf16(f[j], f[j + 1]);
-              o.y = pack_bf16(f[j + 2], f[j + 3]);
-              o.z = pack_bf16(f[j + 4], f[j + 5]);
-              o.w = pack_bf16(f[j + 6], f[j + 7]);
-              *reinterpret_cast<uint4*>(crow + j) = o;
-            }
-          } else {
-            for (int j = 0; j < 32 && gn0 + j < p.N; ++j) {
-              float val = p.accumulate ? f[j] + __bfloat162float(crow[j]) : f[j];
-              crow[j] = __float2bfloat16_rn(val);
-            }
-          }
-        }
-      }
+      store_chunk(p, gm, n0 + c * 32, r, vec_ok);
     }
   } else {
     // Give copies that may still be in flight time to land before the CTA's
@@ -225,6 +231,182 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 0) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Persistent variant for large shapes: 128 x 256 output tiles, one CTA per SM looping
+// over tiles, four 48 KB stages, and the accumulator double-buffered in tensor memory
+// (2 x 256 columns) so that the epilogue of one tile (four dedicated warps) runs under
+// the main loop of the next.  Warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 =
+// epilogue.  Same arithmetic and K order per output element as gemm_tc_kernel.
+// ---------------------------------------------------------------------------
+constexpr int P_BM = 128, P_BN = 256, P_STAGES = 4;
+constexpr int P_A_BYTES = P_BM * BK * 2, P_B_BYTES = P_BN * BK * 2;
+constexpr int P_SMEM = P_STAGES * (P_A_BYTES + P_B_BYTES) + 1024;
+constexpr int P_THREADS = 192;
+constexpr int P_BLOCK_BYTES = 64 * BK * 2;   // one [64 K rows x 64 MN elements] box
+
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
+                          const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[P_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[P_STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + P_STAGES * P_A_BYTES;
+  const int nk = (p.K + BK - 1) / BK;
+  const int tiles_n = (p.N + P_BN - 1) / P_BN;
+  const int tiles = ((p.M + P_BM - 1) / P_BM) * tiles_n;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < P_STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_empty[b], 4);
+    }
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmA);
+    ptx::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;   // running K-iteration index over all my tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * P_BM, n0 = (t % tiles_n) * P_BN;
+        for (int i = 0; i < nk; ++i, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (uint32_t)(it / P_STAGES) & 1u;
+          if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, p.spin_limit, abortp)) {
+            abort_flag = 1;
+            report_timeout(p.status, KID_GEMM_TC, i);
+            ok = false;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx(&full_bar[s], P_A_BYTES + P_B_BYTES);
+          if (p.a_mn) {
+#pragma unroll
+            for (int blk = 0; blk < P_BM / 64; ++blk)
+              ptx::tma_load_2d(sA + s * P_A_BYTES + blk * P_BLOCK_BYTES, &tmA, m0 + 64 * blk,
+                               i * BK, &full_bar[s]);
+          } else {
+            ptx::tma_load_2d(sA + s * P_A_BYTES, &tmA, i * BK, m0, &full_bar[s]);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int blk = 0; blk < P_BN / 64; ++blk)
+              ptx::tma_load_2d(sB + s * P_B_BYTES + blk * P_BLOCK_BYTES, &tmB, n0 + 64 * blk,
+                               i * BK, &full_bar[s]);
+          } else {
+            ptx::tma_load_2d(sB + s * P_B_BYTES, &tmB, i * BK, n0, &full_bar[s]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = ptx::umma_idesc_bf16(P_BM, P_BN) | (p.a_mn ? (1u << 15) : 0u) |
+                             (p.b_mn ? (1u << 16) : 0u);
+      const uint64_t a_step = p.a_mn ? 128 : 2, b_step = p.b_mn ? 128 : 2;
+      int it = 0, lt = 0;   // K-iteration and tile counters of this CTA
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++lt) {
+        const int b = lt & 1;
+        // the epilogue must have drained this accumulator buffer (two tiles ago)
+        if (!ptx::mbar_wait(&acc_empty[b], (((uint32_t)(lt >> 1)) & 1u) ^ 1u, p.spin_limit * 8,
+                            abortp)) {
+          abort_flag = 1;
+          report_timeout(p.status, KID_GEMM_TC, 0xFFFE);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * P_BN);
+        for (int i = 0; i < nk; ++i, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (uint32_t)(it / P_STAGES) & 1u;
+          if (!ptx::mbar_wait(&full_bar[s], ph, p.spin_limit, abortp)) {
+            abort_flag = 1;
+            report_timeout(p.status, KID_GEMM_TC, i);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ptx::smem_u32(sA + s * P_A_BYTES);
+          const uint32_t b_addr = ptx::smem_u32(sB + s * P_B_BYTES);
+          const uint64_t da = p.a_mn ? ptx::umma_desc_mn_sw128(a_addr, P_BLOCK_BYTES)
+                                     : ptx::umma_desc_k_sw128(a_addr);
+          const uint64_t db = p.b_mn ? ptx::umma_desc_mn_sw128(b_addr, P_BLOCK_BYTES)
+                                     : ptx::umma_desc_k_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            ptx::umma_bf16(d_tmem, da + a_step * k, db + b_step * k, idesc,
+                           (i > 0 || k > 0) ? 1u : 0u);
+          ptx::umma_commit(&empty_bar[s]);   // frees the stage when these MMAs retire
+        }
+        if (ok) ptx::umma_commit(&acc_full[b]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ----- epilogue warps 2..5: warp w may read TMEM lanes [32 (w % 4), +32) -----
+    const int quarter = warp & 3;
+    const bool vec_ok = ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0);
+    int lt = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++lt) {
+      const int b = lt & 1;
+      const int m0 = (t / tiles_n) * P_BM, n0 = (t % tiles_n) * P_BN;
+      bool ok = ptx::mbar_wait(&acc_full[b], ((uint32_t)(lt >> 1)) & 1u, p.spin_limit * 8, abortp);
+      if (!ok && abort_flag == 0) {
+        abort_flag = 1;
+        report_timeout(p.status, KID_GEMM_TC, 0xFFFF);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const int gm = m0 + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < P_BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * P_BN + c * 32),
+                       r);
+        ptx::tmem_ld_wait();
+        store_chunk(p, gm, n0 + c * 32, r, vec_ok);
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[b]);
+    }
+  }
+  if (abort_flag != 0) {
+    // let copies that may still be in flight land before shared and tensor memory go
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -289,9 +471,28 @@ int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int l
   return gemm_tc(M, N, K, A, lda, 0, W, ldw, 0, bias, C, ldc, c_is_f32, accumulate, stream);
 }
 
+int gemm_tc_persistent(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
+                       int b_mn, const GemmParams& p, cudaStream_t stream);
+namespace { int sm_count(); }
+
 int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
             int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
             cudaStream_t stream) {
+  {
+    // option gemm_persistent: 0 = the persistent 128x256 kernel once its tiles fill the SMs,
+    // 1 = never, 2 = always
+    const long want = options().gemm_persistent;
+    const long tiles = (long)((M + P_BM - 1) / P_BM) * ((N + P_BN - 1) / P_BN);
+    if (want == 2 || (want == 0 && tiles >= sm_count())) {
+      GemmParams q;
+      q.M = M; q.N = N; q.K = K;
+      q.bias = bias; q.C = C; q.ldc = ldc; q.c_is_f32 = c_is_f32; q.accumulate = accumulate;
+      q.spin_limit = options().spin_limit;
+      q.status = device_status_ptr();
+      q.a_mn = a_mn; q.b_mn = b_mn;
+      return gemm_tc_persistent(M, N, K, A, lda, a_mn, W, ldw, b_mn, q, stream);
+    }
+  }
   static bool attr_set = false;
   if (!attr_set) {
     ELMAN_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -315,6 +516,47 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
   p.a_mn = a_mn; p.b_mn = b_mn;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, p);
+  count_launch(true);
+  ELMAN_CUDA_CHECK(cudaGetLastError());
+  return ELMAN_OK;
+}
+
+namespace {
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 148;
+    }
+  }
+  return n;
+}
+}  // namespace
+
+// The persistent 128x256 kernel: worth it once there is at least about one tile per SM.
+int gemm_tc_persistent(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
+                       int b_mn, const GemmParams& p, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    ELMAN_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_persistent_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
+    attr_set = true;
+  }
+  CUtensorMap tmA, tmB;
+  if (a_mn)
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK));
+  else
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, P_BM));
+  if (b_mn)
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, BK));
+  else
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, P_BN));
+  const int tiles = ((M + P_BM - 1) / P_BM) * ((N + P_BN - 1) / P_BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_tc_persistent_kernel<<<grid, P_THREADS, P_SMEM, stream>>>(tmA, tmB, p);
   count_launch(true);
   ELMAN_CUDA_CHECK(cudaGetLastError());
   return ELMAN_OK;
