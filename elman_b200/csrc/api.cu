@@ -140,18 +140,19 @@ static int gemm_nn(int dtype, int M, int N, int K, const void* A, int lda, const
   return gemm_generic(dtype, M, N, K, A, lda, 1, Bm, ldb, 1, nullptr, C, ldc, accumulate, st);
 }
 
-// C[M,N] = At^T Bt_ where the inputs are stored as Am[K,M] and Bm[K,N] (sum over
-// the leading "row" index, K = T*B).  AT / BT are the transposed copies [M,K] and
-// [N,K]; when `at_ready` / `bt_ready` they already hold the data.
-static int gemm_tn(int dtype, int M, int N, long K, const void* Am, const void* Bm, void* AT,
-                   bool at_ready, void* BT, bool bt_ready, void* C, cudaStream_t st) {
+// C[M,N] = Am^T Bm where the inputs are stored as Am[K,M] and Bm[K,N] (sum over the
+// leading "row" index, K = T*B): both operands are MN-major for the tensor core and are
+// read in place.  `splitk` is optional scratch for fp32 partial sums over K ranges.
+static size_t splitk_scratch_bytes(int dtype, int M, int N) {
+  return dtype == ELMAN_BF16 ? (size_t)GEMM_MAX_KSPLIT * M * N * sizeof(float) : 0;
+}
+static int gemm_tn(int dtype, int M, int N, long K, const void* Am, const void* Bm, void* C,
+                   cudaStream_t st, float* splitk = nullptr, size_t splitk_bytes = 0) {
   if (M == 0 || N == 0) return ELMAN_OK;
-  (void)AT; (void)BT; (void)at_ready; (void)bt_ready;
   if (use_tc(dtype) && K < (1L << 31) && (M & 7) == 0 && (N & 7) == 0 && (K & 7) == 0 &&
       gemm_tc_supported(M, N, (int)K, Am, M, Bm, N, C, N, 0)) {
-    // both operands are [K, *] with the M / N extent contiguous: MN-major A and B
     return gemm_tc(M, N, (int)K, (const bf16*)Am, M, 1, (const bf16*)Bm, N, 1, nullptr, C, N, 0, 0,
-                   st);
+                   st, splitk, splitk_bytes);
   }
   return gemm_generic(dtype, M, N, (int)K, Am, 1, M, Bm, N, 1, nullptr, C, N, 0, st);
 }
@@ -201,7 +202,7 @@ static size_t carve_e1_fwd(int dtype, int T, int B, int d, void* ws, E1FwdWs* o)
   return c.total();
 }
 
-struct E1BwdWs { void* Wt; void* dv; float* db; int* sync; void* WxT; void* dvT; void* xT; };
+struct E1BwdWs { void* Wt; void* dv; float* db; int* sync; void* WxT; float* splitk; size_t splitk_bytes; };
 static size_t carve_e1_bwd(int dtype, int T, int B, int d, void* ws, E1BwdWs* o) {
   Carver c(ws);
   size_t es = esize(dtype);
@@ -210,7 +211,9 @@ static size_t carve_e1_bwd(int dtype, int T, int B, int d, void* ws, E1BwdWs* o)
   o->db = (float*)c.take((size_t)d * sizeof(float));
   size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
   o->sync = (int*)c.take(sb);
-  o->WxT = o->dvT = o->xT = nullptr;  // the GEMMs read transposed operands in place
+  o->WxT = nullptr;  // the GEMMs read transposed operands in place
+  o->splitk_bytes = splitk_scratch_bytes(dtype, d, d);   // partial sums of the dW GEMMs
+  o->splitk = o->splitk_bytes ? (float*)c.take(o->splitk_bytes) : nullptr;
   return c.total();
 }
 
@@ -425,8 +428,8 @@ int elman_e1_backward_carry(int dtype, int flags, int T, int B, int d, const voi
   // dx = dv W_x ; dW_x = dv^T x ; dW_h = dv^T h[0:T]
   PhaseTimer timer(3, st);
   ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, w.WxT, dx, d, 0, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, w.dvT, false, w.xT, false, dW_x, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, w.dvT, true, w.xT, false, dW_h, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, dW_h, st, w.splitk, w.splitk_bytes));
   return ELMAN_OK;
 }
 
@@ -528,7 +531,7 @@ int elman_e0_forward(int dtype, int training, int T, int B, int d, const void* x
 
 struct E0BwdWs {
   void* Wt; void* dv; void* dg; float* db; float* cs; int* sync;
-  void* WT2; void* dvT; void* xT;
+  void* WT2; float* splitk; size_t splitk_bytes;
 };
 static size_t carve_e0_bwd(int dtype, int T, int B, int d, void* ws, E0BwdWs* o) {
   Carver c(ws);
@@ -540,7 +543,9 @@ static size_t carve_e0_bwd(int dtype, int T, int B, int d, void* ws, E0BwdWs* o)
   o->cs = (float*)c.take(column_sum_scratch_bytes(d));
   size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
   o->sync = (int*)c.take(sb);
-  o->WT2 = o->dvT = o->xT = nullptr;  // the GEMMs read transposed operands in place
+  o->WT2 = nullptr;  // the GEMMs read transposed operands in place
+  o->splitk_bytes = splitk_scratch_bytes(dtype, d, d);
+  o->splitk = o->splitk_bytes ? (float*)c.take(o->splitk_bytes) : nullptr;
   return c.total();
 }
 
@@ -585,9 +590,9 @@ int elman_e0_backward(int dtype, int T, int B, int d, const void* W_x, const voi
   ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, w.WT2, dx, d, 0, st));
   ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dg, d, W_gate, d, w.WT2, dx, d, 1, st));
   // dW_x = dv^T x ; dW_h = dv^T h[0:T] ; dW_gate = dg^T x
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, w.dvT, false, w.xT, false, dW_x, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dg, x, w.dvT, false, w.xT, true, dW_gate, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, w.dvT, false, w.xT, false, dW_h, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dg, x, dW_gate, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, dW_h, st, w.splitk, w.splitk_bytes));
   return ELMAN_OK;
 }
 
@@ -801,11 +806,11 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, co
   for (const Job& jb : jobs) {
     if (jb.is_u) {  // dU [d, r] = A^T [d, TB] * Bm [TB, rp]
       void* out = padded ? w.dUP : jb.dU_or_dV;
-      ELMAN_RETURN_IF(gemm_tn(dtype, d, rp, TB, jb.A, jb.Bm, nullptr, false, nullptr, false, out, st));
+      ELMAN_RETURN_IF(gemm_tn(dtype, d, rp, TB, jb.A, jb.Bm, out, st));
       if (padded) ELMAN_RETURN_IF(resize2d(dtype, out, d, rp, jb.dU_or_dV, d, r, st));
     } else {        // dV [r, d] = A^T [rp, TB] * Bm [TB, d]
       void* out = padded ? w.dVP : jb.dU_or_dV;
-      ELMAN_RETURN_IF(gemm_tn(dtype, rp, d, TB, jb.A, jb.Bm, nullptr, false, nullptr, false, out, st));
+      ELMAN_RETURN_IF(gemm_tn(dtype, rp, d, TB, jb.A, jb.Bm, out, st));
       if (padded) ELMAN_RETURN_IF(copy_rows(dtype, out, jb.dU_or_dV, (long)r * d, st));
     }
   }
@@ -847,7 +852,7 @@ int elman_gemm(int dtype, int op, int M, int N, int K, const void* A, const void
   REQUIRE_PTR(A); REQUIRE_PTR(B);
   if (op == ELMAN_GEMM_NT) return proj_nt(dtype, M, N, K, A, K, B, K, bias, C, N, accumulate, st);
   if (op == ELMAN_GEMM_NN) return gemm_nn(dtype, M, N, K, A, K, B, N, nullptr, C, N, accumulate, st);
-  return gemm_tn(dtype, M, N, K, A, B, nullptr, false, nullptr, false, C, st);
+  return gemm_tn(dtype, M, N, K, A, B, C, st);
 }
 
 size_t elman_column_sum_workspace(int N) { return column_sum_scratch_bytes(N < 0 ? 0 : N); }

@@ -119,9 +119,12 @@ int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int l
                cudaStream_t stream);
 // General form: a_mn / b_mn != 0 mean the operand is stored [K, M] resp. [K, N]
 // (MN-major), which the tensor core reads directly — no transpose pass.
+// `splitk`: optional scratch for fp32 partial sums (GEMM_MAX_KSPLIT * M * N floats cover every
+// case); with it, shapes with few output tiles and a long K are cut along K.
+constexpr int GEMM_MAX_KSPLIT = 4;
 int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
             int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
-            cudaStream_t stream);
+            cudaStream_t stream, float* splitk = nullptr, size_t splitk_bytes = 0);
 bool gemm_tc_supported(int M, int N, int K, const void* A, int lda, const void* W, int ldw,
                        const void* C, int ldc, int c_is_f32);
 

@@ -35,6 +35,8 @@ struct GemmParams {
   int* status;
   int a_mn;  // A is given as [K, M] (M contiguous): MN-major operand, no transpose pass
   int b_mn;  // W is given as [K, N] (N contiguous)
+  int ksplit = 1;             // persistent kernel: K range cut into this many work items per tile
+  float* partial = nullptr;   // [ksplit][M][N] fp32 partial sums when ksplit > 1
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -264,6 +266,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   const int nk = (p.K + BK - 1) / BK;
   const int tiles_n = (p.N + P_BN - 1) / P_BN;
   const int tiles = ((p.M + P_BM - 1) / P_BM) * tiles_n;
+  const int items = tiles * p.ksplit;   // work items: (tile, K range) pairs, the K range fastest
 
   if (tid == 0) {
     abort_flag = 0;
@@ -293,9 +296,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     if (lane == 0) {
       int it = 0;   // running K-iteration index over all my tiles
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+        const int t = w / p.ksplit, sp = w - t * p.ksplit;
         const int m0 = (t / tiles_n) * P_BM, n0 = (t % tiles_n) * P_BN;
-        for (int i = 0; i < nk; ++i, ++it) {
+        const int k_lo = (int)((long)sp * nk / p.ksplit), k_hi = (int)((long)(sp + 1) * nk / p.ksplit);
+        for (int i = k_lo; i < k_hi; ++i, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (uint32_t)(it / P_STAGES) & 1u;
           if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, p.spin_limit, abortp)) {
@@ -332,7 +337,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       const uint64_t a_step = p.a_mn ? 128 : 2, b_step = p.b_mn ? 128 : 2;
       int it = 0, lt = 0;   // K-iteration and tile counters of this CTA
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++lt) {
+      for (int w = blockIdx.x; w < items && ok; w += gridDim.x, ++lt) {
+        const int sp = w % p.ksplit;
+        const int k_lo = (int)((long)sp * nk / p.ksplit), k_hi = (int)((long)(sp + 1) * nk / p.ksplit);
         const int b = lt & 1;
         // the epilogue must have drained this accumulator buffer (two tiles ago)
         if (!ptx::mbar_wait(&acc_empty[b], (((uint32_t)(lt >> 1)) & 1u) ^ 1u, p.spin_limit * 8,
@@ -344,7 +351,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(b * P_BN);
-        for (int i = 0; i < nk; ++i, ++it) {
+        for (int i = k_lo; i < k_hi; ++i, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (uint32_t)(it / P_STAGES) & 1u;
           if (!ptx::mbar_wait(&full_bar[s], ph, p.spin_limit, abortp)) {
@@ -363,7 +370,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             ptx::umma_bf16(d_tmem, da + a_step * k, db + b_step * k, idesc,
-                           (i > 0 || k > 0) ? 1u : 0u);
+                           (i > k_lo || k > 0) ? 1u : 0u);
           ptx::umma_commit(&empty_bar[s]);   // frees the stage when these MMAs retire
         }
         if (ok) ptx::umma_commit(&acc_full[b]);
@@ -375,7 +382,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     const int quarter = warp & 3;
     const bool vec_ok = ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0);
     int lt = 0;
-    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++lt) {
+    for (int w = blockIdx.x; w < items; w += gridDim.x, ++lt) {
+      const int t = w / p.ksplit, sp = w - t * p.ksplit;
       const int b = lt & 1;
       const int m0 = (t / tiles_n) * P_BM, n0 = (t % tiles_n) * P_BN;
       bool ok = ptx::mbar_wait(&acc_full[b], ((uint32_t)(lt >> 1)) & 1u, p.spin_limit * 8, abortp);
@@ -393,7 +401,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         ptx::tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * P_BN + c * 32),
                        r);
         ptx::tmem_ld_wait();
-        store_chunk(p, gm, n0 + c * 32, r, vec_ok);
+        if (p.ksplit == 1) {
+          store_chunk(p, gm, n0 + c * 32, r, vec_ok);
+        } else if (gm < p.M) {   // raw partial sums; splitk_reduce_kernel finishes the job
+          float* dst = p.partial + ((long)sp * p.M + gm) * p.N + n0 + c * 32;
+          if (n0 + c * 32 + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && n0 + c * 32 + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
+          }
+        }
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -407,6 +426,26 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
+}
+
+// C = sum over the K ranges of the partial sums (+ bias) (+ C), in a fixed order.
+__global__ void splitk_reduce_kernel(GemmParams p) {
+  const long total = (long)p.M * p.N;
+  for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (long)gridDim.x * blockDim.x) {
+    const long m = e / p.N;
+    const int n = (int)(e - m * p.N);
+    float acc = 0.f;
+    for (int sp = 0; sp < p.ksplit; ++sp) acc += p.partial[(long)sp * total + e];
+    if (p.bias != nullptr) acc += __bfloat162float(p.bias[n]);
+    if (p.c_is_f32) {
+      float* c = (float*)p.C + m * p.ldc + n;
+      *c = p.accumulate ? *c + acc : acc;
+    } else {
+      bf16* c = (bf16*)p.C + m * p.ldc + n;
+      *c = __float2bfloat16_rn(p.accumulate ? acc + __bfloat162float(*c) : acc);
+    }
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -477,14 +516,27 @@ namespace { int sm_count(); }
 
 int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
             int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
-            cudaStream_t stream) {
+            cudaStream_t stream, float* splitk, size_t splitk_bytes) {
   {
     // option gemm_persistent: 0 = the persistent 128x256 kernel once its tiles fill the SMs,
     // 1 = never, 2 = always
     const long want = options().gemm_persistent;
     const long tiles = (long)((M + P_BM - 1) / P_BM) * ((N + P_BN - 1) / P_BN);
-    if (want == 2 || (want == 0 && tiles >= sm_count())) {
+    // few output tiles but a long K (weight gradients summed over all time steps): cut K so
+    // that the work items fill the SMs, if the caller gave room for the partial sums
+    int ksplit = 1;
+    if (splitk != nullptr && want != 1 && tiles * 2 <= sm_count()) {
+      const int nk = (K + BK - 1) / BK;
+      ksplit = (int)(sm_count() / tiles);
+      if (ksplit > GEMM_MAX_KSPLIT) ksplit = GEMM_MAX_KSPLIT;
+      while (ksplit > 1 && (nk / ksplit < 8 ||
+                            (size_t)ksplit * M * N * sizeof(float) > splitk_bytes))
+        --ksplit;
+    }
+    if (want == 2 || ksplit > 1 || (want == 0 && tiles >= sm_count())) {
       GemmParams q;
+      q.ksplit = ksplit;
+      q.partial = splitk;
       q.M = M; q.N = N; q.K = K;
       q.bias = bias; q.C = C; q.ldc = ldc; q.c_is_f32 = c_is_f32; q.accumulate = accumulate;
       q.spin_limit = options().spin_limit;
@@ -555,10 +607,18 @@ int gemm_tc_persistent(int M, int N, int K, const bf16* A, int lda, int a_mn, co
   else
     ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, P_BN));
   const int tiles = ((M + P_BM - 1) / P_BM) * ((N + P_BN - 1) / P_BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int items = tiles * p.ksplit;
+  const int grid = items < sm_count() ? items : sm_count();
   gemm_tc_persistent_kernel<<<grid, P_THREADS, P_SMEM, stream>>>(tmA, tmB, p);
   count_launch(true);
   ELMAN_CUDA_CHECK(cudaGetLastError());
+  if (p.ksplit > 1) {
+    const long total = (long)M * N;
+    const int rgrid = (int)((total + 255) / 256 < 148L * 8 ? (total + 255) / 256 : 148L * 8);
+    splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(p);
+    count_launch(false);
+    ELMAN_CUDA_CHECK(cudaGetLastError());
+  }
   return ELMAN_OK;
 }
 

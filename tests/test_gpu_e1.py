@@ -230,3 +230,18 @@ def test_host_pipeline_delivers_the_device_results():
             assert torch.equal(g[n], t.cpu()), n
     with pytest.raises(RuntimeError, match="pinned"):
         pipe.submit(calls[0]["x"].cuda(), calls[0]["z"], calls[0]["d_output"])
+
+
+def test_weight_gradients_with_split_k_match_oracle():
+    """T*B large against d: the dW GEMMs have few output tiles and a long K, which the
+    persistent kernel cuts into K ranges with fp32 partial sums (deterministic reduce)."""
+    inp = orc.make_e1_inputs(80, 32, 256, seed=77)
+    got, ref = run_e1(inp, torch.bfloat16)
+    assert_close(errors(got, oracle_e1(ref)), TOL[torch.bfloat16], "split-K dW vs oracle")
+    again, _ = run_e1(inp, torch.bfloat16)
+    for k in ("dW_x", "dW_h", "dx"):
+        assert torch.equal(got[k], again[k]), k
+    with option("gemm_persistent", 1):      # the 128x128 kernel, no K split
+        plain, _ = run_e1(inp, torch.bfloat16)
+    for k in ("dW_x", "dW_h"):
+        assert orc.rel_err(got[k].float().cpu(), plain[k].float().cpu()) < 5e-3, k
