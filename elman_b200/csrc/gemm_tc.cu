@@ -47,16 +47,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // One 32-column chunk of one output row, as it comes out of tensor memory: bias, optional
 // accumulate into C, conversion and store.  `gm` is the row, `gn0` the chunk's first column.
 __device__ __forceinline__ void store_chunk(const GemmParams& p, int gm, int gn0,
-                                            const uint32_t (&r)[32], bool vec_ok) {
+                                            const uint32_t (&r)[32], bool vec_ok,
+                                            const bf16* bias32) {
   if (gm < p.M && gn0 < p.N) {
     float f[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
     const bool full = gn0 + 32 <= p.N;
-    if (p.bias != nullptr) {
+    if (bias32 != nullptr) {   // the 32 bias values of this chunk (global or shared memory)
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (full || gn0 + j < p.N) f[j] += __bfloat162float(p.bias[gn0 + j]);
+      for (int j = 0; j < 32; j += 2)
+        if (full || gn0 + j + 1 < p.N) {
+          const float2 b2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(bias32 + j));
+          f[j] += b2.x;
+          f[j + 1] += b2.y;
+        } else if (gn0 + j < p.N) {
+          f[j] += __bfloat162float(bias32[j]);
+        }
     }
     if (p.c_is_f32) {
       float* crow = (float*)p.C + (long)gm * p.ldc + gn0;
@@ -71,8 +78,9 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int gm, int gn0
           *reinterpret_cast<float4*>(crow + j) = o;
         }
       } else {
-        for (int j = 0; j < 32 && gn0 + j < p.N; ++j)
-          crow[j] = p.accumulate ? crow[j] + f[j] : f[j];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gn0 + j < p.N) crow[j] = p.accumulate ? crow[j] + f[j] : f[j];
       }
     } else {
       bf16* crow = (bf16*)p.C + (long)gm * p.ldc + gn0;
@@ -97,10 +105,12 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int gm, int gn0
           *reinterpret_cast<uint4*>(crow + j) = o;
         }
       } else {
-        for (int j = 0; j < 32 && gn0 + j < p.N; ++j) {
-          float val = p.accumulate ? f[j] + __bfloat162float(crow[j]) : f[j];
-          crow[j] = __float2bfloat16_rn(val);
-        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (gn0 + j < p.N) {
+            float val = p.accumulate ? f[j] + __bfloat162float(crow[j]) : f[j];
+            crow[j] = __float2bfloat16_rn(val);
+          }
       }
     }
   }
@@ -223,7 +233,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t r[32];
       ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
       ptx::tmem_ld_wait();
-      store_chunk(p, gm, n0 + c * 32, r, vec_ok);
+      store_chunk(p, gm, n0 + c * 32, r, vec_ok,
+                  p.bias != nullptr ? p.bias + n0 + c * 32 : nullptr);
     }
   } else {
     // Give copies that may still be in flight time to land before the CTA's
@@ -239,13 +250,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // Persistent variant for large shapes: 128 x 256 output tiles, one CTA per SM looping
 // over tiles, four 48 KB stages, and the accumulator double-buffered in tensor memory
 // (2 x 256 columns) so that the epilogue of one tile (four dedicated warps) runs under
-// the main loop of the next.  Warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 =
+// the main loop of the next.  Warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 =
 // epilogue.  Same arithmetic and K order per output element as gemm_tc_kernel.
 // ---------------------------------------------------------------------------
 constexpr int P_BM = 128, P_BN = 256, P_STAGES = 4;
 constexpr int P_A_BYTES = P_BM * BK * 2, P_B_BYTES = P_BN * BK * 2;
 constexpr int P_SMEM = P_STAGES * (P_A_BYTES + P_B_BYTES) + 1024;
-constexpr int P_THREADS = 192;
+constexpr int P_EPI_WARPS = 8;   // two per quarter of the TMEM lanes, each takes half of the columns
+constexpr int P_THREADS = 64 + 32 * P_EPI_WARPS;
 constexpr int P_BLOCK_BYTES = 64 * BK * 2;   // one [64 K rows x 64 MN elements] box
 
 __global__ void __launch_bounds__(P_THREADS, 1)
@@ -258,6 +270,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) bf16 s_bias[2][P_BN];   // bias of the tile in accumulator buffer b
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -276,7 +289,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(&acc_full[b], 1);
-      ptx::mbar_init(&acc_empty[b], 4);
+      ptx::mbar_init(&acc_empty[b], P_EPI_WARPS);
     }
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(&tmA);
@@ -378,39 +391,63 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     __syncwarp();
   } else {
-    // ----- epilogue warps 2..5: warp w may read TMEM lanes [32 (w % 4), +32) -----
+    // ----- epilogue warps 2..9: warp w may read TMEM lanes [32 (w % 4), +32); the two warps
+    // of a quarter split the tile's columns -----
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int et = tid - 64;                   // 0..255 among the epilogue threads
+    constexpr int CH = P_BN / 32 / 2;          // 32-column chunks per warp
     const bool vec_ok = ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0);
     int lt = 0;
     for (int w = blockIdx.x; w < items; w += gridDim.x, ++lt) {
       const int t = w / p.ksplit, sp = w - t * p.ksplit;
       const int b = lt & 1;
       const int m0 = (t / tiles_n) * P_BM, n0 = (t % tiles_n) * P_BN;
+      if (p.bias != nullptr) {   // one bias value per epilogue thread, while the MMAs still run
+        const int n = n0 + et;
+        s_bias[b][et] = n < p.N ? p.bias[n] : __float2bfloat16_rn(0.f);
+      }
       bool ok = ptx::mbar_wait(&acc_full[b], ((uint32_t)(lt >> 1)) & 1u, p.spin_limit * 8, abortp);
       if (!ok && abort_flag == 0) {
         abort_flag = 1;
         report_timeout(p.status, KID_GEMM_TC, 0xFFFF);
       }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      // all epilogue threads: one shared verdict, and the bias values become visible
+      uint32_t stop;
+      asm volatile(
+          "{\n\t.reg .pred pp, qq;\n\t"
+          "setp.ne.b32 pp, %1, 0;\n\t"
+          "bar.red.or.pred qq, 1, %2, pp;\n\t"
+          "selp.b32 %0, 1, 0, qq;\n\t}"
+          : "=r"(stop)
+          : "r"((uint32_t)(!ok || abort_flag != 0)), "n"(32 * P_EPI_WARPS)
+          : "memory");
+      if (stop) break;
       ptx::tc_fence_after();
       const int gm = m0 + quarter * 32 + lane;
-#pragma unroll 1
-      for (int c = 0; c < P_BN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * P_BN + c * 32),
-                       r);
+      const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                            (uint32_t)(b * P_BN + half * (P_BN / 2));
+      uint32_t r[2][32];
+      ptx::tmem_ld32(tsrc, r[0]);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
         ptx::tmem_ld_wait();
+        if (c + 1 < CH) ptx::tmem_ld32(tsrc + (uint32_t)((c + 1) * 32), r[(c + 1) & 1]);
+        const int col = half * (P_BN / 2) + c * 32;
         if (p.ksplit == 1) {
-          store_chunk(p, gm, n0 + c * 32, r, vec_ok);
+          store_chunk(p, gm, n0 + col, r[c & 1], vec_ok,
+                      p.bias != nullptr ? &s_bias[b][col] : nullptr);
         } else if (gm < p.M) {   // raw partial sums; splitk_reduce_kernel finishes the job
-          float* dst = p.partial + ((long)sp * p.M + gm) * p.N + n0 + c * 32;
-          if (n0 + c * 32 + 32 <= p.N && (p.N & 3) == 0) {
+          float* dst = p.partial + ((long)sp * p.M + gm) * p.N + n0 + col;
+          if (n0 + col + 32 <= p.N && (p.N & 3) == 0) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+              *reinterpret_cast<uint4*>(dst + j) =
+                  make_uint4(r[c & 1][j], r[c & 1][j + 1], r[c & 1][j + 2], r[c & 1][j + 3]);
           } else {
-            for (int j = 0; j < 32 && n0 + c * 32 + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + col + j < p.N) dst[j] = __uint_as_float(r[c & 1][j]);
           }
         }
       }
