@@ -245,3 +245,21 @@ def test_weight_gradients_with_split_k_match_oracle():
         plain, _ = run_e1(inp, torch.bfloat16)
     for k in ("dW_x", "dW_h"):
         assert orc.rel_err(got[k].float().cpu(), plain[k].float().cpu()) < 5e-3, k
+
+
+@pytest.mark.parametrize("T,B,d", [(6, 48, 256), (5, 64, 256), (4, 96, 384), (5, 128, 512),
+                                   (3, 256, 512), (4, 160, 256), (3, 512, 256)])
+def test_large_batch_plans_match_oracle(T, B, d):
+    """Batches over 32 take the throughput plan (wide batch groups pipelined through the
+    resident weight tile, publisher warp, W in tensor memory when needed): forward and
+    backward against the oracle, and against the latency plan."""
+    inp = orc.make_e1_inputs(T, B, d, seed=B + d)
+    before = _lib.tc_launch_count()
+    got, ref = run_e1(inp, torch.bfloat16)
+    assert _lib.tc_launch_count() - before >= 2, "the recurrences must take the tcgen05 kernel"
+    assert _lib.device_status()[0] == 0
+    assert_close(errors(got, oracle_e1(ref)), TOL[torch.bfloat16], "throughput plan vs oracle")
+    with option("rec_large_batch", 0):
+        other, _ = run_e1(inp, torch.bfloat16)
+    for k in ("h", "output", "dx", "dz"):
+        assert orc.rel_err(got[k].float().cpu(), other[k].float().cpu()) < 1e-2, k
