@@ -158,11 +158,25 @@ class LadderLM(nn.Module):
         n = sms // blocks if blocks > 0 else 2
         return max(1, min(n, self.depth))
 
+    def _chunk_edges(self, T):
+        """Time-chunk boundaries.  `pipeline_sizes` (a list of chunk lengths summing to T)
+        overrides the uniform cut into `pipeline_chunks` chunks.  (Tapered schedules — short
+        chunks at both ends to shorten the wavefront's ramp — measured no better than the
+        uniform cut at depth 6, T = 512: the step is bound by total SM time, not by the ramp.)"""
+        sizes = getattr(self, "pipeline_sizes", None)
+        if sizes and sum(sizes) == T and all(n > 0 for n in sizes):
+            edges = [0]
+            for n in sizes:
+                edges.append(edges[-1] + int(n))
+            return edges
+        C = self.pipeline_chunks
+        return [(T * c) // C for c in range(C + 1)]
+
     def _pipelined_layers(self, h, prev_hiddens):
         from .mamba_gated_elman import ChunkLink
         B, T, _ = h.shape
-        C = self.pipeline_chunks
-        edges = [(T * c) // C for c in range(C + 1)]
+        edges = self._chunk_edges(T)
+        C = len(edges) - 1
         main = torch.cuda.current_stream(h.device)
         pre_streams, rec_streams, post_streams = self._pipeline_streams(
             h.device, self._recurrence_stream_count(h, edges[1] - edges[0]))
