@@ -59,6 +59,8 @@ SIGNATURES = {
     "elman_e5_forward": (_I, [_I, _I, _I, _I, _I, _I] + [_P] * 9 + [_P] * 3 + [_P, _Z, _P]),
     "elman_e5_backward_workspace": (_Z, [_I, _I, _I, _I, _I]),
     "elman_e5_backward": (_I, [_I, _I, _I, _I, _I] + [_P] * 10 + [_P] * 8 + [_P, _Z, _P]),
+    "elman_e5_backward_carry": (_I, [_I, _I, _I, _I, _I] + [_P] * 11 + [_P] * 9 + [_P, _Z, _P]),
+    "elman_b200_lowrank_blocks": (_I, [_I, _I, _I, _I, _I]),
     "elman_projection": (_I, [_I, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P]),
 }
 

@@ -736,6 +736,23 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, co
                       const void* x, const void* h, const void* v, const void* d_output, void* dx,
                       void* dU_h, void* dV_h, void* dU_x, void* dV_x, void* dU_z, void* dV_z,
                       void* db, void* workspace, size_t workspace_bytes, void* stream) {
+  return elman_e5_backward_carry(dtype, T, B, d, r, U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, d_output,
+                                 nullptr, dx, dU_h, dV_h, dU_x, dV_x, dU_z, dV_z, db, nullptr,
+                                 workspace, workspace_bytes, stream);
+}
+
+int elman_b200_lowrank_blocks(int dtype, int T, int B, int d, int r) {
+  if (T <= 0 || B <= 0 || d <= 0 || r <= 0 || !use_tc(dtype)) return 0;
+  return lowrank_tc_supported(T, B, d, r, 0) && lowrank_tc_supported(T, B, d, r, 1)
+             ? lowrank_tc_blocks(T, B, d, r) : 0;
+}
+
+int elman_e5_backward_carry(int dtype, int T, int B, int d, int r, const void* U_h,
+                            const void* V_h, const void* U_x, const void* V_x, const void* U_z,
+                            const void* V_z, const void* x, const void* h, const void* v,
+                            const void* d_output, const void* dv_in, void* dx, void* dU_h,
+                            void* dV_h, void* dU_x, void* dV_x, void* dU_z, void* dV_z, void* db,
+                            void* dv_out, void* workspace, size_t workspace_bytes, void* stream) {
   ELMAN_RETURN_IF(check_common(dtype, T, B, d));
   ELMAN_ARG_CHECK(r >= 1, "rank must be positive (got %d)", r);
   if (d == 0) return ELMAN_OK;
@@ -747,6 +764,13 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, co
     void* outs[6] = {dU_h, dV_h, dU_x, dV_x, dU_z, dV_z};
     for (void* p : outs) ELMAN_CUDA_CHECK(cudaMemsetAsync(p, 0, (size_t)d * r * es, st));
     ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    if (dv_out != nullptr && B > 0) {   // no steps: the carried gradient passes through
+      if (dv_in != nullptr)
+        ELMAN_CUDA_CHECK(cudaMemcpyAsync(dv_out, dv_in, (size_t)B * d * es,
+                                         cudaMemcpyDeviceToDevice, st));
+      else
+        ELMAN_CUDA_CHECK(cudaMemsetAsync(dv_out, 0, (size_t)B * d * es, st));
+    }
     return ELMAN_OK;
   }
   REQUIRE_PTR(U_h); REQUIRE_PTR(V_h); REQUIRE_PTR(U_x); REQUIRE_PTR(V_x); REQUIRE_PTR(U_z);
@@ -775,6 +799,14 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, co
   ELMAN_RETURN_IF(proj_nt(dtype, TB, d, rp, w.Vz, rp, Uz, rp, nullptr, w.gate, d, 0, st));
   ELMAN_RETURN_IF(transpose2d(dtype, d, r, U_h, w.Ut, st));  // [r,d]
   ELMAN_RETURN_IF(transpose2d(dtype, r, d, V_h, w.Vt, st));  // [d,r]
+  {  // slot T of dv: the pre-activation gradient of the step after this call's last one
+    const size_t slot = (size_t)B * d * es;
+    char* last = (char*)w.dv + (size_t)T * slot;
+    if (dv_in != nullptr)
+      ELMAN_CUDA_CHECK(cudaMemcpyAsync(last, dv_in, slot, cudaMemcpyDeviceToDevice, st));
+    else
+      ELMAN_CUDA_CHECK(cudaMemsetAsync(last, 0, slot, st));
+  }
   if (use_tc(dtype) && lowrank_tc_supported(T, B, d, r, 1)) {
     // dh_rec = (dv U) V: first product with U^T [r,d], second with V^T [d,r]
     LowRankTcArgs ta{};
@@ -789,6 +821,8 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r, const void* U_h, co
                      w.sync};
     ELMAN_RETURN_IF(lowrank_bwd_generic(dtype, a, st));
   }
+  if (dv_out != nullptr)
+    ELMAN_CUDA_CHECK(cudaMemcpyAsync(dv_out, w.dv, (size_t)B * d * es, cudaMemcpyDeviceToDevice, st));
   ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
   // rank-r activations and their gradients, all time steps at once
   ELMAN_RETURN_IF(proj_nt(dtype, TB, rp, d, x, d, Vx, d, nullptr, w.Vx, rp, 0, st));

@@ -220,6 +220,7 @@ struct LowRankTcArgs {
   int* sync;           // 256 bytes
 };
 bool lowrank_tc_supported(int T, int B, int d, int r, int bwd);
+int lowrank_tc_blocks(int T, int B, int d, int r);   // resident blocks (one cluster), 0 if unsupported
 void lowrank_tc_pad_bytes(int d, int r, size_t* up_bytes, size_t* vp_bytes);
 int lowrank_tc(const LowRankTcArgs& a, cudaStream_t stream);
 

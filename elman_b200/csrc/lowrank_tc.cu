@@ -546,6 +546,11 @@ bool lr_launchable(const LrPlan& pl) {
 
 }  // namespace
 
+int lowrank_tc_blocks(int T, int B, int d, int r) {
+  LrPlan f = lr_plan(T, B, d, r, false), b = lr_plan(T, B, d, r, true);
+  return (f.ok && b.ok) ? f.NC : 0;
+}
+
 bool lowrank_tc_supported(int T, int B, int d, int r, int bwd) {
   if (options().force_generic != 0 || lr_encode_fn() == nullptr) return false;
   LrPlan pl = lr_plan(T, B, d, r, bwd != 0);
@@ -571,10 +576,8 @@ int lowrank_tc(const LowRankTcArgs& a, cudaStream_t stream) {
   count_launch(false);
   ELMAN_CUDA_CHECK(cudaGetLastError());
   ELMAN_CUDA_CHECK(cudaMemsetAsync(a.sync, 0, 256, stream));
-  if (bwd) {  // slot T of the gradient state is the all-zero "gradient from the future"
-    ELMAN_CUDA_CHECK(cudaMemsetAsync((bf16*)a.state + (size_t)a.T * a.B * a.d, 0,
-                                     (size_t)a.B * a.d * sizeof(bf16), stream));
-  }
+  // (backward: slot T of the gradient state — the gradient carried in from later steps, or
+  // zeros — is filled by the caller)
   CUtensorMap tmU, tmState, tmIn[4], tmOut[2];
   ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmU, a.UP, (uint64_t)a.d, (uint64_t)pl.r_pad,
                                        (uint64_t)pl.r_pad, 128));

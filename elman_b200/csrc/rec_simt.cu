@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(NTHREADS) lowrank_simt_kernel(LowRankParams p)
   int step_no = 0;
   for (int s = 0; s < p.T; ++s) {
     const int t = BWD ? p.T - 1 - s : s;
-    const bool has_rec = BWD ? (t + 1 < p.T) : true;
+    const bool has_rec = true;   // backward: slot T of dv holds the carried-in gradient (or zeros)
     const T* state = BWD ? (const T*)p.dv + (long)(t + 1) * BD : (const T*)p.h + (long)t * BD;
     if (has_rec) {
       // phase A: tmp[b, q] = sum_k V[q, k] state[b, k]

@@ -375,6 +375,47 @@ def pure_lowrank_elman_backward(U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, d_output)
     return [dx, dU[0], dV[0], dU[1], dV[1], dU[2], dV[2], db]
 
 
+def pure_lowrank_elman_backward_carry(U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, d_output, dv_in=None):
+    """Backward over one time chunk -> [dx, dU_h, dV_h, dU_x, dV_x, dU_z, dV_z, db, dv_out]
+    (an extension, as mamba_gated_elman_backward_carry)."""
+    fn = "pure_lowrank_elman_backward_carry"
+    tensors = dict(U_h=U_h, V_h=V_h, U_x=U_x, V_x=V_x, U_z=U_z, V_z=V_z, x=x, h=h, v=v,
+                   d_output=d_output)
+    if dv_in is not None:
+        tensors["dv_in"] = dv_in
+    dt = _check_inputs(fn, x, **tensors)
+    T, B, d = x.shape
+    r = U_h.shape[1]
+    _shape(fn, h, (T + 1, B, d), "h"); _shape(fn, v, (T, B, d), "v")
+    _shape(fn, d_output, (T, B, d), "d_output")
+    if dv_in is not None:
+        _shape(fn, dv_in, (B, d), "dv_in")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        dx = torch.empty_like(x)
+        dU = [torch.empty(d, r, dtype=x.dtype, device=x.device) for _ in range(3)]
+        dV = [torch.empty(r, d, dtype=x.dtype, device=x.device) for _ in range(3)]
+        db = torch.empty(d, dtype=x.dtype, device=x.device)
+        dv_out = torch.empty(B, d, dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e5_backward_workspace(dt, T, B, d, r), x.device)
+        rc = lib.elman_e5_backward_carry(dt, T, B, d, r, _ptr(U_h), _ptr(V_h), _ptr(U_x), _ptr(V_x),
+                                         _ptr(U_z), _ptr(V_z), _ptr(x), _ptr(h), _ptr(v),
+                                         _ptr(d_output), _ptr(dv_in), _ptr(dx), _ptr(dU[0]),
+                                         _ptr(dV[0]), _ptr(dU[1]), _ptr(dV[1]), _ptr(dU[2]),
+                                         _ptr(dV[2]), _ptr(db), _ptr(dv_out), ws.data_ptr(),
+                                         ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [dx, dU[0], dV[0], dU[1], dV[1], dU[2], dV[2], db, dv_out]
+
+
+def lowrank_blocks(dtype, T, B, d, r):
+    """Thread blocks one E5 recurrence launch keeps resident (0: cooperative-launch kernel)."""
+    if dtype not in _DT:
+        raise RuntimeError(f"lowrank_blocks: dtype {dtype} is not supported")
+    return int(_lib.load().elman_b200_lowrank_blocks(_DT[dtype], int(T), int(B), int(d), int(r)))
+
+
 # The reference exposes the fused E5 kernels under separate names; here both
 # names run the same (already fused) path.
 pure_lowrank_elman_forward_fused = pure_lowrank_elman_forward

@@ -149,11 +149,8 @@ class LadderLM(nn.Module):
         fit on the device together: one stream per layer while that holds."""
         if self.pipeline_streams > 0:
             return self.pipeline_streams
-        from . import hasty_pytorch_lib
-        layer = self.layers[0]
-        d_inner = getattr(layer, "d_inner", self.dim)
-        blocks = hasty_pytorch_lib.recurrence_blocks(h.dtype, chunk_len, h.size(0), d_inner,
-                                                     self.pipeline_flags)
+        blocks = self.layers[0].chunk_recurrence_blocks(h.dtype, chunk_len, h.size(0),
+                                                        self.pipeline_flags)
         sms = torch.cuda.get_device_properties(h.device).multi_processor_count
         n = sms // blocks if blocks > 0 else 2
         return max(1, min(n, self.depth))
@@ -182,8 +179,8 @@ class LadderLM(nn.Module):
             h.device, self._recurrence_stream_count(h, edges[1] - edges[0]))
         shared = [layer.chunk_weights() for layer in self.layers]
         # one transposed copy per layer and pass for the backward recurrences of all chunks
-        shared_t = [w.detach().t().contiguous() if torch.is_grad_enabled() else None
-                    for w in shared]
+        shared_t = [w.detach().t().contiguous() if (w is not None and torch.is_grad_enabled())
+                    else None for w in shared]
         # time-major chunks [Tc,B,D]: the cell's own layout, so no layer transposes anything
         h_chunks = [h[:, edges[c]:edges[c + 1]].transpose(0, 1).contiguous() for c in range(C)]
         start = torch.cuda.Event()   # everything the side streams read is enqueued before this
@@ -206,7 +203,8 @@ class LadderLM(nn.Module):
             state = (torch.zeros(B, d_inner, device=h.device, dtype=h.dtype) if state is None
                      else state.detach())
             state.record_stream(sr)
-            shared[i].record_stream(sr)
+            if shared[i] is not None:
+                shared[i].record_stream(sr)
             if shared_t[i] is not None:
                 shared_t[i].record_stream(sr)
 
@@ -233,7 +231,8 @@ class LadderLM(nn.Module):
                 with torch.cuda.stream(sr):
                     sr.wait_event(pre_ev)
                     pre.record_stream(sr)
-                    z.record_stream(sr)
+                    if z is not None:
+                        z.record_stream(sr)
                     cell_out, state = layer.chunk_rec(pre, z, state, shared[i], link,
                                                       self.pipeline_flags, shared_t[i])
                     rec_ev = record(sr)

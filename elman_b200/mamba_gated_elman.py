@@ -276,6 +276,10 @@ class MambaGatedElman(nn.Module):
     def supports_time_chunks(self):
         return not self.use_conv  # the causal conv would need its own carry
 
+    def chunk_recurrence_blocks(self, dtype, T, B, flags=0):
+        """Thread blocks one recurrence launch of this layer keeps resident (0: cooperative)."""
+        return hasty_pytorch_lib.recurrence_blocks(dtype, T, B, self.d_inner, flags)
+
     def chunk_weights(self):
         """What every chunk of one forward pass shares: the effective W_h, computed once
         (the spectral-norm power iteration advances once per pass, as in forward())."""

@@ -35,6 +35,37 @@ class PureLowRankElmanFunction(torch.autograd.Function):
 PureLowRankElmanFusedFunction = PureLowRankElmanFunction
 
 
+class PureLowRankElmanChunkFunction(torch.autograd.Function):
+    """One time chunk of a longer sequence (no counterpart in the reference):
+    forward(x, h0, U_h, V_h, U_x, V_x, U_z, V_z, b) -> (output [T,B,d], h_last [B,d]).
+    As with the E1 chunk nodes, the h_last -> next chunk's h0 edge carries the
+    pre-activation gradient of the later chunk's first step backward, not dL/dh."""
+
+    @staticmethod
+    def forward(ctx, x, h0, U_h, V_h, U_x, V_x, U_z, V_z, b):
+        h, output, v = hasty_pytorch_lib.pure_lowrank_elman_forward(
+            True, x, h0, U_h, V_h, U_x, V_x, U_z, V_z, b)
+        ctx.save_for_backward(U_h, V_h, U_x, V_x, U_z, V_z, x, h, v)
+        ctx.set_materialize_grads(False)
+        return output, h[-1].clone()
+
+    @staticmethod
+    def backward(ctx, grad_output, dv_in):
+        U_h, V_h, U_x, V_x, U_z, V_z, x, h, v = ctx.saved_tensors
+        if grad_output is None:
+            grad_output = torch.zeros_like(x)
+        if x.is_cuda:
+            here = torch.cuda.current_stream(x.device)
+            grad_output.record_stream(here)
+            if dv_in is not None:
+                dv_in.record_stream(here)
+        r = hasty_pytorch_lib.pure_lowrank_elman_backward_carry(
+            U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, grad_output.contiguous(),
+            None if dv_in is None else dv_in.contiguous())
+        dx, dU_h, dV_h, dU_x, dV_x, dU_z, dV_z, db, dv_out = r
+        return dx, dv_out, dU_h, dV_h, dU_x, dV_x, dU_z, dV_z, db
+
+
 class PureLowRankElmanCell(nn.Module):
     def __init__(self, dim, rank=64, use_fused=True, use_cuda_graph=False):
         super().__init__()
@@ -85,6 +116,29 @@ class PureLowRankElman(nn.Module):
         """x: [B,T,dim] -> (output [B,T,dim], h_final [B,dim])."""
         cell_out, h_all = self.cell(x.permute(1, 0, 2).contiguous(), h0)
         return self.dropout(cell_out.permute(1, 0, 2).contiguous()), h_all[-1]
+
+    # ---- time-chunked execution (LadderLM's layer/time pipeline), time-major [Tc,B,dim] ----
+    # The layer is the cell: nothing runs before the recurrence call (which contains the
+    # low-rank projections) and only dropout after it.
+    supports_time_chunks = True
+
+    def chunk_weights(self):
+        return None
+
+    def chunk_recurrence_blocks(self, dtype, T, B, flags=0):
+        return hasty_pytorch_lib.lowrank_blocks(dtype, T, B, self.dim, self.rank)
+
+    def chunk_pre(self, x, W_h, link):
+        return x.contiguous(), None
+
+    def chunk_rec(self, pre, z, h0, W_h, link, flags=0, W_h_T=None):
+        c = self.cell
+        return PureLowRankElmanChunkFunction.apply(
+            pre, h0.contiguous(), c.U_h.contiguous(), c.V_h.contiguous(), c.U_x.contiguous(),
+            c.V_x.contiguous(), c.U_z.contiguous(), c.V_z.contiguous(), c.b.contiguous())
+
+    def chunk_post(self, cell_out):
+        return self.dropout(cell_out)
 
     def extra_repr(self):
         return (f"dim={self.dim}, rank={self.rank}, fused={self.use_fused}, "

@@ -117,6 +117,10 @@ class StockElman(nn.Module):
     def supports_time_chunks(self):
         return not self.use_conv
 
+    def chunk_recurrence_blocks(self, dtype, T, B, flags=0):
+        """Thread blocks one recurrence launch of this layer keeps resident (0: cooperative)."""
+        return hasty_pytorch_lib.recurrence_blocks(dtype, T, B, self.d_inner, flags)
+
     def chunk_weights(self):
         return self.cell.get_W_h().contiguous()
 

@@ -278,6 +278,25 @@ int elman_e5_backward(int dtype, int T, int B, int d, int r,
                       void* dU_z, void* dV_z, void* db,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * E5 backward over one time chunk of a longer sequence (an extension, as
+ * elman_e1_backward_carry): dv_in [B,d] or NULL is the following chunk's dv_out, dv_out
+ * [B,d] or NULL receives the gradient of this chunk's first pre-activation.
+ * elman_e5_backward is this function with both NULL; same workspace size.
+ */
+int elman_e5_backward_carry(int dtype, int T, int B, int d, int r,
+                            const void* U_h, const void* V_h, const void* U_x, const void* V_x,
+                            const void* U_z, const void* V_z,
+                            const void* x, const void* h, const void* v, const void* d_output,
+                            const void* dv_in,
+                            void* dx, void* dU_h, void* dV_h, void* dU_x, void* dV_x,
+                            void* dU_z, void* dV_z, void* db,
+                            void* dv_out,
+                            void* workspace, size_t workspace_bytes, void* stream);
+/* Thread blocks an E5 recurrence launch of this shape keeps resident (one cluster), or 0
+ * when the shape takes the cooperative-launch kernel; see elman_b200_recurrence_blocks. */
+int elman_b200_lowrank_blocks(int dtype, int T, int B, int d, int r);
+
 /* ---------------------------------------------------------------------------
  * Time-parallel projection  C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) (+ C).
  * This is the GEMM the reference issues through cuBLAS for W_x x_t over all t

@@ -176,16 +176,17 @@ def e5_forward(x: Tensor, h0: Tensor, U_h: Tensor, V_h: Tensor, U_x: Tensor,
 
 def e5_backward(U_h: Tensor, V_h: Tensor, U_x: Tensor, V_x: Tensor, U_z: Tensor,
                 V_z: Tensor, x: Tensor, h: Tensor, v: Tensor,
-                d_output: Tensor) -> Dict[str, Tensor]:
+                d_output: Tensor, dv_in: Tensor = None) -> Dict[str, Tensor]:
     """BPTT with the weight gradients taken as batched products over all steps
-    (the reference accumulates the same sums one step at a time)."""
+    (the reference accumulates the same sums one step at a time).  `dv_in` / "dv0":
+    the time-chunk carry, as in e1_backward (not part of the reference)."""
     T, B, d = x.shape
     x2 = x.reshape(T * B, d)
     Vz = x2 @ V_z.T                      # [TB, r]
     UVz = (Vz @ U_z.T).reshape(T, B, d)   # gate pre-activation, recomputed
     dv_all = torch.zeros_like(x)
     dg_all = torch.zeros_like(x)
-    dh_rec = torch.zeros(B, d, dtype=x.dtype)
+    dh_rec = torch.zeros(B, d, dtype=x.dtype) if dv_in is None else (dv_in @ U_h) @ V_h
     for t in range(T - 1, -1, -1):
         g = UVz[t]
         dh = d_output[t] * silu(g) + dh_rec
@@ -211,6 +212,7 @@ def e5_backward(U_h: Tensor, V_h: Tensor, U_x: Tensor, V_x: Tensor, U_z: Tensor,
         "dU_z": dg2.T @ Vz,
         "dV_z": dVz.T @ x2,
         "db": dv2.sum(0),
+        "dv0": dv_all[0] if T > 0 else dv_in,
     }
 
 

@@ -236,3 +236,52 @@ def test_pipelined_ladder_lm_level0_matches_sequential():
         assert abs(loss_pipe - loss_seq) < 2e-2 * abs(loss_seq)
         for n in g_seq:
             assert orc.rel_err(g_pipe[n].cpu(), g_seq[n].cpu()) < TOL[torch.bfloat16], n
+
+
+@pytest.mark.parametrize("dtype,T,B,d,r,edges", [
+    (torch.float32, 10, 3, 40, 6, (0, 4, 10)),
+    (torch.bfloat16, 24, 16, 256, 32, (0, 8, 9, 24)),     # single-cluster tcgen05 kernel
+    (torch.bfloat16, 12, 32, 384, 48, (0, 5, 12)),
+    (torch.bfloat16, 9, 3, 72, 10, (0, 3, 9)),            # CUDA-core bf16 kernel
+])
+def test_e5_chained_chunks_match_oracle_and_whole_sequence(dtype, T, B, d, r, edges):
+    from _gpu_cases import E5W, oracle_e5, run_e5
+    inp = orc.make_e5_inputs(T, B, d, r, seed=61)
+    dev, ref = round_inputs(inp, dtype)
+    w = [dev[k] for k in E5W]
+    state, fwd = dev["h0"], []
+    for t0, t1 in zip(edges[:-1], edges[1:]):
+        x = dev["x"][t0:t1].contiguous()
+        h, out, v = H.pure_lowrank_elman_forward(True, x, state, *w, dev["b"])
+        fwd.append((x, h, out, v))
+        state = h[-1].contiguous()
+    carry, dxs, sums = None, [], None
+    for (x, h, out, v), t0, t1 in reversed(list(zip(fwd, edges[:-1], edges[1:]))):
+        res = H.pure_lowrank_elman_backward_carry(*w, x, h, v, dev["d_output"][t0:t1].contiguous(),
+                                                  carry)
+        carry = res[8]
+        dxs.insert(0, res[0])
+        parts = [t.float() for t in res[1:8]]
+        sums = parts if sums is None else [a + b for a, b in zip(sums, parts)]
+    torch.cuda.synchronize()
+    got = {"output": torch.cat([f[2] for f in fwd]),
+           "h": torch.cat([fwd[0][1][:1]] + [f[1][1:] for f in fwd]), "dx": torch.cat(dxs)}
+    got.update(dict(zip(("dU_h", "dV_h", "dU_x", "dV_x", "dU_z", "dV_z", "db"), sums)))
+    assert_close(errors(got, oracle_e5(ref)), TOL[dtype], "E5 chunked vs oracle")
+    whole, _ = run_e5(inp, dtype)
+    for k in ("output", "h", "dx"):
+        assert torch.equal(got[k], whole[k]), k
+
+
+def test_pipelined_ladder_lm_level5_matches_sequential():
+    from elman_b200.ladder_lm import LadderLM, zipf_tokens
+    torch.manual_seed(12)
+    model = LadderLM(vocab_size=256, dim=256, depth=3, level=5, rank=32).cuda().bfloat16()
+    tokens = zipf_tokens(8, 65, seed=6).cuda()
+    loss_seq, g_seq = _lm_step(model, tokens)
+    model.pipeline_chunks = 4
+    for _ in range(2):
+        loss_pipe, g_pipe = _lm_step(model, tokens)
+        assert abs(loss_pipe - loss_seq) < 2e-2 * abs(loss_seq)
+        for n in g_seq:
+            assert orc.rel_err(g_pipe[n].cpu(), g_seq[n].cpu()) < TOL[torch.bfloat16], n

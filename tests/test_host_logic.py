@@ -83,6 +83,14 @@ class OracleBackend:
         return [g[k] for k in ("dx", "dU_h", "dV_h", "dU_x", "dV_x", "dU_z", "dV_z", "db")]
 
 
+def _e5_backward_carry(U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, d_output, dv_in=None):
+    g = orc.e5_backward(U_h, V_h, U_x, V_x, U_z, V_z, x, h, v, d_output, dv_in)
+    return [g[k] for k in ("dx", "dU_h", "dV_h", "dU_x", "dV_x", "dU_z", "dV_z", "db", "dv0")]
+
+
+OracleBackend.pure_lowrank_elman_backward_carry = staticmethod(_e5_backward_carry)
+
+
 class _CpuAsCuda(torch.Tensor):
     """A CPU tensor that answers is_cuda=True so the cells' device check passes."""
 
@@ -279,6 +287,35 @@ def test_e0_layer_chunk_pieces_equal_whole_layer(oracle_backend):
         link = e1mod.ChunkLink()
         pre, gate = layer.chunk_pre(x2[:, t0:t1].transpose(0, 1).contiguous(), W_h, link)
         cell_out, state = layer.chunk_rec(pre, gate, state, W_h, link)
+        outs.append(layer.chunk_post(cell_out).transpose(0, 1))
+    out2 = torch.cat(outs, dim=1)
+    (out2 * d_out).sum().backward()
+    assert orc.rel_err(out2, torch.Tensor(out1.detach())) < 1e-5
+    assert orc.rel_err(state, torch.Tensor(h1.detach())) < 1e-5
+    assert orc.rel_err(x2.grad, torch.Tensor(want_dx)) < 1e-5
+    for n, p_ in layer.named_parameters():
+        assert orc.rel_err(p_.grad, want[n]) < 1e-5, n
+
+
+def test_e5_layer_chunk_pieces_equal_whole_layer(oracle_backend):
+    """PureLowRankElman in time chunks (state forward, pre-activation gradient backward)
+    reproduces its own whole-sequence forward() and gradients."""
+    torch.manual_seed(4)
+    dim, B, T = 24, 2, 7
+    layer = e5mod.PureLowRankElman(dim, rank=5)
+    x1 = as_fake_cuda(torch.randn(B, T, dim)).requires_grad_(True)
+    d_out = torch.randn(B, T, dim)
+    out1, h1 = layer(x1)
+    (out1 * d_out).sum().backward()
+    want = {n: p_.grad.clone() for n, p_ in layer.named_parameters()}
+    want_dx = x1.grad.clone()
+    layer.zero_grad()
+    x2 = torch.Tensor(x1.detach().clone()).requires_grad_(True)
+    state = torch.zeros(B, dim)
+    outs = []
+    for t0, t1 in ((0, 2), (2, 3), (3, 7)):
+        pre, z = layer.chunk_pre(x2[:, t0:t1].transpose(0, 1), None, None)
+        cell_out, state = layer.chunk_rec(pre, z, state, None, None)
         outs.append(layer.chunk_post(cell_out).transpose(0, 1))
     out2 = torch.cat(outs, dim=1)
     (out2 * d_out).sum().backward()
