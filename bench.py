@@ -61,6 +61,8 @@ def parse_args():
                     help="lm workload, our arm: capture the training step (with the gradient "
                          "all-reduce for N > 1) into a CUDA graph (default); 0 = eager step, "
                          "DistributedDataParallel for N > 1")
+    ap.add_argument("--lm-level", type=int, default=1, choices=[0, 1, 5],
+                    help="lm workload: ladder level of the layers (configs[2] is level 1)")
     ap.add_argument("--time-steps", type=int, default=0,
                     help="c4 workload: sequence length instead of 2048 (small captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -446,7 +448,7 @@ def run_lm(args, rank, world, local_rank):
         mamba_gated_elman.hasty_pytorch_lib = _RefCudaBackend
     torch.manual_seed(1234)
     chunks = args.pipeline_chunks if args.impl == "ours" else 0
-    model = ladder_lm.LadderLM(vocab_size=256, dim=D, depth=6, level=1, expansion=1.0,
+    model = ladder_lm.LadderLM(vocab_size=256, dim=D, depth=6, level=args.lm_level, expansion=1.0,
                                pipeline_chunks=chunks, pipeline_streams=args.pipeline_streams)
     model = model.to(dev).bfloat16()
     net = model
@@ -509,11 +511,12 @@ def run_lm(args, rank, world, local_rank):
     if rank == 0:
         value = B * T * world * args.steps / (ms / 1e3)
         print(json.dumps({
-            "impl": args.impl, "metric": "E1 d1280x6 LM training tokens/s (B32 x T512 per GPU)",
+            "impl": args.impl,
+            "metric": f"E{args.lm_level} d1280x6 LM training tokens/s (B32 x T512 per GPU)",
             "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[2]: LadderLM level 1, d=1280, depth 6, AdamW, "
+            "config": {"workload": f"configs[2]: LadderLM level {args.lm_level}, d=1280, depth 6, AdamW, "
                                    "Zipf(1.1) tokens, data parallel" +
                                    ("" if world == 1 else
                                     " (NCCL gradient all-reduce inside the step graph)" if graphed
