@@ -284,6 +284,7 @@ int elman_b200_set_option(const char* name, long value) {
   else if (!strcmp(name, "rec_direct_publish")) o.rec_direct_publish = value;
   else if (!strcmp(name, "rec_w_tmem")) o.rec_w_tmem = value;
   else if (!strcmp(name, "rec_large_batch")) o.rec_large_batch = value;
+  else if (!strcmp(name, "rec_fin_groups")) o.rec_fin_groups = value;
   else if (!strcmp(name, "gemm_persistent")) o.gemm_persistent = value;
   else return set_error(ELMAN_ERR_ARG, "unknown option '%s'", name);
   return ELMAN_OK;
@@ -302,6 +303,7 @@ long elman_b200_get_option(const char* name) {
   if (!strcmp(name, "rec_direct_publish")) return o.rec_direct_publish;
   if (!strcmp(name, "rec_w_tmem")) return o.rec_w_tmem;
   if (!strcmp(name, "rec_large_batch")) return o.rec_large_batch;
+  if (!strcmp(name, "rec_fin_groups")) return o.rec_fin_groups;
   if (!strcmp(name, "gemm_persistent")) return o.gemm_persistent;
   return -1;
 }

@@ -44,8 +44,12 @@ constexpr int TILE_M = 128;
 constexpr int NUM_EPI_THREADS = 128;
 constexpr int NUM_MMA_WARPS = 4;
 constexpr int NUM_DRAIN_THREADS = 128;  // four warps: one per quarter of the TMEM lanes
-constexpr int NUM_THREADS =
-    32 + NUM_MMA_WARPS * 32 + NUM_DRAIN_THREADS + NUM_EPI_THREADS + 32;  // + publisher warp
+// FG = number of finalising warp groups: 1 everywhere except the throughput plan with four or
+// more batch groups, where two groups alternate over the (step, group) items.
+constexpr int threads_for(int fg) {
+  return 32 + NUM_MMA_WARPS * 32 + NUM_DRAIN_THREADS + fg * NUM_EPI_THREADS + 32;  // + publisher warp
+}
+constexpr int NUM_THREADS = threads_for(1);
 constexpr int MAX_S = 8;
 constexpr int MAX_GROUPS = 16;
 constexpr int MAX_QUADS = 2;       // batch quads (4 rows) per epilogue thread and step
@@ -154,17 +158,17 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_THREADS) : "memory");
 }
-// Barrier over the epilogue threads that also ORs a predicate: every thread gets
-// the same answer, so they can leave a loop together.
-__device__ __forceinline__ bool epi_bar_or(bool pred) {
+// Barrier over the threads of one finalising group (named barrier 1 + group) that also
+// ORs a predicate: every thread gets the same answer, so they can leave a loop together.
+__device__ __forceinline__ bool epi_bar_or(bool pred, int group) {
   uint32_t r;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.b32 p, %1, 0;\n\t"
-      "bar.red.or.pred q, 1, %2, p;\n\t"
+      "bar.red.or.pred q, %3, %2, p;\n\t"
       "selp.b32 %0, 1, 0, q;\n\t}"
       : "=r"(r)
-      : "r"((uint32_t)pred), "n"(NUM_EPI_THREADS)
+      : "r"((uint32_t)pred), "n"(NUM_EPI_THREADS), "r"(1 + group)
       : "memory");
   return r != 0;
 }
@@ -276,8 +280,8 @@ __device__ __forceinline__ void stg_u32(bf16* p, uint32_t v) {
   *reinterpret_cast<unsigned int*>(p) = v;
 }
 
-template <bool BWD>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <bool BWD, int FG>
+__global__ void __launch_bounds__(threads_for(FG), 1)
 rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmState,
               const __grid_constant__ CUtensorMap tmI0, const __grid_constant__ CUtensorMap tmI1,
               const __grid_constant__ CUtensorMap tmI2, const __grid_constant__ CUtensorMap tmI3,
@@ -295,7 +299,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   __shared__ __align__(8) uint64_t in_empty[2];       // ... and were consumed
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ float db_part[2][NUM_EPI_THREADS];
+  __shared__ float db_part[2][FG * NUM_EPI_THREADS];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int S = p.S, Kc = p.Kc, Npad = p.Npad, Ng = p.Ng, G = p.G, nmw = p.nmw;
@@ -349,7 +353,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     ptx::tmem_alloc(&tmem_slot, tmem_cols);
     ptx::tmem_relinquish();
   }
-  if (tid < NUM_EPI_THREADS) { db_part[0][tid] = 0.f; db_part[1][tid] = 0.f; }
+  if (tid < FG * NUM_EPI_THREADS) { db_part[0][tid] = 0.f; db_part[1][tid] = 0.f; }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -540,9 +544,14 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       if (tracer) stamp(p.trace, q, 5);  // partials scattered
     }
     __syncwarp();
-  } else if (warp <= NUM_MMA_WARPS + (NUM_DRAIN_THREADS + NUM_EPI_THREADS) / 32) {
+  } else if (warp <= NUM_MMA_WARPS + (NUM_DRAIN_THREADS + FG * NUM_EPI_THREADS) / 32) {
     // ============================ finalise ===================================
-    const int et = tid - (1 + NUM_MMA_WARPS) * 32 - NUM_DRAIN_THREADS;   // 0..127
+    // FG groups of four warps; group fg takes the items q with q % FG == fg.  With FG = 2 that
+    // is also the index of the double-buffered staging area, input tiles and barriers, so the
+    // groups share nothing and one finalises while the other prepares or stores.
+    const int ft = tid - (1 + NUM_MMA_WARPS) * 32 - NUM_DRAIN_THREADS;
+    const int fg = ft / NUM_EPI_THREADS;
+    const int et = ft - fg * NUM_EPI_THREADS;   // 0..127 within the group
     // finalise mapping: this thread owns the feature pair fp of my chunk for the
     // batch quads qd0, qd0 + nbq, ... (a quad = 4 consecutive batch rows)
     const int pairs = rows_own / 2;
@@ -603,7 +612,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       }
     };
 
-    for (int q = 0; q < total_q; ++q) {
+    for (int q = fg; q < total_q; q += FG) {
       const int step = q / G;
       const long base_q = block_base(q);
       const int a = q & 1;
@@ -689,7 +698,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       if (et == 0) stamp(p.trace, q, 7);  // new state stored
       // all 128 epilogue threads meet here, whether their waits succeeded or not,
       // and agree on whether to stop
-      if (epi_bar_or(!good || abort_flag != 0)) {
+      if (epi_bar_or(!good || abort_flag != 0, fg)) {
         abort_flag = 1;
         break;
       }
@@ -716,7 +725,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       if (et == 0) stamp(p.trace, q, 15);  // late outputs stored
       if (et == 0) stamp(p.trace, q, 10);  // next step's inputs requested
     }
-    if (BWD) { db_part[0][et] = db0; db_part[1][et] = db1; }
+    if (BWD) { db_part[0][ft] = db0; db_part[1][ft] = db1; }
   } else {
     // =========================== publisher ==================================
     // Waits until the four epilogue warps have stored their part of the new state
@@ -747,7 +756,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // feature tid of my chunk = pair tid/2, element tid%2, summed over the batch slots
     const int pairs = rows_own / 2;
     float ssum = 0.f;
-    for (int k = tid / 2; k < NUM_EPI_THREADS; k += pairs) ssum += db_part[tid & 1][k];
+    for (int k = tid / 2; k < FG * NUM_EPI_THREADS; k += pairs) ssum += db_part[tid & 1][k];
     p.db[i * TILE_M + (int)j * rows_own + tid] = ssum;
   }
   // no CTA may exit while a peer can still address its shared memory
@@ -819,6 +828,7 @@ int make_io_tmap(CUtensorMap* out, const void* base, int slots, int B, int d, in
 
 struct RecPlan {
   int S, Kc, G, Ng, Npad, nstages, nmw, w_tmem;
+  int fg;   // finalising warp groups (kernel instantiation)
   uint32_t tmem_cols;
   size_t smem;
   bool ok;
@@ -876,6 +886,9 @@ RecPlan plan_for(int B, int d, int S, int ng_cap, bool want_w_tmem, int nin) {
   if (plan_smem(S, Kc, Npad, nstages, w_tmem, nin) > smem_cap) return pl;
   pl.S = S; pl.Kc = Kc; pl.G = G; pl.Ng = Ng; pl.Npad = Npad; pl.nstages = nstages;
   pl.nmw = nmw; pl.tmem_cols = cols;
+  // with four or more batch groups in flight the finalising warps set the pace: two groups
+  // of them alternate (a second kernel instantiation, so the other plans keep their registers)
+  pl.fg = (G >= 4 && options().rec_fin_groups != 1) ? 2 : 1;
   pl.smem = plan_smem(S, Kc, Npad, nstages, w_tmem, nin);
   pl.ok = true;
   return pl;
@@ -884,7 +897,7 @@ RecPlan plan_for(int B, int d, int S, int ng_cap, bool want_w_tmem, int nin) {
 // Every CTA waits on every other one, so the whole grid must be resident at once:
 // ask the runtime how many clusters of this shape fit.
 bool plan_is_coresident(const RecPlan& pl, int d) {
-  auto kern = rec_tc_kernel<false>;
+  auto kern = pl.fg == 2 ? rec_tc_kernel<false, 2> : rec_tc_kernel<false, 1>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) !=
       cudaSuccess) {
     cudaGetLastError();
@@ -892,7 +905,7 @@ bool plan_is_coresident(const RecPlan& pl, int d) {
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((d / TILE_M) * pl.S);
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(threads_for(pl.fg));
   cfg.dynamicSmemBytes = pl.smem;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -915,7 +928,7 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
   RecPlan none{};
   none.ok = false;
   if (T < 1 || B < 1 || d < 128 || (d % 128) != 0) return none;
-  struct Key { int B, d, compact; long s, g, w, wt, lb; };  // compact also carries the direction
+  struct Key { int B, d, compact; long s, g, w, wt, lb, fgo; };  // compact also carries the direction
   const int nin = bwd ? 4 : 2;  // arrays the epilogue reads per step
   compact = (compact ? 1 : 0) | (bwd ? 2 : 0);
   struct Entry { Key k; RecPlan pl; };
@@ -924,11 +937,11 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
   static std::mutex cache_mutex;   // callers may come from several host threads (autograd's)
   std::lock_guard<std::mutex> lock(cache_mutex);
   const Key key{B, d, compact, options().rec_ksplit, options().rec_groups, options().rec_mma_warps,
-                options().rec_w_tmem, options().rec_large_batch};
+                options().rec_w_tmem, options().rec_large_batch, options().rec_fin_groups};
   for (int i = 0; i < ncache; ++i) {
     const Key& c = cache[i].k;
     if (c.B == key.B && c.d == key.d && c.compact == key.compact && c.s == key.s &&
-        c.g == key.g && c.w == key.w && c.wt == key.wt && c.lb == key.lb)
+        c.g == key.g && c.w == key.w && c.wt == key.wt && c.lb == key.lb && c.fgo == key.fgo)
       return cache[i].pl;
   }
   RecPlan found = none;
@@ -971,10 +984,10 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
   return found;
 }
 
-template <bool BWD>
-int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* state,
-                  cudaStream_t stream) {
-  auto kern = rec_tc_kernel<BWD>;
+template <bool BWD, int FG>
+int launch_rec_tc_fg(const RecPlan& pl, RecTcParams& p, const void* W, const void* state,
+                     cudaStream_t stream) {
+  auto kern = rec_tc_kernel<BWD, FG>;
   CUtensorMap tmW, tmState, tmI[4];
   ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmW, W, (uint64_t)p.d, (uint64_t)p.d, (uint64_t)p.d, TILE_M));
   ELMAN_RETURN_IF(make_state_tmap(&tmState, state, p.T + 1, p.B, p.d, pl.Npad, pl.Kc / 64));
@@ -992,7 +1005,7 @@ int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* 
                                         (int)pl.smem));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((p.d / TILE_M) * pl.S);
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(threads_for(FG));
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
@@ -1011,6 +1024,13 @@ int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* 
   ELMAN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmW, tmState, tmI[0], tmI[1], tmI[2], tmI[3], p));
   count_launch(true);
   return ELMAN_OK;
+}
+
+template <bool BWD>
+int launch_rec_tc(const RecPlan& pl, RecTcParams& p, const void* W, const void* state,
+                  cudaStream_t stream) {
+  if (pl.fg == 2) return launch_rec_tc_fg<BWD, 2>(pl, p, W, state, stream);
+  return launch_rec_tc_fg<BWD, 1>(pl, p, W, state, stream);
 }
 
 void fill_plan(const RecPlan& pl, RecTcParams& p) {

@@ -71,6 +71,10 @@ int elman_b200_device_status(int* detail, int clear);
  *                    modes give bit-identical results.
  *   "rec_w_tmem"     1 = keep the recurrent weight tile in tensor memory instead
  *                    of shared memory (A operand read from TMEM); bit-identical
+ *   "rec_fin_groups" 0 (default) = launches with four or more batch groups use the kernel
+ *                    instantiation with two finalising warp groups, 1 = always one group
+ *   "gemm_persistent" 0 (default) = the persistent 128x256 GEMM kernel once its tiles fill the
+ *                    SMs (and for the split-K weight gradients), 1 = never, 2 = always
  *   "rec_large_batch" 1 (default) = batches over 32 rows take the throughput plan of
  *                    the tensor-core recurrence (widest batch group first), 0 = the
  *                    latency plan for every batch size
