@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include <atomic>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -223,7 +224,12 @@ static int run_rec_fwd(int dtype, int T, int B, int d, const void* W, const void
   PhaseTimer timer(0, st);
   RecFwdArgs a{T, B, d, W, pre, g, h, y, v, sync};
   a.compact = compact;
-  if (dense_tc_ok(dtype, T, B, d, 0)) return rec_fwd_tc(a, st);
+  if (dense_tc_ok(dtype, T, B, d, 0)) {
+    // a plan that was co-resident when it was made may not be at launch time (another
+    // context holds SMs): nothing was launched then, and the CUDA-core kernel takes over
+    const int rc = rec_fwd_tc(a, st);
+    if (rc != ELMAN_ERR_UNSUPPORTED) return rc;
+  }
   return rec_fwd_generic(dtype, a, st);
 }
 
@@ -243,7 +249,10 @@ static int run_rec_bwd(int dtype, int T, int B, int d, const void* Wt, const voi
   PhaseTimer timer(1, st);
   RecBwdArgs a{T, B, d, Wt, h, v, g, dy, dv, dg, db, sync};
   a.compact = compact;
-  if (dense_tc_ok(dtype, T, B, d, 1)) return rec_bwd_tc(a, st);
+  if (dense_tc_ok(dtype, T, B, d, 1)) {
+    const int rc = rec_bwd_tc(a, st);
+    if (rc != ELMAN_ERR_UNSUPPORTED) return rc;   // see run_rec_fwd
+  }
   return rec_bwd_generic(dtype, a, st);
 }
 
@@ -286,6 +295,7 @@ int elman_b200_set_option(const char* name, long value) {
   else if (!strcmp(name, "rec_large_batch")) o.rec_large_batch = value;
   else if (!strcmp(name, "rec_fin_groups")) o.rec_fin_groups = value;
   else if (!strcmp(name, "gemm_persistent")) o.gemm_persistent = value;
+  else if (!strcmp(name, "test_stall_step")) o.test_stall_step = value;
   else return set_error(ELMAN_ERR_ARG, "unknown option '%s'", name);
   return ELMAN_OK;
 }
@@ -305,6 +315,7 @@ long elman_b200_get_option(const char* name) {
   if (!strcmp(name, "rec_large_batch")) return o.rec_large_batch;
   if (!strcmp(name, "rec_fin_groups")) return o.rec_fin_groups;
   if (!strcmp(name, "gemm_persistent")) return o.gemm_persistent;
+  if (!strcmp(name, "test_stall_step")) return o.test_stall_step;
   return -1;
 }
 
@@ -464,13 +475,18 @@ int elman_e1_forward_static(int dtype, int training, int T, int B, int d, const 
   int dev = 0;
   ELMAN_CUDA_CHECK(cudaGetDevice(&dev));
   ELMAN_ARG_CHECK(dev >= 0 && dev < kMaxDevices, "device index %d out of range", dev);
-  if (g_e1_static_scratch_ptr[dev] == nullptr) {
-    // set-up, once per device, with that device current
-    void* ptr = nullptr;
-    ELMAN_CUDA_CHECK(cudaGetSymbolAddress((void**)&ptr, g_e1_static_scratch));
-    g_e1_static_scratch_ptr[dev] = ptr;
+  void* scratch = nullptr;
+  {
+    static std::mutex setup_mutex;
+    std::lock_guard<std::mutex> lock(setup_mutex);
+    if (g_e1_static_scratch_ptr[dev] == nullptr) {
+      // set-up, once per device, with that device current
+      void* ptr = nullptr;
+      ELMAN_CUDA_CHECK(cudaGetSymbolAddress((void**)&ptr, g_e1_static_scratch));
+      g_e1_static_scratch_ptr[dev] = ptr;
+    }
+    scratch = g_e1_static_scratch_ptr[dev];
   }
-  void* scratch = g_e1_static_scratch_ptr[dev];
   cudaStream_t st = (cudaStream_t)stream;
   struct NoAllocScope {
     NoAllocScope() { g_no_alloc = true; }

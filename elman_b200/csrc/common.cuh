@@ -53,6 +53,10 @@ struct Options {
   long gemm_persistent = 0;    // 0 auto, 1 never, 2 always: the persistent 128x256 GEMM kernel
   long rec_fin_groups = 0;     // 0 auto (two finalising groups from four batch groups on), 1 = always one
   long rec_large_batch = 1;    // 1: batches over 32 take the wide-group throughput plan
+  // Failure-detection test hook: >= 1 makes thread block 0 of the tensor-core kernels wait, at
+  // that step (GEMM: K iteration), for something nothing will deliver, so that a real bounded
+  // wait runs out and the give-up path of every role executes.  -1 = off.
+  long test_stall_step = -1;
 };
 Options& options();
 void count_launch(bool tensor_core);

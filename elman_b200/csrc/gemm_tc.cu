@@ -10,12 +10,35 @@
 // warp 1 issues tcgen05.mma (M=128, N=128, K=16) into a 128-column TMEM
 // accumulator, and all four warps drain it with tcgen05.ld.  Two CTAs fit on an
 // SM, so one tile's epilogue overlaps the other's main loop.  No multicast is used.
+#include <mutex>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
 namespace elman {
 
 namespace {
+
+// Per-device host state.  A kernel's opt-in shared-memory size is a per-device (per
+// context) attribute, and callers may use several GPUs and several host threads in one
+// process: remember per device what has been set, under a lock.
+constexpr int kMaxDev = 64;
+std::mutex g_dev_mutex;
+int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return (dev >= 0 && dev < kMaxDev) ? dev : 0;
+}
+template <typename Kernel>
+int ensure_dynamic_smem(Kernel kern, int bytes, bool* done_per_device) {
+  const int dev = current_device_slot();
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!done_per_device[dev]) {
+    ELMAN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done_per_device[dev] = true;
+  }
+  return ELMAN_OK;
+}
 
 constexpr int BM = 128, BN = 128, BK = 64;
 constexpr int STAGES = 3;
@@ -35,6 +58,7 @@ struct GemmParams {
   int* status;
   int a_mn;  // A is given as [K, M] (M contiguous): MN-major operand, no transpose pass
   int b_mn;  // W is given as [K, N] (N contiguous)
+  int stall_step = -1;        // test hook: block 0 arms a stage at this K iteration but loads nothing
   int ksplit = 1;             // persistent kernel: K range cut into this many work items per tile
   float* partial = nullptr;   // [ksplit][M][N] fp32 partial sums when ksplit > 1
 };
@@ -165,6 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           break;
         }
         ptx::mbar_arrive_expect_tx(&full_bar[s], A_TILE_BYTES + B_TILE_BYTES);
+        if (i == p.stall_step && blockIdx.x == 0 && blockIdx.y == 0) continue;
         if (p.a_mn) {  // two boxes of [64 K rows x 64 M elements]
           ptx::tma_load_2d(sA + s * A_TILE_BYTES, &tmA, m0, i * BK, &full_bar[s]);
           ptx::tma_load_2d(sA + s * A_TILE_BYTES + A_TILE_BYTES / 2, &tmA, m0 + 64, i * BK,
@@ -323,6 +348,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           ptx::mbar_arrive_expect_tx(&full_bar[s], P_A_BYTES + P_B_BYTES);
+          if (it == p.stall_step && blockIdx.x == 0) continue;
           if (p.a_mn) {
 #pragma unroll
             for (int blk = 0; blk < P_BM / 64; ++blk)
@@ -577,17 +603,14 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
       q.M = M; q.N = N; q.K = K;
       q.bias = bias; q.C = C; q.ldc = ldc; q.c_is_f32 = c_is_f32; q.accumulate = accumulate;
       q.spin_limit = options().spin_limit;
+      q.stall_step = (int)options().test_stall_step;
       q.status = device_status_ptr();
       q.a_mn = a_mn; q.b_mn = b_mn;
       return gemm_tc_persistent(M, N, K, A, lda, a_mn, W, ldw, b_mn, q, stream);
     }
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    ELMAN_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          GEMM_SMEM));
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDev] = {false};
+  ELMAN_RETURN_IF(ensure_dynamic_smem(gemm_tc_kernel, GEMM_SMEM, attr_set));
   CUtensorMap tmA, tmB;
   if (a_mn)
     ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK));
@@ -601,6 +624,7 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
   p.M = M; p.N = N; p.K = K;
   p.bias = bias; p.C = C; p.ldc = ldc; p.c_is_f32 = c_is_f32; p.accumulate = accumulate;
   p.spin_limit = options().spin_limit;
+  p.stall_step = (int)options().test_stall_step;
   p.status = device_status_ptr();
   p.a_mn = a_mn; p.b_mn = b_mn;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
@@ -611,29 +635,27 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
 }
 
 namespace {
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+int sm_count() {   // of the current device
+  static int cached[kMaxDev] = {0};
+  const int dev = current_device_slot();
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = 148;
     }
+    cached[dev] = n;
   }
-  return n;
+  return cached[dev];
 }
 }  // namespace
 
 // The persistent 128x256 kernel: worth it once there is at least about one tile per SM.
 int gemm_tc_persistent(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
                        int b_mn, const GemmParams& p, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    ELMAN_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_persistent_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM));
-    attr_set = true;
-  }
+  static bool attr_set[kMaxDev] = {false};
+  ELMAN_RETURN_IF(ensure_dynamic_smem(gemm_tc_persistent_kernel, P_SMEM, attr_set));
   CUtensorMap tmA, tmB;
   if (a_mn)
     ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK));

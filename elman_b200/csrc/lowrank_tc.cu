@@ -53,6 +53,7 @@ struct LowRankTcParams {
   int* abort_word;
   int* status;
   long spin_limit;
+  int stall_step;   // test hook: block 0 withholds its share of the rank vector at this step (-1 off)
 };
 
 // Barrier over the 128 epilogue threads that also ORs a predicate.
@@ -318,7 +319,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
       // barrier also orders last step's bulk-store reads before this step's tile writes
       if (lr_bar_or(!good || abort_flag != 0)) { abort_flag = 1; break; }
       // ---- owner: all-gather my bf16 chunk into every CTA's phase-2 operand tile ----
-      if (is_owner && et < Npad * 4) {
+      if (is_owner && et < Npad * 4 && !(s == p.stall_step && c == 0)) {
         const int b = et >> 2, ch = et & 3;
         const uint4 v = lds_u4(gather_a + (uint32_t)(b * 64 + ch * 16));
         const uint32_t off = (uint32_t)((c >> 1) * h_tile + b * 128 + (((((c & 1) << 2) + ch) ^ (b & 7)) << 4));
@@ -601,6 +602,7 @@ int lowrank_tc(const LowRankTcArgs& a, cudaStream_t stream) {
   p.abort_word = a.sync;
   p.status = device_status_ptr();
   p.spin_limit = options().spin_limit;
+  p.stall_step = (int)options().test_stall_step;
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr;
   if (bwd) {

@@ -31,7 +31,9 @@
 // returns with tensor memory freed.
 #include <cooperative_groups.h>
 
+#include <map>
 #include <mutex>
+#include <tuple>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -80,6 +82,7 @@ struct RecTcParams {
   int* abort_word;  // global abort flag
   int* status;
   long spin_limit;
+  int stall_step;     // test hook: block 0 waits at this step for a count nobody publishes (-1 off)
   long long* trace;   // optional [TRACE_STEPS][TRACE_SLOTS] cycle stamps of CTA 0, or null
 };
 
@@ -420,7 +423,8 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         ok = ok && waiter.wait(&empty_bar[s], ph ^ 1u);
         if (ok && step > 0)
           ok = waiter.wait_counter(p.ready + (grp * MAX_S + (int)j) * COUNTER_STRIDE,
-                                   step * p.R * (p.direct_publish ? NUM_EPI_THREADS / 32 : 1));
+                                   step * p.R * (p.direct_publish ? NUM_EPI_THREADS / 32 : 1) +
+                                       ((step == p.stall_step && blockIdx.x == 0) ? (1 << 28) : 0));
         if (!ok) {
           if (atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, kid, step);
           abort_flag = 1;
@@ -896,8 +900,25 @@ RecPlan plan_for(int B, int d, int S, int ng_cap, bool want_w_tmem, int nin) {
 
 // Every CTA waits on every other one, so the whole grid must be resident at once:
 // ask the runtime how many clusters of this shape fit.
-bool plan_is_coresident(const RecPlan& pl, int d) {
-  auto kern = pl.fg == 2 ? rec_tc_kernel<false, 2> : rec_tc_kernel<false, 1>;
+// One lock for everything that touches the kernels' per-device attributes: the planner's
+// occupancy queries and the set-attribute + launch pair of a launch (a second host thread
+// must not change the shared-memory attribute between the two).
+std::mutex g_rec_mutex;
+
+template <typename Kernel>
+bool kernel_is_coresident(Kernel kern, const RecPlan& pl, int d);
+
+bool plan_is_coresident(const RecPlan& pl, int d, bool bwd) {
+  // the instantiation that will be launched: registers, and so occupancy, differ
+  if (bwd)
+    return pl.fg == 2 ? kernel_is_coresident(rec_tc_kernel<true, 2>, pl, d)
+                      : kernel_is_coresident(rec_tc_kernel<true, 1>, pl, d);
+  return pl.fg == 2 ? kernel_is_coresident(rec_tc_kernel<false, 2>, pl, d)
+                    : kernel_is_coresident(rec_tc_kernel<false, 1>, pl, d);
+}
+
+template <typename Kernel>
+bool kernel_is_coresident(Kernel kern, const RecPlan& pl, int d) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) !=
       cudaSuccess) {
     cudaGetLastError();
@@ -928,21 +949,21 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
   RecPlan none{};
   none.ok = false;
   if (T < 1 || B < 1 || d < 128 || (d % 128) != 0) return none;
-  struct Key { int B, d, compact; long s, g, w, wt, lb, fgo; };  // compact also carries the direction
   const int nin = bwd ? 4 : 2;  // arrays the epilogue reads per step
-  compact = (compact ? 1 : 0) | (bwd ? 2 : 0);
-  struct Entry { Key k; RecPlan pl; };
-  static Entry cache[32];
-  static int ncache = 0;
-  static std::mutex cache_mutex;   // callers may come from several host threads (autograd's)
-  std::lock_guard<std::mutex> lock(cache_mutex);
-  const Key key{B, d, compact, options().rec_ksplit, options().rec_groups, options().rec_mma_warps,
-                options().rec_w_tmem, options().rec_large_batch, options().rec_fin_groups};
-  for (int i = 0; i < ncache; ++i) {
-    const Key& c = cache[i].k;
-    if (c.B == key.B && c.d == key.d && c.compact == key.compact && c.s == key.s &&
-        c.g == key.g && c.w == key.w && c.wt == key.wt && c.lb == key.lb && c.fgo == key.fgo)
-      return cache[i].pl;
+  compact = (compact ? 1 : 0) | (bwd ? 2 : 0);   // also carries the direction
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = 0; }
+  // co-residency depends on the device; callers may come from several host threads
+  // (autograd's) and use several GPUs
+  typedef std::tuple<int, int, int, int, long, long, long, long, long, long> Key;
+  static std::map<Key, RecPlan> cache;
+  std::lock_guard<std::mutex> lock(g_rec_mutex);
+  const Key key(dev, B, d, compact, options().rec_ksplit, options().rec_groups,
+                options().rec_mma_warps, options().rec_w_tmem, options().rec_large_batch,
+                options().rec_fin_groups);
+  {
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
   }
   RecPlan found = none;
   const long want_S = options().rec_ksplit;
@@ -953,7 +974,7 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
       if (want_S > 0 && S != want_S) continue;
       for (int wt = 0; wt <= 1 && !found.ok; ++wt) {
         RecPlan pl = plan_for(B, d, S, 32, wt != 0, nin);
-        if (pl.ok && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d)) found = pl;
+        if (pl.ok && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d, bwd)) found = pl;
       }
     }
   } else if (B <= 32 || options().rec_groups > 0 || options().rec_large_batch == 0) {
@@ -962,7 +983,7 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
       if (want_S > 0 && S != want_S) continue;
       for (int ng_cap = 32; ng_cap >= 16 && !found.ok; ng_cap >>= 1) {
         RecPlan pl = plan_for(B, d, S, ng_cap, options().rec_w_tmem != 0, nin);
-        if (pl.ok && plan_is_coresident(pl, d)) found = pl;
+        if (pl.ok && plan_is_coresident(pl, d, bwd)) found = pl;
       }
     }
   } else {
@@ -975,12 +996,12 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
         for (int wt = 0; wt <= 1 && !found.ok; ++wt) {
           if (wt == 0 && options().rec_w_tmem != 0) continue;
           RecPlan pl = plan_for(B, d, S, ng_cap, wt != 0, nin);
-          if (pl.ok && pl.Ng > ng_cap / 2 && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d))
+          if (pl.ok && pl.Ng > ng_cap / 2 && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d, bwd))
             found = pl;
         }
       }
   }
-  if (ncache < 32) cache[ncache++] = Entry{key, found};
+  cache[key] = found;
   return found;
 }
 
@@ -1001,6 +1022,7 @@ int launch_rec_tc_fg(const RecPlan& pl, RecTcParams& p, const void* W, const voi
     for (int k = 0; k < 4; ++k)
       ELMAN_RETURN_IF(make_io_tmap(&tmI[k], ins[k], slots[k], p.B, p.d, TILE_M / pl.S, pl.Npad));
   }
+  std::lock_guard<std::mutex> lock(g_rec_mutex);   // set-attribute and launch as one unit
   ELMAN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)pl.smem));
   cudaLaunchConfig_t cfg{};
@@ -1041,6 +1063,7 @@ void fill_plan(const RecPlan& pl, RecTcParams& p) {
   p.w_col0 = (uint32_t)(2 * pl.nmw * pl.Npad);
   p.R = p.d / TILE_M;
   p.spin_limit = options().spin_limit;
+  p.stall_step = (int)options().test_stall_step;
   p.status = device_status_ptr();
 }
 

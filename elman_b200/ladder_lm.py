@@ -149,8 +149,9 @@ class LadderLM(nn.Module):
         fit on the device together: one stream per layer while that holds."""
         if self.pipeline_streams > 0:
             return self.pipeline_streams
-        blocks = self.layers[0].chunk_recurrence_blocks(h.dtype, chunk_len, h.size(0),
-                                                        self.pipeline_flags)
+        # layers may differ in width and plan: the widest launch decides
+        blocks = max(layer.chunk_recurrence_blocks(h.dtype, chunk_len, h.size(0),
+                                                   self.pipeline_flags) for layer in self.layers)
         sms = torch.cuda.get_device_properties(h.device).multi_processor_count
         n = sms // blocks if blocks > 0 else 2
         return max(1, min(n, self.depth))

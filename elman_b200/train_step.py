@@ -13,6 +13,20 @@ no host synchronisation inside the model (LadderLM has none).
 import torch
 
 
+def raise_on_device_timeout(where="a replayed step"):
+    """Bounded device-side waits that give up are reported through a host-mapped status
+    word.  The library's entry points read it when they are called, but a graph replay calls
+    none of them: read it here (a plain host load, no synchronisation) and raise, so that the
+    optimizer never keeps stepping on the results of a launch that gave up."""
+    from . import _lib
+    code, detail = _lib.device_status()
+    if code != 0:
+        raise _lib.ElmanB200Error(
+            f"{where}: an earlier launch gave up a bounded device-side wait "
+            f"(kernel {(detail >> 24) & 0xFF}, step {detail & 0xFFFFFF}); its results, and every "
+            "step replayed since, are invalid")
+
+
 class GraphedTrainStep:
     def __init__(self, net, optimizer, example_tokens, max_grad_norm=1.0, autocast_dtype=None,
                  warmup_steps=3, after_backward=None):
@@ -59,9 +73,16 @@ class GraphedTrainStep:
     def __call__(self, tokens):
         """Copies `tokens` (host or device) into the captured input and replays the step.
         Returns the captured loss tensor (valid until the next call)."""
+        raise_on_device_timeout("GraphedTrainStep")   # covers every replay up to the last one
         self.tokens.copy_(tokens, non_blocking=True)
         self.graph.replay()
         return self.loss
+
+    def loss_value(self):
+        """The last step's loss on the host; raises if any launch of it gave up a wait."""
+        value = float(self.loss)          # synchronises with the replay
+        raise_on_device_timeout("GraphedTrainStep.loss_value")
+        return value
 
 
 def allreduce_gradients(params, group=None):

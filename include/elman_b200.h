@@ -78,6 +78,12 @@ int elman_b200_device_status(int* detail, int clear);
  *   "rec_large_batch" 1 (default) = batches over 32 rows take the throughput plan of
  *                    the tensor-core recurrence (widest batch group first), 0 = the
  *                    latency plan for every batch size
+ *   "test_stall_step" failure-detection test hook, -1 (default) = off.  With a value k >= 1
+ *                    thread block 0 of the next tensor-core launches (recurrences: at time
+ *                    step k; projection GEMMs: at K iteration k) waits for something that
+ *                    nothing delivers.  The wait runs out after "spin_limit" polls, the
+ *                    kernel records ELMAN_ERR_TIMEOUT in the status word, every block gives
+ *                    up and the launch returns; its results are invalid.  Nothing faults.
  * Returns ELMAN_OK or ELMAN_ERR_ARG for an unknown name.
  */
 int elman_b200_set_option(const char* name, long value);

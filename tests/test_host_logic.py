@@ -324,3 +324,29 @@ def test_e5_layer_chunk_pieces_equal_whole_layer(oracle_backend):
     assert orc.rel_err(x2.grad, torch.Tensor(want_dx)) < 1e-5
     for n, p_ in layer.named_parameters():
         assert orc.rel_err(p_.grad, want[n]) < 1e-5, n
+
+
+def test_graphed_step_raises_when_the_status_word_reports_a_timeout(monkeypatch):
+    """A graph replay calls no library entry point, so nothing else would look at the status
+    word: the step wrapper reads it and raises."""
+    from elman_b200 import _lib, train_step
+    monkeypatch.setattr(_lib, "device_status", lambda clear=False: (0, 0))
+    train_step.raise_on_device_timeout()          # clean: no exception
+    monkeypatch.setattr(_lib, "device_status", lambda clear=False: (3, (3 << 24) | 17))
+    with pytest.raises(_lib.ElmanB200Error, match="kernel 3, step 17"):
+        train_step.raise_on_device_timeout()
+
+    class _Graph:
+        replays = 0
+
+        def replay(self):
+            self.replays += 1
+
+    step = train_step.GraphedTrainStep.__new__(train_step.GraphedTrainStep)
+    step.tokens, step.graph, step.loss = torch.zeros(2), _Graph(), torch.tensor(1.0)
+    with pytest.raises(_lib.ElmanB200Error):
+        step(torch.ones(2))
+    assert step.graph.replays == 0                # the poisoned step was not replayed
+    monkeypatch.setattr(_lib, "device_status", lambda clear=False: (0, 0))
+    step(torch.ones(2))
+    assert step.graph.replays == 1 and step.loss_value() == 1.0
