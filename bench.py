@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--time-steps", type=int, default=0,
                     help="c4 workload: sequence length instead of 2048 (small captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sub-records", action="store_true",
+                    help="skip the reference_cuda and lm sub-records of the default line")
     ap.add_argument("--cpu-seconds", type=float, default=12.0,
                     help="CPU work to spend on the cpu_baseline leg (whole passes, at least 2)")
     ap.add_argument("--cpu-sample-steps", type=int, default=0,
@@ -254,18 +256,13 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def run_reference_cuda(args, rank, local_rank):
+def measure_reference_cuda_cell(inp, steps, warmup):
     """The reference's unmodified CUDA kernels (cuBLAS GEMM + elementwise kernels per time
-    step) on the same GPU and inputs; prints the same JSON line with impl=reference_cuda."""
-    if rank != 0:
-        return
+    step, rebuilt for sm_100 into oracle/_ref) on the current GPU and the given inputs.
+    Returns {"ms_per_step", "value"} or {"unavailable": why}."""
     from oracle import ref_cuda
     if not (torch.cuda.is_available() and ref_cuda.available()):
-        print(json.dumps({"impl": "reference_cuda",
-                          "unavailable": "oracle/_ref/libelman_ref_cuda.so not built or no GPU"}))
-        return
-    torch.cuda.set_device(local_rank)
-    inp = make_inputs(1234)
+        return {"unavailable": "oracle/_ref/libelman_ref_cuda.so not built or no GPU"}
     d = {k: v.to(torch.bfloat16).cuda().contiguous() for k, v in inp.items()}
     flush_buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
 
@@ -273,23 +270,37 @@ def run_reference_cuda(args, rank, local_rank):
         h, out, v, _ = ref_cuda.e1_forward(True, d["x"], d["z"], d["h0"], d["W_x"], d["W_h"], d["b"])
         return ref_cuda.e1_backward(d["W_x"], d["W_h"], d["x"], d["z"], h, v, d["d_output"])
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
     torch.cuda.synchronize()
     total = 0.0
-    for _ in range(args.steps):
+    for _ in range(steps):
         flush_buf.zero_()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record(); step(); e.record(); e.synchronize()
         total += s.elapsed_time(e)
-    value = B * T * args.steps / (total / 1e3)
+    return {"ms_per_step": total / steps, "value": B * T * steps / (total / 1e3), "unit": UNIT,
+            "steps": steps,
+            "what": "reference kernels (elman/cuda/lib, unmodified) compiled for sm_100, same "
+                    "inputs, same GPU, L2 flushed between iterations"}
+
+
+def run_reference_cuda(args, rank, local_rank):
+    """Prints the headline JSON line for the reference's own CUDA kernels (impl=reference_cuda)."""
+    if rank != 0:
+        return
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local_rank)
+    rec = measure_reference_cuda_cell(make_inputs(1234), args.steps, args.warmup)
+    if "unavailable" in rec:
+        print(json.dumps({"impl": "reference_cuda", "unavailable": rec["unavailable"]}))
+        return
     print(json.dumps({
-        "impl": "reference_cuda", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total / args.steps,
+        "impl": "reference_cuda", "metric": METRIC, "value": rec["value"], "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": rec["ms_per_step"],
         "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "configs[1]: E1 cell fwd+bwd, bf16, d=1280, B=32, T=512",
-                   "what": "reference kernels (elman/cuda/lib, unmodified) compiled for sm_100"}}),
-        flush=True)
+                   "what": rec["what"]}}), flush=True)
 
 
 class _RefCudaBackend:
@@ -426,114 +437,138 @@ def run_c4(args, rank, world, local_rank):
             "device_status": _lib.device_status()[0]}), flush=True)
 
 
-def run_lm(args, rank, world, local_rank):
+def measure_lm(args, rank, world, local_rank, impl, steps, warmup):
     """configs[2]: full E1 byte-level LM (d=1280 x 6 layers, 49.5M parameters), bf16, AdamW,
     T=512, 32 sequences per GPU, seeded Zipf(1.1) token ids; one step = forward, loss,
-    backward, gradient clipping, optimizer step; data-parallel with DDP over NCCL for N > 1."""
+    backward, gradient all-reduce (N > 1), gradient clipping, optimizer step.  Every step's
+    tokens come from pinned host memory and the loss is read back at the end of the timed
+    region.  The process group, if any, must exist already.  Returns the record (rank 0) or
+    None; the step graph is released before returning."""
     import torch.distributed as dist
     from elman_b200 import _lib
     from elman_b200 import ladder_lm, mamba_gated_elman
 
-    torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")  # required to capture NCCL
-        dist.init_process_group(backend="nccl", device_id=dev)
-    if args.impl == "reference_cuda":
+    saved_backend = mamba_gated_elman.hasty_pytorch_lib
+    if impl == "reference_cuda":
         from oracle import ref_cuda
         if not ref_cuda.available():
-            if rank == 0:
-                print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref not built"}))
-            return
+            return {"unavailable": "oracle/_ref not built"} if rank == 0 else None
         mamba_gated_elman.hasty_pytorch_lib = _RefCudaBackend
-    torch.manual_seed(1234)
-    chunks = args.pipeline_chunks if args.impl == "ours" else 0
-    model = ladder_lm.LadderLM(vocab_size=256, dim=D, depth=6, level=args.lm_level, expansion=1.0,
-                               pipeline_chunks=chunks, pipeline_streams=args.pipeline_streams)
-    model = model.to(dev).bfloat16()
-    net = model
-    graphed = args.impl == "ours" and args.cuda_graph != 0
-    if world > 1 and not graphed:
-        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank],
-                                                        find_unused_parameters=False)
-    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
-                            capturable=graphed)
-    host_tokens = ladder_lm.zipf_tokens(B, T + 1, seed=1234 + rank).pin_memory()
-    if graphed:
-        from elman_b200.train_step import GraphedTrainStep
-        from elman_b200.train_step import allreduce_gradients
-        if world > 1:  # same initial weights on every rank; gradients averaged inside the graph
-            for p_ in model.parameters():
-                dist.broadcast(p_.data, src=0)
-        gstep = GraphedTrainStep(net, opt, host_tokens.to(dev), max_grad_norm=1.0,
-                                 autocast_dtype=torch.bfloat16,
-                                 after_backward=allreduce_gradients if world > 1 else None)
-
-    def step():
+    try:
+        torch.manual_seed(1234)
+        chunks = args.pipeline_chunks if impl == "ours" else 0
+        model = ladder_lm.LadderLM(vocab_size=256, dim=D, depth=6, level=args.lm_level,
+                                   expansion=1.0, pipeline_chunks=chunks,
+                                   pipeline_streams=args.pipeline_streams)
+        model = model.to(dev).bfloat16()
+        net = model
+        graphed = impl == "ours" and args.cuda_graph != 0
+        if world > 1 and not graphed:
+            net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank],
+                                                            find_unused_parameters=False)
+        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
+                                capturable=graphed)
+        host_tokens = ladder_lm.zipf_tokens(B, T + 1, seed=1234 + rank).pin_memory()
+        gstep = None
+        reducer = None
         if graphed:
-            return gstep(host_tokens)
-        tok = host_tokens.to(dev, non_blocking=True)
-        opt.zero_grad(set_to_none=True)
-        with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
-            loss = net(tok, return_loss=True)
-        loss.backward()
-        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
-        opt.step()
-        return loss
+            from elman_b200 import train_step
+            if world > 1:  # same initial weights on every rank; gradients averaged inside the graph
+                for p_ in model.parameters():
+                    dist.broadcast(p_.data, src=0)
+                reducer = train_step.make_gradient_reducer(model)
+            gstep = train_step.GraphedTrainStep(net, opt, host_tokens.to(dev), max_grad_norm=1.0,
+                                                autocast_dtype=torch.bfloat16, reducer=reducer)
 
-    def barrier():
+        def step():
+            if graphed:
+                return gstep(host_tokens)
+            tok = host_tokens.to(dev, non_blocking=True)
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+                loss = net(tok, return_loss=True)
+            loss.backward()
+            torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+            opt.step()
+            return loss
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        for _ in range(max(warmup, 3)):
+            step()
+        barrier()
+        launches0 = _lib.launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler.begin()
+        ev0.record()
+        for _ in range(steps):
+            loss = step()
+        ev1.record()
+        loss_val = float(loss.detach())  # device -> host read of the step's result
+        barrier()
+        sampler.end()
+        clocks = sampler.stop() if rank == 0 else None
+        status = _lib.device_status()[0]
+        ms = ev0.elapsed_time(ev1)
+        t_all = torch.tensor([ms], dtype=torch.float64, device=dev)
         if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    launches0 = _lib.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.begin()
-    ev0.record()
-    for _ in range(args.steps):
-        loss = step()
-    ev1.record()
-    loss_val = float(loss.detach())  # device -> host read of the step's result
-    barrier()
-    sampler.end()
-    clocks = sampler.stop() if rank == 0 else None
-    ms = ev0.elapsed_time(ev1)
-    t_all = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
-    ms = float(t_all.cpu())
-    if rank == 0:
-        value = B * T * world * args.steps / (ms / 1e3)
-        print(json.dumps({
-            "impl": args.impl,
-            "metric": f"E{args.lm_level} d1280x6 LM training tokens/s (B32 x T512 per GPU)",
-            "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"configs[2]: LadderLM level {args.lm_level}, d=1280, depth 6, AdamW, "
-                                   "Zipf(1.1) tokens, data parallel" +
-                                   ("" if world == 1 else
-                                    " (NCCL gradient all-reduce inside the step graph)" if graphed
-                                    else " (DistributedDataParallel over NCCL)"),
-                       "params": model.get_num_params(),
-                       "pipeline_chunks": chunks, "cuda_graph": bool(graphed)},
-            "final_loss": loss_val, "clocks": clocks,
-            "gpu_launches": (gstep.library_launches_per_step * args.steps if graphed
-                             else _lib.launch_count() - launches0)}), flush=True)
-    if world > 1:
+            dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+        ms = float(t_all.cpu())
+        rec = None
+        if rank == 0:
+            rec = {
+                "impl": impl,
+                "metric": f"E{args.lm_level} d1280x6 LM training tokens/s (B32 x T512 per GPU)",
+                "value": B * T * world * steps / (ms / 1e3), "unit": UNIT, "n_gpus": world,
+                "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms / steps,
+                "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"configs[2]: LadderLM level {args.lm_level}, d=1280, depth 6, "
+                                       "AdamW, Zipf(1.1) tokens from pinned host memory each step, "
+                                       "data parallel",
+                           "params": model.get_num_params(),
+                           "pipeline_chunks": chunks, "cuda_graph": bool(graphed)},
+                "allreduce": (None if world == 1 else
+                              (reducer.describe() if reducer is not None else
+                               "DistributedDataParallel over NCCL")),
+                "final_loss": loss_val, "clocks": clocks, "device_status": status,
+                "gpu_launches": (gstep.library_launches_per_step * steps if graphed
+                                 else _lib.launch_count() - launches0)}
         if graphed:
             # NCCL cannot tear a communicator down while a CUDA graph that captured its
-            # kernels is alive: release the graph first, and never let teardown hang the run
+            # kernels is alive: release the graph before anybody destroys the group
             gstep.graph = None
             gstep = None
-            import gc
-            gc.collect()
+        del model, net, opt
+        import gc
+        gc.collect()
+        torch.cuda.synchronize()
+        return rec
+    finally:
+        mamba_gated_elman.hasty_pytorch_lib = saved_backend
+
+
+def init_process_group(world, local_rank):
+    import torch.distributed as dist
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "0")  # required to capture NCCL
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+
+
+def run_lm(args, rank, world, local_rank):
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    init_process_group(world, local_rank)
+    rec = measure_lm(args, rank, world, local_rank, args.impl, args.steps, args.warmup)
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    if world > 1:
         torch.cuda.synchronize()
         dist.barrier()
         _destroy_process_group_bounded(20.0)
@@ -584,8 +619,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group(backend="nccl", device_id=dev)
+    init_process_group(world, local_rank)
 
     inp = make_inputs(1234 + rank)
     host = {k: v.to(torch.bfloat16).contiguous().pin_memory() for k, v in inp.items()}
@@ -693,6 +727,28 @@ def main():
         dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms, e2e_serial_ms = (float(v) for v in t_all.cpu())
 
+    # Beside the headline, outside its timed region (as the CPU baseline is): the same cell
+    # through the reference's own CUDA kernels on this GPU (rank 0), and the configs[2] LM
+    # training step on all N ranks, with its gradient all-reduce — the workload that has a
+    # collective — plus, at N = 1, the same LM step through the reference's kernels.
+    del pipe, res
+    sub = {}
+    if not args.no_sub_records:
+        if rank == 0:
+            sub["reference_cuda"] = measure_reference_cuda_cell(inp, min(args.steps, 10), 3)
+        lm_steps = max(5, min(args.steps, 20))
+        lm = measure_lm(args, rank, world, local_rank, "ours", lm_steps, 3)
+        if rank == 0 and lm is not None:
+            keep = ("ms_per_step", "value", "unit", "n_gpus", "steps", "allreduce", "clocks",
+                    "final_loss", "gpu_launches", "device_status", "config")
+            sub["lm"] = {k: lm[k] for k in keep if k in lm}
+            if world == 1:
+                ref_lm = measure_lm(args, rank, world, local_rank, "reference_cuda", 5, 3)
+                sub["lm"]["reference_cuda_ms_per_step"] = (
+                    ref_lm.get("ms_per_step") if ref_lm else None)
+                if ref_lm and "unavailable" in ref_lm:
+                    sub["lm"]["reference_cuda_unavailable"] = ref_lm["unavailable"]
+
     if rank == 0:
         tokens = B * T * world * args.steps
         value = tokens / (total_ms / 1e3)
@@ -703,7 +759,9 @@ def main():
         dom = "fwd" if rec_fwd_ms >= rec_bwd_ms else "bwd"
         dom_ms = max(rec_fwd_ms, rec_bwd_ms)
         rec_flops = 2.0 * T * B * D * D               # per launch of either recurrence kernel
-        rec_bytes = 5.0 * B * D * 2 * T               # algorithmic HBM bytes per launch
+        # algorithmic HBM bytes per launch: forward reads pre, z and writes h, v, y;
+        # backward reads h, v, z, dy and writes dv, dz
+        rec_bytes = (6.0 if dom == "bwd" else 5.0) * B * D * 2 * T
         achieved_tf = rec_flops / (dom_ms / 1e3) / 1e12 if dom_ms > 0 else 0.0
         peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
         roofline = {
@@ -743,6 +801,7 @@ def main():
                           "recurrence_bwd_us_per_step": rec_bwd_ms * 1e3 / T},
             "wall_s_timed_region": wall,
         }
+        line.update(sub)
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
@@ -763,8 +822,9 @@ def main():
         print(json.dumps(line), flush=True)
 
     if world > 1:
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        _destroy_process_group_bounded(20.0)
 
 
 if __name__ == "__main__":
