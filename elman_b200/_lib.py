@@ -61,6 +61,12 @@ SIGNATURES = {
     "elman_e5_backward": (_I, [_I, _I, _I, _I, _I] + [_P] * 10 + [_P] * 8 + [_P, _Z, _P]),
     "elman_e5_backward_carry": (_I, [_I, _I, _I, _I, _I] + [_P] * 11 + [_P] * 9 + [_P, _Z, _P]),
     "elman_b200_lowrank_blocks": (_I, [_I, _I, _I, _I, _I]),
+    "elman_add_rmsnorm_backward_workspace": (_Z, [_I]),
+    "elman_add_rmsnorm_forward": (_I, [_I, _L, _I, _P, _P, _P, _c.c_float, _P, _P, _P, _P]),
+    "elman_add_rmsnorm_backward": (_I, [_I, _L, _I] + [_P] * 8 + [_P, _Z, _P]),
+    "elman_in_proj_workspace": (_Z, [_I, _L, _I]),
+    "elman_in_proj_split_silu": (_I, [_I, _L, _I, _I] + [_P] * 5 + [_P, _Z, _P]),
+    "elman_silu_backward_concat": (_I, [_I, _L, _I, _P, _P, _P, _P, _P]),
     "elman_projection": (_I, [_I, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P]),
 }
 

@@ -997,4 +997,86 @@ int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d, cons
   return float_to_dtype(dtype, w.db, db, d, st);
 }
 
+// ------------------ the layer's time-parallel ops around the cell ------------------
+
+size_t elman_add_rmsnorm_backward_workspace(int D) {
+  return add_rmsnorm_bwd_scratch_bytes(D < 0 ? 0 : D);
+}
+
+int elman_add_rmsnorm_forward(int dtype, long M, int D, const void* x, const float* residual_in,
+                              const void* weight, float eps, float* residual_out, void* y,
+                              float* rstd, void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(M >= 0 && D >= 0, "negative size");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (M == 0 || D == 0) return ELMAN_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(weight); REQUIRE_PTR(residual_out); REQUIRE_PTR(y); REQUIRE_PTR(rstd);
+  return add_rmsnorm_fwd(dtype, M, D, x, residual_in, weight, eps, residual_out, y, rstd,
+                         (cudaStream_t)stream);
+}
+
+int elman_add_rmsnorm_backward(int dtype, long M, int D, const void* dy,
+                               const float* dresidual_out, const float* residual_out,
+                               const float* rstd, const void* weight, float* dresidual_in,
+                               void* dx, void* dweight, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(M >= 0 && D >= 0, "negative size");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (D == 0) return ELMAN_OK;
+  REQUIRE_PTR(dweight);
+  if (M > 0) {
+    REQUIRE_PTR(dy); REQUIRE_PTR(residual_out); REQUIRE_PTR(rstd); REQUIRE_PTR(weight);
+    REQUIRE_PTR(workspace);
+    ELMAN_ARG_CHECK(dresidual_in != nullptr || dx != nullptr, "neither dresidual_in nor dx given");
+    if (workspace_bytes < add_rmsnorm_bwd_scratch_bytes(D))
+      return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes,
+                       add_rmsnorm_bwd_scratch_bytes(D));
+  }
+  return add_rmsnorm_bwd(dtype, M, D, dy, dresidual_out, residual_out, rstd, weight, dresidual_in,
+                         dx, dweight, (float*)workspace, (cudaStream_t)stream);
+}
+
+size_t elman_in_proj_workspace(int dtype, long M, int d_inner) {
+  if (M <= 0 || d_inner <= 0) return 0;
+  return ((size_t)M * 2 * d_inner * esize(dtype) + 255) & ~(size_t)255;
+}
+
+int elman_in_proj_split_silu(int dtype, long M, int d_inner, int K, const void* u, const void* W_in,
+                             void* x_raw, void* x_act, void* z, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(M >= 0 && d_inner >= 0 && K >= 0 && M < (1L << 31), "bad size");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (M == 0 || d_inner == 0) return ELMAN_OK;
+  REQUIRE_PTR(u); REQUIRE_PTR(W_in); REQUIRE_PTR(x_raw); REQUIRE_PTR(x_act); REQUIRE_PTR(z);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int N = 2 * d_inner;
+  if (use_tc(dtype) && (d_inner & 31) == 0 && K > 0 &&
+      gemm_tc_supported((int)M, N, K, u, K, W_in, K, x_raw, d_inner, 0) &&
+      ((((uintptr_t)x_raw | (uintptr_t)x_act | (uintptr_t)z) & 15) == 0)) {
+    // split and silu inside the GEMM's epilogue: xz never exists in memory
+    GemmSplit sp{d_inner, x_act, z};
+    return gemm_tc((int)M, N, K, (const bf16*)u, K, 0, (const bf16*)W_in, K, 0, nullptr, x_raw,
+                   d_inner, 0, 0, st, nullptr, 0, &sp);
+  }
+  REQUIRE_PTR(workspace);
+  if (workspace_bytes < elman_in_proj_workspace(dtype, M, d_inner))
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes,
+                     elman_in_proj_workspace(dtype, M, d_inner));
+  if (K == 0) ELMAN_CUDA_CHECK(cudaMemsetAsync(workspace, 0, (size_t)M * N * esize(dtype), st));
+  else ELMAN_RETURN_IF(proj_nt(dtype, (int)M, N, K, u, K, W_in, K, nullptr, workspace, N, 0, st));
+  return split_silu(dtype, M, d_inner, workspace, x_raw, x_act, z, st);
+}
+
+int elman_silu_backward_concat(int dtype, long M, int d_inner, const void* d_act, const void* x_raw,
+                               const void* dz, void* dxz, void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(M >= 0 && d_inner >= 0, "negative size");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (M == 0 || d_inner == 0) return ELMAN_OK;
+  REQUIRE_PTR(d_act); REQUIRE_PTR(x_raw); REQUIRE_PTR(dz); REQUIRE_PTR(dxz);
+  return silu_bwd_concat(dtype, M, d_inner, d_act, x_raw, dz, dxz, (cudaStream_t)stream);
+}
+
 }  // extern "C"

@@ -127,9 +127,30 @@ int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int l
 // `splitk`: optional scratch for fp32 partial sums (GEMM_MAX_KSPLIT * M * N floats cover every
 // case); with it, shapes with few output tiles and a long K are cut along K.
 constexpr int GEMM_MAX_KSPLIT = 4;
+// Optional epilogue of the layer's input projection: the N = 2*split output columns are not
+// stored as one matrix but as three dense [M, split] ones — columns [0, split) raw into C and
+// silu-activated into C_act, columns [split, 2*split) into C_hi.  split % 32 == 0, bf16 out.
+struct GemmSplit {
+  int split;
+  void* C_act;
+  void* C_hi;
+};
 int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
             int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
-            cudaStream_t stream, float* splitk = nullptr, size_t splitk_bytes = 0);
+            cudaStream_t stream, float* splitk = nullptr, size_t splitk_bytes = 0,
+            const GemmSplit* split = nullptr);
+
+// Elementwise layer kernels (layer_ops.cu).
+size_t add_rmsnorm_bwd_scratch_bytes(int D);
+int add_rmsnorm_fwd(int dtype, long M, int D, const void* x, const float* res_in, const void* w,
+                    float eps, float* res_out, void* y, float* rstd, cudaStream_t st);
+int add_rmsnorm_bwd(int dtype, long M, int D, const void* dy, const float* dres_out,
+                    const float* res_out, const float* rstd, const void* w, float* dres_in,
+                    void* dx, void* dw, float* scratch, cudaStream_t st);
+int split_silu(int dtype, long M, int d, const void* xz, void* x_raw, void* x_act, void* z,
+               cudaStream_t st);
+int silu_bwd_concat(int dtype, long M, int d, const void* d_act, const void* x_raw, const void* dz,
+                    void* dxz, cudaStream_t st);
 bool gemm_tc_supported(int M, int N, int K, const void* A, int lda, const void* W, int ldw,
                        const void* C, int ldc, int c_is_f32);
 

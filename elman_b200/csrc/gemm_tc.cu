@@ -58,6 +58,9 @@ struct GemmParams {
   int* status;
   int a_mn;  // A is given as [K, M] (M contiguous): MN-major operand, no transpose pass
   int b_mn;  // W is given as [K, N] (N contiguous)
+  int split = 0;              // > 0: the input projection's three-output epilogue (GemmSplit)
+  void* C_act = nullptr;
+  void* C_hi = nullptr;
   int stall_step = -1;        // test hook: block 0 arms a stage at this K iteration but loads nothing
   int ksplit = 1;             // persistent kernel: K range cut into this many work items per tile
   float* partial = nullptr;   // [ksplit][M][N] fp32 partial sums when ksplit > 1
@@ -73,6 +76,34 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ void store_chunk(const GemmParams& p, int gm, int gn0,
                                             const uint32_t (&r)[32], bool vec_ok,
                                             const bf16* bias32) {
+  if (p.split > 0) {
+    // input projection of the layer: columns left of `split` are the recurrence's input —
+    // stored raw (for the backward pass) and silu-activated — the others the gate input.
+    // split % 32 == 0, so a chunk never straddles; all three outputs are dense [M, split].
+    if (gm < p.M && gn0 < p.N) {
+      const bool hi = gn0 >= p.split;
+      const long off = (long)gm * p.split + (hi ? gn0 - p.split : gn0);
+      bf16* raw = (hi ? (bf16*)p.C_hi : (bf16*)p.C) + off;
+      bf16* act = (bf16*)p.C_act + off;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 o, a;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+        uint32_t* aw = reinterpret_cast<uint32_t*>(&a);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float f0 = __uint_as_float(r[j + 2 * q]), f1 = __uint_as_float(r[j + 2 * q + 1]);
+          ow[q] = pack_bf16(f0, f1);
+          // silu of the value as stored (rounded to bf16), as a separate pass would see it
+          const float2 rf = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&ow[q]));
+          aw[q] = pack_bf16(siluf_(rf.x), siluf_(rf.y));
+        }
+        *reinterpret_cast<uint4*>(raw + j) = o;
+        if (!hi) *reinterpret_cast<uint4*>(act + j) = a;
+      }
+    }
+    return;
+  }
   if (gm < p.M && gn0 < p.N) {
     float f[32];
 #pragma unroll
@@ -579,7 +610,14 @@ namespace { int sm_count(); }
 
 int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
             int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
-            cudaStream_t stream, float* splitk, size_t splitk_bytes) {
+            cudaStream_t stream, float* splitk, size_t splitk_bytes, const GemmSplit* split) {
+  if (split != nullptr) {
+    if (split->split <= 0 || (split->split & 31) != 0 || N != 2 * split->split || c_is_f32 ||
+        accumulate || bias != nullptr || (((uintptr_t)C | (uintptr_t)split->C_act |
+                                           (uintptr_t)split->C_hi) & 15) != 0)
+      return set_error(ELMAN_ERR_UNSUPPORTED, "split epilogue: shape or alignment not supported");
+    splitk = nullptr;   // the three-output epilogue has no partial-sum form
+  }
   {
     // option gemm_persistent: 0 = the persistent 128x256 kernel once its tiles fill the SMs,
     // 1 = never, 2 = always
@@ -606,6 +644,7 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
       q.stall_step = (int)options().test_stall_step;
       q.status = device_status_ptr();
       q.a_mn = a_mn; q.b_mn = b_mn;
+      if (split != nullptr) { q.split = split->split; q.C_act = split->C_act; q.C_hi = split->C_hi; }
       return gemm_tc_persistent(M, N, K, A, lda, a_mn, W, ldw, b_mn, q, stream);
     }
   }
@@ -627,6 +666,7 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
   p.stall_step = (int)options().test_stall_step;
   p.status = device_status_ptr();
   p.a_mn = a_mn; p.b_mn = b_mn;
+  if (split != nullptr) { p.split = split->split; p.C_act = split->C_act; p.C_hi = split->C_hi; }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, p);
   count_launch(true);

@@ -443,3 +443,94 @@ def projection(A, W, bias=None, out=None, accumulate=False):
                                   1 if accumulate else 0, _stream(A.device))
         _lib.check(rc, fn)
     return out
+
+
+# ------------------------------ layer ops around the cell (extensions of the C ABI)
+
+def add_rmsnorm_forward(x, residual_in, weight, eps):
+    """x [..., D] (+ residual_in fp32, or None) -> (y like x, residual_out fp32, rstd fp32 [rows])
+    through elman_add_rmsnorm_forward."""
+    fn = "add_rmsnorm_forward"
+    dt = _check_inputs(fn, x, x=x, weight=weight)
+    D = x.shape[-1]
+    M = x.numel() // max(D, 1)
+    _shape(fn, weight, (D,), "weight")
+    if residual_in is not None:
+        if residual_in.dtype != torch.float32 or not residual_in.is_contiguous() or \
+                residual_in.shape != x.shape or residual_in.device != x.device:
+            raise RuntimeError(f"{fn}: residual_in must be a contiguous float32 tensor shaped like x")
+    with torch.cuda.device(x.device):
+        res_out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        y = torch.empty_like(x)
+        rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+        rc = _lib.load().elman_add_rmsnorm_forward(dt, M, D, _ptr(x), _ptr(residual_in), _ptr(weight),
+                                                   float(eps), _ptr(res_out), _ptr(y), _ptr(rstd),
+                                                   _stream(x.device))
+        _lib.check(rc, fn)
+    return y, res_out, rstd
+
+
+def add_rmsnorm_backward(dy, dres_out, res_out, rstd, weight, want_dres_in, want_dx):
+    """-> (dres_in fp32 or None, dx like dy or None, dweight [D]) through
+    elman_add_rmsnorm_backward."""
+    fn = "add_rmsnorm_backward"
+    dt = _check_inputs(fn, dy, dy=dy, weight=weight)
+    D = dy.shape[-1]
+    M = dy.numel() // max(D, 1)
+    for name, t in (("dres_out", dres_out), ("res_out", res_out), ("rstd", rstd)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or not t.is_cuda):
+            raise RuntimeError(f"{fn}: {name} must be a contiguous float32 CUDA tensor")
+    lib = _lib.load()
+    with torch.cuda.device(dy.device):
+        dres_in = torch.empty(dy.shape, dtype=torch.float32, device=dy.device) if want_dres_in else None
+        dx = torch.empty_like(dy) if want_dx else None
+        dw = torch.empty(D, dtype=dy.dtype, device=dy.device)
+        ws = _workspace(lib.elman_add_rmsnorm_backward_workspace(D), dy.device)
+        rc = lib.elman_add_rmsnorm_backward(dt, M, D, _ptr(dy), _ptr(dres_out), _ptr(res_out),
+                                            _ptr(rstd), _ptr(weight), _ptr(dres_in), _ptr(dx),
+                                            _ptr(dw), ws.data_ptr(), ws.numel(), _stream(dy.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(dy.device))
+    return dres_in, dx, dw
+
+
+def in_proj_split_silu(u, W_in):
+    """u [M,K], W_in [2*d,K] -> (x_raw, x_act = silu(x_raw), z), each [M,d], through
+    elman_in_proj_split_silu (split and silu in the GEMM epilogue on the bf16 path)."""
+    fn = "in_proj_split_silu"
+    dt = _check_inputs(fn, u, u=u, W_in=W_in)
+    M, K = u.shape
+    if W_in.dim() != 2 or W_in.shape[1] != K or W_in.shape[0] % 2:
+        raise RuntimeError(f"{fn}: W_in must be [2*d_inner, {K}]")
+    d = W_in.shape[0] // 2
+    lib = _lib.load()
+    with torch.cuda.device(u.device):
+        x_raw, x_act, z = (torch.empty(M, d, dtype=u.dtype, device=u.device) for _ in range(3))
+        need = 0 if (dt == _lib.ELMAN_BF16 and d % 32 == 0 and K % 8 == 0
+                     and _lib.get_option("force_generic") == 0) else lib.elman_in_proj_workspace(dt, M, d)
+        ws = _workspace(need, u.device)
+        rc = lib.elman_in_proj_split_silu(dt, M, d, K, _ptr(u), _ptr(W_in), _ptr(x_raw), _ptr(x_act),
+                                          _ptr(z), ws.data_ptr(), ws.numel() if need else 0,
+                                          _stream(u.device))
+        if rc == 4 and not need:   # the library chose the two-pass form after all
+            ws = _workspace(lib.elman_in_proj_workspace(dt, M, d), u.device)
+            rc = lib.elman_in_proj_split_silu(dt, M, d, K, _ptr(u), _ptr(W_in), _ptr(x_raw),
+                                              _ptr(x_act), _ptr(z), ws.data_ptr(), ws.numel(),
+                                              _stream(u.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(u.device))
+    return x_raw, x_act, z
+
+
+def silu_backward_concat(d_act, x_raw, dz):
+    """-> dxz [M, 2*d] = [d_act * silu'(x_raw) | dz] through elman_silu_backward_concat."""
+    fn = "silu_backward_concat"
+    dt = _check_inputs(fn, d_act, d_act=d_act, x_raw=x_raw, dz=dz)
+    M, d = d_act.shape
+    _shape(fn, x_raw, (M, d), "x_raw"); _shape(fn, dz, (M, d), "dz")
+    with torch.cuda.device(d_act.device):
+        dxz = torch.empty(M, 2 * d, dtype=d_act.dtype, device=d_act.device)
+        rc = _lib.load().elman_silu_backward_concat(dt, M, d, _ptr(d_act), _ptr(x_raw), _ptr(dz),
+                                                    _ptr(dxz), _stream(d_act.device))
+        _lib.check(rc, fn)
+    return dxz

@@ -13,6 +13,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import fused_ops
 from .mamba_gated_elman import MambaGatedElman
 from .pure_lowrank_elman import PureLowRankElman
 from .stock_elman import StockElman
@@ -32,8 +33,12 @@ class LadderLM(nn.Module):
     def __init__(self, vocab_size=256, dim=512, depth=12, level=0, expansion=1.0, rank=None,
                  dropout=0.0, r_h_mode="spectral_norm", r_h_init_gain=0.1, mamba2_init=False,
                  use_conv=False, d_conv=4, loss_chunk_size=0, pipeline_chunks=0,
-                 pipeline_streams=0, **unused):
+                 pipeline_streams=0, fused_ops=True, **unused):
         super().__init__()
+        # fused_ops (not a reference argument): residual add + RMSNorm as one kernel each way
+        # and the head as a library GEMM (the reference's fused_add_norm switch, ladder_lm.py
+        # :986-1003, selects a Triton kernel for the same purpose); False = framework ops
+        self.fused_ops = bool(fused_ops)
         # pipeline_chunks > 1 (not a reference argument): run the layer stack as a
         # wavefront over (layer, time chunk) on several CUDA streams, see _pipelined_layers
         self.pipeline_chunks = int(pipeline_chunks)
@@ -80,18 +85,15 @@ class LadderLM(nn.Module):
             new_hiddens = []
             residual = None
             for i, (ln, layer) in enumerate(zip(self.layer_norms, self.layers)):
-                residual = (h + residual) if residual is not None else h
-                h = ln(residual.to(dtype=ln.weight.dtype))
-                if self.residual_in_fp32:
-                    residual = residual.to(torch.float32)
+                h, residual = self._add_norm(ln, h, residual)
                 h, h_final = layer(h, prev_hiddens[i])
                 new_hiddens.append(h_final)
-        h = self.norm((h + residual).to(dtype=self.norm.weight.dtype))
+        h, _ = self._add_norm(self.norm, h, residual, last=True)
         if time_major and (not return_loss or self.loss_chunk_size > 0):
             h = h.transpose(0, 1).contiguous()   # back to [B,T,D] for the callers below
             time_major = False
         if not return_loss:
-            logits = self.lm_head(h)
+            logits = self._head(h)
             return (logits, (new_hiddens, None)) if return_prev_hiddens else logits
         if actual_length is not None:
             positions = torch.arange(target.size(1), device=h.device).unsqueeze(0)
@@ -107,14 +109,32 @@ class LadderLM(nn.Module):
             for t0 in range(0, T_total, self.loss_chunk_size):
                 t1 = min(t0 + self.loss_chunk_size, T_total)
                 tc = target[:, t0:t1]
-                total = total + F.cross_entropy(self.lm_head(h[:, t0:t1]).reshape(-1, self.vocab_size),
+                total = total + F.cross_entropy(self._head(h[:, t0:t1]).reshape(-1, self.vocab_size),
                                                 tc.reshape(-1), ignore_index=-100, reduction="sum")
                 count = count + (tc != -100).sum()
             loss = total / count.clamp(min=1)
         else:
-            loss = F.cross_entropy(self.lm_head(h).view(-1, self.vocab_size), target.reshape(-1),
+            loss = F.cross_entropy(self._head(h).view(-1, self.vocab_size), target.reshape(-1),
                                    ignore_index=-100)
         return (loss, (new_hiddens, None)) if return_prev_hiddens else loss
+
+    def _add_norm(self, norm, h, residual, last=False):
+        """residual = h + residual (fp32 stream); h = norm(residual in the layer's dtype).
+        Returns (h, residual); with `last` the residual is not needed any more."""
+        if self.fused_ops and self.residual_in_fp32 and fused_ops.library_handles(h) \
+                and h.dtype == norm.weight.dtype:
+            return fused_ops.AddRMSNormFunction.apply(
+                h, residual, norm.weight, fused_ops.rmsnorm_eps(norm, h.dtype))
+        residual = (h + residual) if residual is not None else h
+        h = norm(residual.to(dtype=norm.weight.dtype))
+        if self.residual_in_fp32 and not last:
+            residual = residual.to(torch.float32)
+        return h, residual
+
+    def _head(self, h):
+        if self.fused_ops and fused_ops.library_handles(h) and h.dtype == self.lm_head.weight.dtype:
+            return fused_ops.linear(h.contiguous(), self.lm_head.weight)
+        return self.lm_head(h)
 
     # ------------------------------------------------------------------ pipeline
     #
@@ -218,10 +238,7 @@ class LadderLM(nn.Module):
                     hin.record_stream(sp)
                     if rin is not None:
                         rin.record_stream(sp)
-                    residual = (hin + rin) if rin is not None else hin
-                    hn = ln(residual.to(dtype=ln.weight.dtype))
-                    if self.residual_in_fp32:
-                        residual = residual.to(torch.float32)
+                    hn, residual = self._add_norm(ln, hin, rin)
                     link = ChunkLink()
                     pre, z = layer.chunk_pre(hn, shared[i], link)
                     return pre, z, link, residual, record(sp)

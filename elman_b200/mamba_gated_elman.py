@@ -13,7 +13,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from . import hasty_pytorch_lib
+from . import fused_ops, hasty_pytorch_lib
 from ._spectral import spectrally_normalised
 
 
@@ -128,6 +128,7 @@ class LinearFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, W, b):
         ctx.save_for_backward(x, W)
+        ctx.has_bias = b is not None
         x2 = x.reshape(-1, x.shape[-1])
         return hasty_pytorch_lib.gemm(hasty_pytorch_lib.GEMM_NT, x2, W, b).view(*x.shape[:-1],
                                                                               W.shape[0])
@@ -139,7 +140,7 @@ class LinearFunction(torch.autograd.Function):
         dy2 = dy.contiguous().view(-1, W.shape[0])
         dx = G.gemm(G.GEMM_NN, dy2, W).view(x.shape)
         dW = G.gemm(G.GEMM_TN, dy2, x.reshape(-1, x.shape[-1]))
-        return dx, dW, G.column_sum(dy2)
+        return dx, dW, (G.column_sum(dy2) if ctx.has_bias else None)
 
 
 class E1ChunkRecurrenceFunction(torch.autograd.Function):
@@ -248,6 +249,9 @@ class MambaGatedElman(nn.Module):
                                         w_h_init_gain=r_h_init_gain, mamba2_init=mamba2_init)
         self.out_proj = nn.Linear(self.d_inner, dim, bias=False)
         self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
+        # projections and their elementwise tails through the library's own kernels (False:
+        # nn.Linear / framework ops, the reference's op-by-op form; same arithmetic)
+        self.fused = True
         self._init_weights()
 
     def _init_weights(self):
@@ -261,6 +265,8 @@ class MambaGatedElman(nn.Module):
     def forward(self, x, h0=None, **kwargs):
         """x: [B,T,dim] -> (output [B,T,dim], h_final [B,d_inner])."""
         B, T, D = x.shape
+        if self.fused and not self.use_conv and fused_ops.library_handles(x):
+            return self.forward_fused(x, h0)
         x_proj, z = self.in_proj(x).chunk(2, dim=-1)
         if self.use_conv:
             x_proj = self.conv1d(x_proj.transpose(1, 2))[:, :, :T].transpose(1, 2)
@@ -270,6 +276,28 @@ class MambaGatedElman(nn.Module):
         cell_out, h_all = self.cell(x_rnn, z_rnn, h0)
         y = self.dropout(cell_out.permute(1, 0, 2).contiguous())
         return self.out_proj(y), h_all[-1]
+
+    def forward_fused(self, x, h0=None, time_major=False):
+        """forward() with every op on the library's kernels: one transposing copy of the input
+        to the cell's time-major layout, in_proj with split + silu in its GEMM epilogue, the
+        cell, out_proj as a library GEMM, one transposing copy back (none with time_major)."""
+        xt = x if time_major else x.transpose(0, 1).contiguous()
+        x_act, z = fused_ops.InProjSplitSiluFunction.apply(xt, self.in_proj.weight)
+        cell_out, h_all = self.cell(x_act, z, h0)
+        y = fused_ops.linear(self.dropout(cell_out), self.out_proj.weight)
+        return (y if time_major else y.transpose(0, 1).contiguous()), h_all[-1]
+
+    def _in_proj_act(self, x):
+        """(silu(x half), gate half) of in_proj(x), contiguous, for time-major x."""
+        if self.fused and fused_ops.library_handles(x):
+            return fused_ops.InProjSplitSiluFunction.apply(x, self.in_proj.weight)
+        x_proj, z = self.in_proj(x).chunk(2, dim=-1)
+        return F.silu(x_proj).contiguous(), z.contiguous()
+
+    def _out_proj(self, y):
+        if self.fused and fused_ops.library_handles(y):
+            return fused_ops.linear(y, self.out_proj.weight)
+        return self.out_proj(y)
 
     # ---- time-chunked execution (used by LadderLM's layer/time pipeline) ----
     @property
@@ -290,33 +318,33 @@ class MambaGatedElman(nn.Module):
         preceding chunk) -> (output in the layout of x, h_last).  Chained over the chunks of
         a sequence this equals forward() on the whole sequence.  Time-major callers skip the
         three layout copies around the cell: every other op of the layer is per token."""
-        x_proj, z = self.in_proj(x).chunk(2, dim=-1)
         if time_major:
-            x_rnn, z_rnn = F.silu(x_proj).contiguous(), z.contiguous()
+            x_rnn, z_rnn = self._in_proj_act(x)
         else:
+            x_proj, z = self.in_proj(x).chunk(2, dim=-1)
             x_rnn = F.silu(x_proj).permute(1, 0, 2).contiguous()
             z_rnn = z.permute(1, 0, 2).contiguous()
         cell = self.cell
         cell_out, h_last = MambaGatedElmanChunkFunction.apply(
             x_rnn, z_rnn, h0.contiguous(), cell.W_x.contiguous(), W_h, cell.b.contiguous(), flags)
         y = cell_out if time_major else cell_out.permute(1, 0, 2).contiguous()
-        return self.out_proj(self.dropout(y)), h_last
+        return self._out_proj(self.dropout(y)), h_last
 
     # The same chunk in three pieces, for callers that put them on different streams:
     # chunk_pre (time-parallel, up to the projected inputs), chunk_rec (the recurrence
     # alone) and chunk_post (output projection).  All time-major [Tc,B,*].
     def chunk_pre(self, x, W_h, link):
-        x_proj, z = self.in_proj(x).chunk(2, dim=-1)
+        x_act, z = self._in_proj_act(x)
         cell = self.cell
-        pre = E1ChunkProjectionFunction.apply(F.silu(x_proj).contiguous(), cell.W_x.contiguous(),
-                                              cell.b.contiguous(), W_h, link)
-        return pre, z.contiguous()
+        pre = E1ChunkProjectionFunction.apply(x_act, cell.W_x.contiguous(), cell.b.contiguous(),
+                                              W_h, link)
+        return pre, z
 
     def chunk_rec(self, pre, z, h0, W_h, link, flags=0, W_h_T=None):
         return E1ChunkRecurrenceFunction.apply(pre, z, h0.contiguous(), W_h, link, flags, W_h_T)
 
     def chunk_post(self, cell_out):
-        return self.out_proj(self.dropout(cell_out))
+        return self._out_proj(self.dropout(cell_out))
 
     def extra_repr(self):
         return f"dim={self.dim}, d_inner={self.d_inner}, use_conv={self.use_conv}, LEVEL=1_MAMBA_GATED"

@@ -125,9 +125,11 @@ class StockElman(nn.Module):
         return self.cell.get_W_h().contiguous()
 
     def chunk_pre(self, x, W_h, link):
+        from . import fused_ops
         from .mamba_gated_elman import E1ChunkProjectionFunction, LinearFunction
         cell = self.cell
-        x_proj = self.in_proj(x).contiguous()
+        x_proj = (fused_ops.linear(x.contiguous(), self.in_proj.weight)
+                  if fused_ops.library_handles(x) else self.in_proj(x).contiguous())
         pre = E1ChunkProjectionFunction.apply(x_proj, cell.W_x.contiguous(), cell.b.contiguous(),
                                               W_h, link)
         gate = LinearFunction.apply(x_proj, cell.W_gate.contiguous(), cell.b_gate.contiguous())
@@ -138,7 +140,10 @@ class StockElman(nn.Module):
         return E1ChunkRecurrenceFunction.apply(pre, gate, h0.contiguous(), W_h, link, flags, W_h_T)
 
     def chunk_post(self, cell_out):
-        return self.out_proj(self.dropout(cell_out))
+        from . import fused_ops
+        y = self.dropout(cell_out)
+        return (fused_ops.linear(y, self.out_proj.weight) if fused_ops.library_handles(y)
+                else self.out_proj(y))
 
     def extra_repr(self):
         return f"dim={self.dim}, d_inner={self.d_inner}, LEVEL=0_STOCK"

@@ -29,11 +29,14 @@ def raise_on_device_timeout(where="a replayed step"):
 
 class GraphedTrainStep:
     def __init__(self, net, optimizer, example_tokens, max_grad_norm=1.0, autocast_dtype=None,
-                 warmup_steps=3, after_backward=None):
-        """`after_backward(params)`, if given, runs between backward and clipping, inside
-        the captured step: the place for a data-parallel gradient all-reduce."""
+                 warmup_steps=3, after_backward=None, reducer=None):
+        """`reducer` (a FlatGradients, optional): the gradients live in its flat buffer; it
+        zeroes them, all-reduces them bucket by bucket while backward still runs (N > 1) and
+        clips them.  `after_backward(params)` (the older hook), if given, runs between
+        backward and clipping, inside the captured step."""
         self.net, self.opt = net, optimizer
         self.after_backward = after_backward
+        self.reducer = reducer
         self.max_grad_norm = max_grad_norm
         self.autocast_dtype = autocast_dtype
         self.tokens = example_tokens.clone()
@@ -46,7 +49,8 @@ class GraphedTrainStep:
         torch.cuda.current_stream(self.tokens.device).wait_stream(side)
         torch.cuda.synchronize(self.tokens.device)
         self.graph = torch.cuda.CUDAGraph()
-        self.opt.zero_grad(set_to_none=True)
+        if self.reducer is None:
+            self.opt.zero_grad(set_to_none=True)
         from . import _lib
         before = _lib.launch_count()
         with torch.cuda.graph(self.graph):
@@ -55,7 +59,9 @@ class GraphedTrainStep:
         self.library_launches_per_step = _lib.launch_count() - before
 
     def _eager_step(self, zero=True):
-        if zero:
+        if self.reducer is not None:
+            self.reducer.zero()          # also inside the captured step: one memset
+        elif zero:
             self.opt.zero_grad(set_to_none=True)
         if self.autocast_dtype is not None:
             with torch.autocast(device_type="cuda", dtype=self.autocast_dtype):
@@ -63,10 +69,15 @@ class GraphedTrainStep:
         else:
             loss = self.net(self.tokens, return_loss=True)
         loss.backward()
+        if self.reducer is not None:
+            self.reducer.finish()
         if self.after_backward is not None:
             self.after_backward(self.params)
         if self.max_grad_norm:
-            torch.nn.utils.clip_grad_norm_(self.params, self.max_grad_norm)
+            if self.reducer is not None:
+                self.reducer.clip_(self.max_grad_norm)
+            else:
+                torch.nn.utils.clip_grad_norm_(self.params, self.max_grad_norm)
         self.opt.step()
         return loss.detach()
 
@@ -100,3 +111,150 @@ def allreduce_gradients(params, group=None):
         n = g.numel()
         g.copy_(flat[offset:offset + n].view_as(g))
         offset += n
+
+
+class FlatGradients:
+    """Every gradient of a model as a view into ONE pre-allocated flat buffer, cut into
+    buckets, and — for data-parallel training — one all-reduce per bucket that starts as
+    soon as that bucket's gradients are final, on a communication stream of its own, while
+    the backward pass of the remaining layers still runs.
+
+    This is what DistributedDataParallel does for the reference (bucketed NCCL all-reduce
+    overlapped with autograd, train_ladder.py:306-307), without its copies: gradients are
+    accumulated by autograd straight into the buffer the collective reads, nothing is
+    concatenated before or copied back after.  Capturable into a CUDA graph (fixed
+    addresses, no host synchronisation); the cross-stream edges become graph edges.
+
+      buckets        list of lists of parameters, in the order their gradients become final
+                     (last layer first); every parameter in exactly one bucket
+      group / world  process group and its size; world 1 (or no initialised group) means no
+                     collective — the flat buffer still serves zeroing and clipping
+
+    Per step: zero() -> forward/backward -> finish() -> clip_() -> optimizer.
+    """
+
+    def __init__(self, buckets, group=None):
+        import torch.distributed as dist
+        self.group = group
+        self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        params = [p for b in buckets for p in b]
+        if len({id(p) for p in params}) != len(params):
+            raise ValueError("a parameter appears in more than one bucket")
+        if not params:
+            raise ValueError("no parameters")
+        dtype, device = params[0].dtype, params[0].device
+        for p in params:
+            if p.dtype != dtype or p.device != device:
+                raise ValueError("all parameters must share one dtype and device")
+        total = 0
+        self._slices = []
+        for b in buckets:      # 256-byte aligned buckets
+            start = total
+            for p in b:
+                total += p.numel()
+            total = (total + 127) // 128 * 128
+            self._slices.append((start, total))
+        self.flat = torch.zeros(total, dtype=dtype, device=device)
+        self.bucket_views = [self.flat[a:b] for a, b in self._slices]
+        self.params = params
+        self._pending = []
+        self._bucket_of = {}
+        self._hooks = []
+        for bi, (b, (start, _)) in enumerate(zip(buckets, self._slices)):
+            off = start
+            for p in b:
+                p.grad = self.flat[off:off + p.numel()].view_as(p)
+                off += p.numel()
+                self._bucket_of[id(p)] = bi
+                if self.world > 1:
+                    self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad_final))
+            self._pending.append(len(b))
+        self._sizes = list(self._pending)
+        self.comm_stream = torch.cuda.Stream(device=device) if (device.type == "cuda" and self.world > 1) else None
+        self._launched = 0
+
+    def describe(self):
+        if self.world == 1:
+            return "none (one rank); gradients in one flat buffer"
+        mb = [round((b - a) * self.flat.element_size() / 1e6, 1) for a, b in self._slices]
+        return (f"NCCL all-reduce of {len(mb)} buckets {mb} MB, each released on a communication "
+                "stream when its gradients are final, overlapped with the rest of backward, "
+                "inside the step graph; gradients are views into one flat buffer (no cat, no copy-back)")
+
+    def zero(self):
+        self.flat.zero_()
+        self._pending = list(self._sizes)
+        self._launched = 0
+
+    def _on_grad_final(self, p):
+        # autograd accumulated in place into the view; a replaced .grad would break the scheme
+        bi = self._bucket_of[id(p)]
+        self._pending[bi] -= 1
+        if self._pending[bi] == 0:
+            self._reduce_bucket(bi)
+
+    def _reduce_bucket(self, bi):
+        import torch.distributed as dist
+        self._launched += 1
+        view = self.bucket_views[bi]
+        if self.comm_stream is None:
+            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
+            return
+        here = torch.cuda.current_stream(view.device)   # the stream this gradient became final on
+        ready = torch.cuda.Event()
+        ready.record(here)
+        self.comm_stream.wait_event(ready)
+        with torch.cuda.stream(self.comm_stream):
+            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
+
+    def finish(self):
+        """After backward: buckets whose hooks did not all fire (a parameter without a
+        gradient this step) are reduced now; the caller's stream then waits for the
+        communication stream and the sums become means."""
+        if self.world == 1:
+            return
+        for bi, left in enumerate(self._pending):
+            if left > 0:
+                self._pending[bi] = 0
+                self._reduce_bucket(bi)
+        if self.comm_stream is not None:
+            torch.cuda.current_stream(self.flat.device).wait_stream(self.comm_stream)
+        self.flat.mul_(1.0 / self.world)
+
+    def clip_(self, max_norm, eps=1e-6):
+        """torch.nn.utils.clip_grad_norm_ (train_ladder.py:542-543 of the reference) on the
+        flat buffer: one norm, one scale, no host synchronisation.  Returns the norm."""
+        total = torch.linalg.vector_norm(self.flat, 2, dtype=torch.float32)
+        coef = torch.clamp(max_norm / (total + eps), max=1.0)
+        self.flat.mul_(coef.to(self.flat.dtype) if self.flat.dtype == torch.float64 else coef)
+        return total
+
+    def check_views(self):
+        """True while every parameter's .grad still is its view into the flat buffer."""
+        lo = self.flat.data_ptr()
+        hi = lo + self.flat.numel() * self.flat.element_size()
+        return all(p.grad is not None and lo <= p.grad.data_ptr() < hi for p in self.params)
+
+
+def ladder_buckets(model):
+    """Buckets for a LadderLM in the order backward completes them: the last layer (with its
+    pre-norm) first, the embedding / final norm last.  Other modules: one bucket."""
+    layers = getattr(model, "layers", None)
+    norms = getattr(model, "layer_norms", None)
+    if layers is None or norms is None:
+        return [[p for p in model.parameters() if p.requires_grad]]
+    seen, buckets = set(), []
+    for i in reversed(range(len(layers))):
+        b = [p for p in list(layers[i].parameters()) + list(norms[i].parameters())
+             if p.requires_grad and id(p) not in seen]
+        seen.update(id(p) for p in b)
+        if b:
+            buckets.append(b)
+    rest = [p for p in model.parameters() if p.requires_grad and id(p) not in seen]
+    if rest:
+        buckets.append(rest)
+    return buckets
+
+
+def make_gradient_reducer(model, group=None):
+    return FlatGradients(ladder_buckets(model), group=group)

@@ -366,6 +366,48 @@ int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d,
                                  void* dv, void* dz, void* db,
                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * The time-parallel ops of the layer and the model around the cell (the callers of the
+ * hot path), one kernel per pass.
+ *
+ * elman_add_rmsnorm_forward / _backward: residual add + RMSNorm with an fp32 residual
+ *   stream — LadderLM's per-layer "residual = x + residual; x = norm(residual)"
+ *   (elman/models/ladder_lm.py:986-1003, :1013-1026: the fused rms_norm_fn of mamba_ssm
+ *   when that package is present, else add, cast, nn.RMSNorm, cast as separate passes).
+ *     x [M,D] (dtype), residual_in [M,D] fp32 or NULL (first layer)
+ *     residual_out [M,D] fp32 = x + residual_in
+ *     y [M,D] (dtype) = round(residual_out) * rstd * weight,
+ *     rstd [M] fp32 = 1/sqrt(mean(round(residual_out)^2) + eps)
+ *   Backward takes dy (gradient of y) and dresidual_out (gradient that reaches residual_out
+ *   from later layers, fp32, or NULL) and returns dresidual_in (fp32, or NULL) and/or dx
+ *   (dtype, or NULL) — the same values, residual_in and x being summed — and dweight [D].
+ *
+ * elman_in_proj_split_silu: the layer's input projection with its tail
+ *   (elman/models/mamba_gated_elman.py:283-297: in_proj, chunk, silu, and the two
+ *   contiguous copies): xz = u W_in^T with u [M,K], W_in [2*d_inner, K];
+ *     x_raw = xz[:, :d_inner], x_act = silu(x_raw), z = xz[:, d_inner:], each dense
+ *     [M, d_inner].  For bf16 with d_inner % 32 == 0 the split and the silu run in the
+ *   epilogue of the tcgen05 GEMM and xz is never written; otherwise `workspace`
+ *   (elman_in_proj_workspace bytes) holds xz for a separate pass.
+ * elman_silu_backward_concat: dxz [M, 2*d_inner] = [ d_act * silu'(x_raw) | dz ], the
+ *   operand of the projection's backward GEMMs.
+ * ------------------------------------------------------------------------- */
+size_t elman_add_rmsnorm_backward_workspace(int D);
+int elman_add_rmsnorm_forward(int dtype, long M, int D, const void* x, const float* residual_in,
+                              const void* weight, float eps, float* residual_out, void* y,
+                              float* rstd, void* stream);
+int elman_add_rmsnorm_backward(int dtype, long M, int D, const void* dy,
+                               const float* dresidual_out, const float* residual_out,
+                               const float* rstd, const void* weight, float* dresidual_in,
+                               void* dx, void* dweight, void* workspace, size_t workspace_bytes,
+                               void* stream);
+size_t elman_in_proj_workspace(int dtype, long M, int d_inner);
+int elman_in_proj_split_silu(int dtype, long M, int d_inner, int K, const void* u, const void* W_in,
+                             void* x_raw, void* x_act, void* z, void* workspace,
+                             size_t workspace_bytes, void* stream);
+int elman_silu_backward_concat(int dtype, long M, int d_inner, const void* d_act, const void* x_raw,
+                               const void* dz, void* dxz, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -48,6 +48,35 @@ class OracleBackend:
         return x.sum(0)
 
     @staticmethod
+    def in_proj_split_silu(u, W_in):
+        xz = u @ W_in.T
+        d = W_in.shape[0] // 2
+        x_raw, z = xz[:, :d].contiguous(), xz[:, d:].contiguous()
+        return x_raw, orc.silu(x_raw), z
+
+    @staticmethod
+    def silu_backward_concat(d_act, x_raw, dz):
+        return torch.cat([d_act * orc.dsilu(x_raw), dz], dim=1)
+
+    @staticmethod
+    def add_rmsnorm_forward(x, residual_in, weight, eps):
+        res = x.float() if residual_in is None else x.float() + residual_in
+        v = res.to(x.dtype).float()
+        rstd = torch.rsqrt(v.pow(2).mean(-1) + eps)
+        y = (v * rstd[..., None] * weight.float()).to(x.dtype)
+        return y, res, rstd.reshape(-1)
+
+    @staticmethod
+    def add_rmsnorm_backward(dy, dres_out, res_out, rstd, weight, want_dres_in, want_dx):
+        D = dy.shape[-1]
+        xh = res_out.to(dy.dtype).float() * rstd.reshape(*dy.shape[:-1], 1)
+        g = dy.float() * weight.float()
+        dxn = rstd.reshape(*dy.shape[:-1], 1) * (g - xh * (g * xh).mean(-1, keepdim=True))
+        total = dxn if dres_out is None else dxn + dres_out
+        dw = (dy.float() * xh).reshape(-1, D).sum(0).to(dy.dtype)
+        return (total if want_dres_in else None), (total.to(dy.dtype) if want_dx else None), dw
+
+    @staticmethod
     def e1_recurrence_forward(training, pre, z, h0, W_h, flags=0):
         d = pre.shape[-1]   # the recurrence alone = the cell with W_x = I, b = 0
         o = orc.e1_forward(pre, z, h0, torch.eye(d, dtype=pre.dtype), W_h, torch.zeros(d, dtype=pre.dtype))
@@ -105,7 +134,8 @@ def as_fake_cuda(t):
 
 @pytest.fixture()
 def oracle_backend(monkeypatch):
-    for mod in (e1mod, e0mod, e5mod):
+    from elman_b200 import fused_ops
+    for mod in (e1mod, e0mod, e5mod, fused_ops):
         monkeypatch.setattr(mod, "hasty_pytorch_lib", OracleBackend)
 
 

@@ -26,7 +26,9 @@ class _FakeCudaLayer(e1mod.MambaGatedElman):
 
 
 def _build(fix, monkeypatch_fn):
+    from elman_b200 import fused_ops
     monkeypatch_fn(e1mod, "hasty_pytorch_lib", OracleBackend)
+    monkeypatch_fn(fused_ops, "hasty_pytorch_lib", OracleBackend)
     monkeypatch_fn(ladder_lm, "_LEVELS", {**ladder_lm._LEVELS, 1: _FakeCudaLayer})
     model = ladder_lm.LadderLM(vocab_size=256, dim=32, depth=2, level=1, expansion=1.0)
     sd = {k[5:]: torch.from_numpy(fix[k]) for k in fix.files if k.startswith("in_p_")}
@@ -129,3 +131,59 @@ def test_allreduce_gradients_averages_over_two_gloo_ranks():
         assert torch.allclose(ga, torch.full((3, 2), 1.5))
         assert torch.allclose(gb, torch.arange(5.0) * 1.5)
         assert none_c
+
+
+def _flat_worker(rank, world, port, out):
+    import torch.distributed as dist
+    from elman_b200.train_step import FlatGradients
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank,
+                            world_size=world)
+    torch.manual_seed(5)                       # same weights on both ranks
+    net = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.Tanh(), torch.nn.Linear(8, 3))
+    unused = torch.nn.Parameter(torch.zeros(4))        # gets no gradient: its bucket is still reduced
+    fg = FlatGradients([list(net[2].parameters()), list(net[0].parameters()) + [unused]])
+    x = torch.randn(5, 6, generator=torch.Generator().manual_seed(100 + rank))
+    results = []
+    for _ in range(2):                         # two steps: the buffer is reused
+        fg.zero()
+        net(x).pow(2).sum().backward()
+        launched_by_hooks = fg._launched
+        fg.finish()
+        results.append(([p.grad.clone() for p in net.parameters()], launched_by_hooks,
+                        fg.check_views(), float(unused.grad.abs().sum())))
+    out.put((rank, results))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_flat_gradient_buckets_are_averaged_over_two_gloo_ranks_as_they_complete():
+    """FlatGradients on two CPU ranks: each bucket is all-reduced from the hook of its last
+    gradient (the layer that finishes backward first goes first), gradients stay views into
+    the flat buffer, and the result is the mean of the two ranks' gradients."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29850 + os.getpid() % 100
+    procs = [ctx.Process(target=_flat_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    torch.manual_seed(5)
+    net = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.Tanh(), torch.nn.Linear(8, 3))
+    want = None
+    for r in range(2):
+        net.zero_grad()
+        x = torch.randn(5, 6, generator=torch.Generator().manual_seed(100 + r))
+        net(x).pow(2).sum().backward()
+        g = [p.grad.clone() / 2 for p in net.parameters()]
+        want = g if want is None else [a + b for a, b in zip(want, g)]
+    for rank in (0, 1):
+        for grads, by_hooks, views_ok, unused_sum in got[rank]:
+            assert by_hooks == 1       # the complete bucket went from its hook, during backward
+            assert views_ok and unused_sum == 0.0
+            for a, b in zip(grads, want):
+                assert torch.allclose(a, b, atol=1e-6)
