@@ -460,26 +460,35 @@ def measure_lm(args, rank, world, local_rank, impl, steps, warmup):
         chunks = args.pipeline_chunks if impl == "ours" else 0
         model = ladder_lm.LadderLM(vocab_size=256, dim=D, depth=6, level=args.lm_level,
                                    expansion=1.0, pipeline_chunks=chunks,
-                                   pipeline_streams=args.pipeline_streams)
+                                   pipeline_streams=args.pipeline_streams,
+                                   fused_ops=(impl == "ours"))
+        if impl != "ours":   # the reference arm: framework ops around the reference's kernels
+            for layer in model.layers:
+                layer.fused = False
         model = model.to(dev).bfloat16()
         net = model
         graphed = impl == "ours" and args.cuda_graph != 0
         if world > 1 and not graphed:
             net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank],
                                                             find_unused_parameters=False)
-        opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1,
-                                capturable=graphed)
         host_tokens = ladder_lm.zipf_tokens(B, T + 1, seed=1234 + rank).pin_memory()
         gstep = None
         reducer = None
         if graphed:
+            # gradients, parameters and optimizer state in flat buffers: one memset, one
+            # all-reduce per layer while backward runs (N > 1), one AdamW launch with the
+            # clipping factor folded in; the whole step captured into a CUDA graph
             from elman_b200 import train_step
-            if world > 1:  # same initial weights on every rank; gradients averaged inside the graph
-                for p_ in model.parameters():
-                    dist.broadcast(p_.data, src=0)
-                reducer = train_step.make_gradient_reducer(model)
+            reducer = train_step.make_gradient_reducer(model)
+            opt = train_step.FlatAdamW(reducer, lr=3e-4, betas=(0.9, 0.95), eps=1e-8,
+                                       weight_decay=0.1)
+            if world > 1:  # same initial weights on every rank
+                dist.broadcast(reducer.flat_params, src=0)
             gstep = train_step.GraphedTrainStep(net, opt, host_tokens.to(dev), max_grad_norm=1.0,
                                                 autocast_dtype=torch.bfloat16, reducer=reducer)
+        else:
+            opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95),
+                                    weight_decay=0.1)
 
         def step():
             if graphed:

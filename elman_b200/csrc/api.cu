@@ -1079,4 +1079,16 @@ int elman_silu_backward_concat(int dtype, long M, int d_inner, const void* d_act
   return silu_bwd_concat(dtype, M, d_inner, d_act, x_raw, dz, dxz, (cudaStream_t)stream);
 }
 
+int elman_adamw_step(int dtype, long n, void* params, const void* grads, void* exp_avg,
+                     void* exp_avg_sq, float lr, float beta1, float beta2, float eps,
+                     float weight_decay, float* step, const float* grad_scale, void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(n >= 0, "negative size");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  REQUIRE_PTR(step);
+  if (n > 0) { REQUIRE_PTR(params); REQUIRE_PTR(grads); REQUIRE_PTR(exp_avg); REQUIRE_PTR(exp_avg_sq); }
+  return adamw_step(dtype, n, params, grads, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay,
+                    step, grad_scale, (cudaStream_t)stream);
+}
+
 }  // extern "C"

@@ -151,6 +151,10 @@ int split_silu(int dtype, long M, int d, const void* xz, void* x_raw, void* x_ac
                cudaStream_t st);
 int silu_bwd_concat(int dtype, long M, int d, const void* d_act, const void* x_raw, const void* dz,
                     void* dxz, cudaStream_t st);
+// AdamW over flat buffers (train_ops.cu); advances *step by one first.
+int adamw_step(int dtype, long n, void* p, const void* g, void* m, void* v, float lr, float beta1,
+               float beta2, float eps, float weight_decay, float* step, const float* grad_scale,
+               cudaStream_t st);
 bool gemm_tc_supported(int M, int N, int K, const void* A, int lda, const void* W, int ldw,
                        const void* C, int ldc, int c_is_f32);
 

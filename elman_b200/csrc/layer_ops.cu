@@ -21,7 +21,8 @@ namespace elman {
 namespace {
 
 constexpr int NT = 256;           // threads per block
-constexpr int MAX_BLOCKS = 592;   // 4 per SM on a 148-SM part; also the partial-sum rows
+constexpr int MAX_BLOCKS = 592;   // 4 per SM on a 148-SM part
+constexpr int BWD_BLOCKS = 296;   // blocks (= partial-sum rows) of the norm's backward pass
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
@@ -124,13 +125,25 @@ add_rmsnorm_bwd_kernel(long M, int D, const T* __restrict__ dy, const float* __r
   }
 }
 
+// out[j] = sum over the rows of partial[rows, D]: 32 columns per block, 8 row lanes that are
+// combined in a fixed order (deterministic)
 template <typename T>
-__global__ void rows_sum_kernel(int rows, int D, const float* __restrict__ partial, T* __restrict__ out) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= D) return;
+__global__ void __launch_bounds__(256)
+rows_sum_kernel(int rows, int D, const float* __restrict__ partial, T* __restrict__ out) {
+  __shared__ float acc[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int r = 0; r < rows; ++r) s += partial[(long)r * D + j];
-  out[j] = from_f<T>(s);
+  if (j < D)
+    for (int r = ty; r < rows; r += 8) s += partial[(long)r * D + j];
+  acc[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += acc[k][tx];
+    out[j] = from_f<T>(t);
+  }
 }
 
 // xz [M, 2d] -> x_raw [M, d] (first half), x_act = silu(first half), z [M, d] (second half)
@@ -195,7 +208,7 @@ int grid_for(long n_items) {
 
 }  // namespace
 
-size_t add_rmsnorm_bwd_scratch_bytes(int D) { return (size_t)MAX_BLOCKS * D * sizeof(float); }
+size_t add_rmsnorm_bwd_scratch_bytes(int D) { return (size_t)BWD_BLOCKS * D * sizeof(float); }
 
 int add_rmsnorm_fwd(int dtype, long M, int D, const void* x, const float* res_in, const void* w,
                     float eps, float* res_out, void* y, float* rstd, cudaStream_t st) {
@@ -220,15 +233,15 @@ int add_rmsnorm_bwd(int dtype, long M, int D, const void* dy, const float* dres_
     ELMAN_CUDA_CHECK(cudaMemsetAsync(dw, 0, (size_t)D * (dtype == ELMAN_F32 ? 4 : 2), st));
     return ELMAN_OK;
   }
-  const int grid = (int)(M < MAX_BLOCKS ? M : MAX_BLOCKS);
+  const int grid = (int)(M < BWD_BLOCKS ? M : BWD_BLOCKS);
   if (dtype == ELMAN_F32) {
     add_rmsnorm_bwd_kernel<float><<<grid, NT, 0, st>>>(M, D, (const float*)dy, dres_out, res_out, rstd,
                                                       (const float*)w, dres_in, (float*)dx, scratch);
-    rows_sum_kernel<float><<<(D + 127) / 128, 128, 0, st>>>(grid, D, scratch, (float*)dw);
+    rows_sum_kernel<float><<<(D + 31) / 32, 256, 0, st>>>(grid, D, scratch, (float*)dw);
   } else {
     add_rmsnorm_bwd_kernel<bf16><<<grid, NT, 0, st>>>(M, D, (const bf16*)dy, dres_out, res_out, rstd,
                                                      (const bf16*)w, dres_in, (bf16*)dx, scratch);
-    rows_sum_kernel<bf16><<<(D + 127) / 128, 128, 0, st>>>(grid, D, scratch, (bf16*)dw);
+    rows_sum_kernel<bf16><<<(D + 31) / 32, 256, 0, st>>>(grid, D, scratch, (bf16*)dw);
   }
   count_launch(false);
   count_launch(false);

@@ -198,10 +198,7 @@ class LadderLM(nn.Module):
         main = torch.cuda.current_stream(h.device)
         pre_streams, rec_streams, post_streams = self._pipeline_streams(
             h.device, self._recurrence_stream_count(h, edges[1] - edges[0]))
-        shared = [layer.chunk_weights() for layer in self.layers]
-        # one transposed copy per layer and pass for the backward recurrences of all chunks
-        shared_t = [w.detach().t().contiguous() if (w is not None and torch.is_grad_enabled())
-                    else None for w in shared]
+        shared, shared_t = [None] * self.depth, [None] * self.depth
         # time-major chunks [Tc,B,D]: the cell's own layout, so no layer transposes anything
         h_chunks = [h[:, edges[c]:edges[c + 1]].transpose(0, 1).contiguous() for c in range(C)]
         start = torch.cuda.Event()   # everything the side streams read is enqueued before this
@@ -219,6 +216,15 @@ class LadderLM(nn.Module):
 
         for i, (ln, layer) in enumerate(zip(self.layer_norms, self.layers)):
             sp, sr, sq = pre_streams[i], rec_streams[i % len(rec_streams)], post_streams[i]
+            with torch.cuda.stream(sp):
+                # what all chunks of this layer share, on the layer's own stream: the effective
+                # W_h (the spectral-norm power iteration) of layer i is needed only when the
+                # wavefront reaches layer i, so the six of them overlap instead of queueing up
+                # in front of the first recurrence; likewise their backward passes
+                shared[i] = layer.chunk_weights()
+                # one transposed copy per layer and pass for the backward recurrences of all chunks
+                shared_t[i] = (shared[i].detach().t().contiguous()
+                               if (shared[i] is not None and torch.is_grad_enabled()) else None)
             d_inner = getattr(layer, "d_inner", self.dim)
             state = prev_hiddens[i]
             state = (torch.zeros(B, d_inner, device=h.device, dtype=h.dtype) if state is None

@@ -73,6 +73,11 @@ class GraphedTrainStep:
             self.reducer.finish()
         if self.after_backward is not None:
             self.after_backward(self.params)
+        if isinstance(self.opt, FlatAdamW) and self.reducer is not None:
+            # clipping folded into the update: the factor is applied as the gradients are read
+            coef = self.reducer.clip_coef(self.max_grad_norm)[0] if self.max_grad_norm else None
+            self.opt.step(grad_scale=coef)
+            return loss.detach()
         if self.max_grad_norm:
             if self.reducer is not None:
                 self.reducer.clip_(self.max_grad_norm)
@@ -221,12 +226,34 @@ class FlatGradients:
             torch.cuda.current_stream(self.flat.device).wait_stream(self.comm_stream)
         self.flat.mul_(1.0 / self.world)
 
+    def clip_coef(self, max_norm, eps=1e-6):
+        """(factor, norm): the factor clip_grad_norm_ would scale the gradients by —
+        min(1, max_norm / (|g| + eps)) — as a 0-dim fp32 device tensor, gradients untouched.
+        FlatAdamW applies it while it reads them."""
+        total = torch.linalg.vector_norm(self.flat, 2, dtype=torch.float32)
+        return torch.clamp(max_norm / (total + eps), max=1.0), total
+
+    def flatten_parameters(self):
+        """Moves the parameters themselves into one flat buffer with the layout of the
+        gradient buffer (every parameter becomes a view of it) and returns that buffer."""
+        if getattr(self, "flat_params", None) is None:
+            flat = torch.zeros_like(self.flat)
+            lo = self.flat.data_ptr()
+            with torch.no_grad():
+                for p in self.params:
+                    off = (p.grad.data_ptr() - lo) // self.flat.element_size()
+                    view = flat[off:off + p.numel()].view_as(p)
+                    view.copy_(p.data)
+                    p.data = view
+            self.flat_params = flat
+        return self.flat_params
+
     def clip_(self, max_norm, eps=1e-6):
         """torch.nn.utils.clip_grad_norm_ (train_ladder.py:542-543 of the reference) on the
         flat buffer: one norm, one scale, no host synchronisation.  Returns the norm."""
         total = torch.linalg.vector_norm(self.flat, 2, dtype=torch.float32)
         coef = torch.clamp(max_norm / (total + eps), max=1.0)
-        self.flat.mul_(coef.to(self.flat.dtype) if self.flat.dtype == torch.float64 else coef)
+        self.flat.mul_(coef.to(self.flat.dtype))   # same dtype: the vectorised kernel
         return total
 
     def check_views(self):
@@ -234,6 +261,57 @@ class FlatGradients:
         lo = self.flat.data_ptr()
         hi = lo + self.flat.numel() * self.flat.element_size()
         return all(p.grad is not None and lo <= p.grad.data_ptr() < hi for p in self.params)
+
+
+class FlatAdamW:
+    """AdamW (torch.optim.AdamW's update rule; train_ladder.py:360-365 of the reference) over
+    the flat parameter / gradient buffers of a FlatGradients: one kernel launch per step
+    (elman_adamw_step) instead of the per-tensor launches of the framework optimizer, with
+    the clipping factor applied while the gradients are read.  Moment estimates are kept in
+    the parameters' dtype, as torch.optim.AdamW keeps them.  The step counter lives on the
+    device, so a captured step advances it on every replay."""
+
+    def __init__(self, grads, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2):
+        if not grads.flat.is_cuda:
+            raise RuntimeError("FlatAdamW runs on CUDA buffers only (no CPU fallback)")
+        self.grads = grads
+        self.flat_params = grads.flatten_parameters()
+        self.exp_avg = torch.zeros_like(grads.flat)
+        self.exp_avg_sq = torch.zeros_like(grads.flat)
+        self.step_count = torch.zeros(1, dtype=torch.float32, device=grads.flat.device)
+        self.defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        self.param_groups = [dict(params=list(grads.params), **self.defaults)]
+
+    def zero_grad(self, set_to_none=False):
+        self.grads.zero()
+
+    def step(self, grad_scale=None):
+        from . import _lib
+        from . import hasty_pytorch_lib as H
+        g = self.param_groups[0]
+        flat = self.flat_params
+        if grad_scale is not None and (grad_scale.dtype != torch.float32 or not grad_scale.is_cuda):
+            raise RuntimeError("FlatAdamW.step: grad_scale must be a float32 CUDA tensor")
+        with torch.cuda.device(flat.device):
+            rc = _lib.load().elman_adamw_step(
+                H._DT[flat.dtype], flat.numel(), flat.data_ptr(), self.grads.flat.data_ptr(),
+                self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(), float(g["lr"]),
+                float(g["betas"][0]), float(g["betas"][1]), float(g["eps"]),
+                float(g["weight_decay"]), self.step_count.data_ptr(),
+                None if grad_scale is None else grad_scale.data_ptr(),
+                torch.cuda.current_stream(flat.device).cuda_stream)
+            _lib.check(rc, "elman_adamw_step")
+
+    def state_dict(self):
+        return {"step": self.step_count.clone(), "exp_avg": self.exp_avg.clone(),
+                "exp_avg_sq": self.exp_avg_sq.clone(), "param_groups": [
+                    {k: v for k, v in self.param_groups[0].items() if k != "params"}]}
+
+    def load_state_dict(self, sd):
+        self.step_count.copy_(sd["step"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.param_groups[0].update(sd["param_groups"][0])
 
 
 def ladder_buckets(model):

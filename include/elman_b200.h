@@ -408,6 +408,24 @@ int elman_in_proj_split_silu(int dtype, long M, int d_inner, int K, const void* 
 int elman_silu_backward_concat(int dtype, long M, int d_inner, const void* d_act, const void* x_raw,
                                const void* dz, void* dxz, void* stream);
 
+/*
+ * elman_adamw_step: one AdamW update (decoupled weight decay) of ALL parameters, which the
+ * caller keeps in one flat buffer, as are the gradients and both moment estimates — the
+ * optimizer step of the reference's training loop (torch.optim.AdamW + clip_grad_norm_,
+ * train_ladder.py:360-365, :542-545) as a single launch:
+ *     g = grads * (*grad_scale)          (grad_scale: device pointer or NULL = 1; the
+ *                                          clipping factor min(1, max_norm / |g|))
+ *     p *= 1 - lr * weight_decay
+ *     m = beta1 m + (1 - beta1) g;  v = beta2 v + (1 - beta2) g^2
+ *     p -= lr / (1 - beta1^t) * m / (sqrt(v) / sqrt(1 - beta2^t) + eps)
+ * `step` is a device float holding the number of updates done so far; the call advances it
+ * by one first (t is the advanced value), so a captured CUDA graph advances it on every
+ * replay.  Arithmetic in fp32, storage in `dtype`.
+ */
+int elman_adamw_step(int dtype, long n, void* params, const void* grads, void* exp_avg,
+                     void* exp_avg_sq, float lr, float beta1, float beta2, float eps,
+                     float weight_decay, float* step, const float* grad_scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -38,18 +38,18 @@ def test_add_rmsnorm_forward_and_backward_match_pytorch(dtype, rows, D, with_res
     dres = torch.randn(*rows, D, generator=g).cuda()
     eps = float(torch.finfo(dtype).eps)
     # reference: autograd through the fp32 math (straight-through the rounding of the input)
-    xr = x.float().requires_grad_(True)
+    xr = x.detach().float().clone().requires_grad_(True)
     rr = res_in.clone().requires_grad_(True) if with_res else None
-    wr = w.float().requires_grad_(True)
+    wr = w.detach().float().clone().requires_grad_(True)
     res = xr if rr is None else xr + rr
     v = res + (res.to(dtype).float() - res).detach()
     y_ref = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * wr
     (y_ref * dy.float()).sum().backward(retain_graph=True)
     (res * dres).sum().backward()
     # library
-    xq = x.clone().requires_grad_(True)
+    xq = x.detach().clone().requires_grad_(True)
     rq = res_in.clone().requires_grad_(True) if with_res else None
-    wq = w.clone().requires_grad_(True)
+    wq = w.detach().clone().requires_grad_(True)
     y, res_out = fused_ops.AddRMSNormFunction.apply(xq, rq, wq, eps)
     ((y.float() * dy.float()).sum() + (res_out * dres).sum()).backward()
     torch.cuda.synchronize()
@@ -96,10 +96,11 @@ def test_in_proj_function_gradients_match_pytorch(dtype, lead, d, K):
     W = (torch.randn(2 * d, K, generator=g) / K ** 0.5).to(dtype).cuda()
     da = torch.randn(*lead, d, generator=g).to(dtype).cuda()
     dzz = torch.randn(*lead, d, generator=g).to(dtype).cuda()
-    ur, Wr = u.float().requires_grad_(True), W.float().requires_grad_(True)
+    ur = u.detach().float().clone().requires_grad_(True)
+    Wr = W.detach().float().clone().requires_grad_(True)
     xz = ur @ Wr.T
     (F.silu(xz[..., :d]) * da.float() + xz[..., d:] * dzz.float()).sum().backward()
-    uq, Wq = u.clone().requires_grad_(True), W.clone().requires_grad_(True)
+    uq, Wq = u.detach().clone().requires_grad_(True), W.detach().clone().requires_grad_(True)
     xa, z = fused_ops.InProjSplitSiluFunction.apply(uq, Wq)
     (xa.float() * da.float() + z.float() * dzz.float()).sum().backward()
     torch.cuda.synchronize()
