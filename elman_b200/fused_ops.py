@@ -17,9 +17,13 @@ from . import hasty_pytorch_lib
 
 
 def rmsnorm_eps(norm_module, dtype):
-    """nn.RMSNorm's effective epsilon: its own, or the machine epsilon of the input dtype."""
+    """nn.RMSNorm's effective epsilon: its own if set, else the machine epsilon of the type
+    torch.rms_norm computes in — float32 for bfloat16 and float32 inputs (the documented
+    "finfo(input.dtype).eps" is not what the kernels use for 16-bit inputs)."""
     eps = getattr(norm_module, "eps", None)
-    return float(torch.finfo(dtype).eps) if eps is None else float(eps)
+    if eps is not None:
+        return float(eps)
+    return float(torch.finfo(torch.float64 if dtype == torch.float64 else torch.float32).eps)
 
 
 class AddRMSNormFunction(torch.autograd.Function):

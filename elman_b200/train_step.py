@@ -44,8 +44,9 @@ class GraphedTrainStep:
         side = torch.cuda.Stream(device=self.tokens.device)
         side.wait_stream(torch.cuda.current_stream(self.tokens.device))
         with torch.cuda.stream(side):
+            self.warmup_losses = []
             for _ in range(warmup_steps):  # eager: creates optimizer state, library handles, streams
-                self._eager_step()
+                self.warmup_losses.append(self._eager_step())
         torch.cuda.current_stream(self.tokens.device).wait_stream(side)
         torch.cuda.synchronize(self.tokens.device)
         self.graph = torch.cuda.CUDAGraph()

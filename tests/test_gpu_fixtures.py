@@ -156,3 +156,31 @@ def test_ladder_lm_on_gpu_matches_reference_fixture(golden_dir, chunks):
     for k, p in model.named_parameters():
         want = torch.from_numpy(fix["out_g_" + k])
         assert orc.rel_err(p.grad.float().cpu(), want) < TOL, k
+
+
+@pytest.mark.parametrize("chunks", [0, 4])
+def test_ladder_lm_bf16_gradients_match_the_fp32_model(chunks):
+    """bf16, every fused op on (add + RMSNorm kernels, in_proj epilogue, library GEMMs for
+    out_proj and the head, tcgen05 recurrences), against the same model in fp32: every
+    parameter gradient within the bf16 tolerance.  Embedding-sized activations (std 0.02) make
+    this sensitive to the norm's epsilon, which the small fp32 fixture is not."""
+    from elman_b200.ladder_lm import LadderLM, zipf_tokens
+    tok = zipf_tokens(8, 129, seed=300).cuda()
+
+    def make(**kw):
+        torch.manual_seed(29)
+        return LadderLM(vocab_size=256, dim=256, depth=3, level=1, r_h_mode="spectral_norm",
+                        **kw).cuda().bfloat16()
+
+    truth = make(pipeline_chunks=0).float()
+    truth(tok, return_loss=True).backward()
+    model = make(pipeline_chunks=chunks)
+    before = _lib.tc_launch_count()
+    loss = model(tok, return_loss=True)
+    loss.backward()
+    torch.cuda.synchronize()
+    assert _lib.tc_launch_count() > before and _lib.device_status()[0] == 0
+    for (n, p), q in zip(model.named_parameters(), truth.parameters()):
+        # W_h's gradient passes through the spectral-norm scale (a near-cancelling sum): wider
+        tol = 0.12 if n.endswith("W_h") else 4e-2
+        assert orc.rel_err(p.grad.float().cpu(), q.grad.cpu()) < tol, n

@@ -36,7 +36,7 @@ def test_add_rmsnorm_forward_and_backward_match_pytorch(dtype, rows, D, with_res
     w = (1 + 0.2 * torch.randn(D, generator=g)).to(dtype).cuda()
     dy = torch.randn(*rows, D, generator=g).to(dtype).cuda()
     dres = torch.randn(*rows, D, generator=g).cuda()
-    eps = float(torch.finfo(dtype).eps)
+    eps = fused_ops.rmsnorm_eps(torch.nn.RMSNorm(D), dtype)
     # reference: autograd through the fp32 math (straight-through the rounding of the input)
     xr = x.detach().float().clone().requires_grad_(True)
     rr = res_in.clone().requires_grad_(True) if with_res else None
@@ -65,6 +65,11 @@ def test_add_rmsnorm_forward_and_backward_match_pytorch(dtype, rows, D, with_res
         ref_mod.weight.copy_(w)
     base = x.float() if res_in is None else x.float() + res_in
     assert rel(y, ref_mod(base.to(dtype))) < tol
+    # ... also where the mean square is far below the 16-bit machine epsilon (embedding-sized
+    # activations): the default epsilon must be the one nn.RMSNorm really uses
+    small = (0.02 * x.float()).to(dtype)
+    ys, _ = fused_ops.AddRMSNormFunction.apply(small, None, w, fused_ops.rmsnorm_eps(ref_mod, dtype))
+    assert rel(ys, ref_mod(small)) < tol
 
 
 @pytest.mark.parametrize("M,d,K,generic", [(2048, 1280, 1280, 0), (192, 64, 64, 0), (50, 96, 40, 0),
