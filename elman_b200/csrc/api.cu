@@ -148,14 +148,15 @@ static size_t splitk_scratch_bytes(int dtype, int M, int N) {
   return dtype == ELMAN_BF16 ? (size_t)GEMM_MAX_KSPLIT * M * N * sizeof(float) : 0;
 }
 static int gemm_tn(int dtype, int M, int N, long K, const void* Am, const void* Bm, void* C,
-                   cudaStream_t st, float* splitk = nullptr, size_t splitk_bytes = 0) {
+                   cudaStream_t st, float* splitk = nullptr, size_t splitk_bytes = 0,
+                   int accumulate = 0) {
   if (M == 0 || N == 0) return ELMAN_OK;
   if (use_tc(dtype) && K < (1L << 31) && (M & 7) == 0 && (N & 7) == 0 && (K & 7) == 0 &&
       gemm_tc_supported(M, N, (int)K, Am, M, Bm, N, C, N, 0)) {
-    return gemm_tc(M, N, (int)K, (const bf16*)Am, M, 1, (const bf16*)Bm, N, 1, nullptr, C, N, 0, 0,
-                   st, splitk, splitk_bytes);
+    return gemm_tc(M, N, (int)K, (const bf16*)Am, M, 1, (const bf16*)Bm, N, 1, nullptr, C, N, 0,
+                   accumulate, st, splitk, splitk_bytes);
   }
-  return gemm_generic(dtype, M, N, (int)K, Am, 1, M, Bm, N, 1, nullptr, C, N, 0, st);
+  return gemm_generic(dtype, M, N, (int)K, Am, 1, M, Bm, N, 1, nullptr, C, N, accumulate, st);
 }
 
 // Optional per-phase timing with CUDA events on the caller's stream (option
@@ -891,7 +892,6 @@ int elman_gemm(int dtype, int op, int M, int N, int K, const void* A, const void
   ELMAN_ARG_CHECK(op == ELMAN_GEMM_NT || op == ELMAN_GEMM_NN || op == ELMAN_GEMM_TN,
                   "unknown GEMM form %d", op);
   ELMAN_ARG_CHECK(bias == nullptr || op == ELMAN_GEMM_NT, "bias only with ELMAN_GEMM_NT");
-  ELMAN_ARG_CHECK(!accumulate || op != ELMAN_GEMM_TN, "ELMAN_GEMM_TN overwrites C");
   ELMAN_RETURN_IF(check_status_on_entry());
   if (M == 0 || N == 0) return ELMAN_OK;
   REQUIRE_PTR(C);
@@ -904,7 +904,7 @@ int elman_gemm(int dtype, int op, int M, int N, int K, const void* A, const void
   REQUIRE_PTR(A); REQUIRE_PTR(B);
   if (op == ELMAN_GEMM_NT) return proj_nt(dtype, M, N, K, A, K, B, K, bias, C, N, accumulate, st);
   if (op == ELMAN_GEMM_NN) return gemm_nn(dtype, M, N, K, A, K, B, N, nullptr, C, N, accumulate, st);
-  return gemm_tn(dtype, M, N, K, A, B, C, st);
+  return gemm_tn(dtype, M, N, K, A, B, C, st, nullptr, 0, accumulate);
 }
 
 size_t elman_column_sum_workspace(int N) { return column_sum_scratch_bytes(N < 0 ? 0 : N); }

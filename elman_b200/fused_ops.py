@@ -16,6 +16,111 @@ import torch
 from . import hasty_pytorch_lib
 
 
+class GradSink:
+    """Weight gradients written by the GEMM that produces them straight into pre-allocated
+    buffers (C += A^T B), on side streams, instead of being returned to autograd.
+
+    Why: in the (layer, time chunk) pipeline every weight receives one gradient contribution
+    per chunk.  Returned to autograd, each contribution costs an extra add kernel, and the
+    weight-gradient GEMMs sit on the streams that carry the chain of data gradients from layer
+    to layer.  With a sink the autograd nodes return None for those weights and only the
+    data-gradient GEMMs stay on the chain (the same idea as gradient-accumulation fusion in
+    large-model trainers; the reference, which runs whole sequences layer by layer, has no
+    counterpart).  Contributions to one weight always come from the same compute stream, so
+    they are serialised on that stream's companion; `join()` makes a stream wait for all of
+    them.  The owner (FlatGradients) registers the targets and joins before it reads them.
+    """
+
+    def __init__(self):
+        self.targets = {}       # data_ptr of the weight -> gradient buffer shaped like it
+        self.streams = {}       # compute stream id -> companion stream
+        self.units_expected = {}
+        self.units_done = {}
+        self.on_group_done = None   # callback(group) once all units of a group ran backward
+
+    def register(self, weight, grad):
+        self.targets[weight.data_ptr()] = grad
+
+    def target(self, weight):
+        return self.targets.get(weight.data_ptr())
+
+    def _companion(self, device):
+        cur = torch.cuda.current_stream(device)
+        side = self.streams.get(cur.cuda_stream)
+        if side is None:
+            side = self.streams[cur.cuda_stream] = torch.cuda.Stream(device=device)
+        return cur, side
+
+    def accumulate_tn(self, grad, A, B):
+        """grad += A^T B (A [K,M], B [K,N]) on the companion of the current stream."""
+        H = hasty_pytorch_lib
+        if not A.is_cuda:                       # (test stand-ins) no streams to use
+            grad.add_(H.gemm(H.GEMM_TN, A, B))
+            return
+        cur, side = self._companion(A.device)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        side.wait_event(ready)
+        A.record_stream(side)
+        B.record_stream(side)
+        with torch.cuda.stream(side):
+            H.gemm(H.GEMM_TN, A, B, out=grad, accumulate=True)
+
+    def join(self, stream=None):
+        """Makes `stream` (default: the current one) wait for every accumulation issued so far."""
+        for side in self.streams.values():
+            stream = stream or torch.cuda.current_stream(side.device)
+            done = torch.cuda.Event()
+            done.record(side)
+            stream.wait_event(done)
+
+    # units: a group (one layer) is complete once all of its (layer, chunk) units have issued
+    # their backward work; the owner then may start reducing that group's gradients
+    def begin_pass(self):
+        self.units_expected.clear()
+        self.units_done.clear()
+
+    def expect_unit(self, group):
+        self.units_expected[group] = self.units_expected.get(group, 0) + 1
+
+    def unit_done(self, group):
+        self.units_done[group] = self.units_done.get(group, 0) + 1
+        if self.units_done[group] == self.units_expected.get(group, 0) and self.on_group_done:
+            self.on_group_done(group)
+
+
+_sink = None
+
+
+def set_grad_sink(sink):
+    """Installs (or, with None, removes) the process-wide GradSink the autograd nodes of this
+    package consult; returns the previous one."""
+    global _sink
+    old, _sink = _sink, sink
+    return old
+
+
+def get_grad_sink():
+    return _sink
+
+
+def weight_grad_tn(weight, A, B):
+    """dW = A^T B for `weight`: returned — or, if a sink holds a buffer for this weight and
+    gradients are being taken for it, accumulated there and None returned."""
+    sink = _sink
+    tgt = sink.target(weight) if (sink is not None and weight.requires_grad) else None
+    if tgt is not None:
+        # only if the buffer still IS this weight's gradient (an entry left behind by an
+        # earlier owner whose memory was reused must never divert a gradient)
+        g = getattr(weight, "grad", None)
+        if g is None or g.data_ptr() != tgt.data_ptr() or g.shape != tgt.shape:
+            tgt = None
+    if tgt is None:
+        return hasty_pytorch_lib.gemm(hasty_pytorch_lib.GEMM_TN, A, B)
+    sink.accumulate_tn(tgt, A, B)
+    return None
+
+
 def rmsnorm_eps(norm_module, dtype):
     """nn.RMSNorm's effective epsilon: its own if set, else the machine epsilon of the type
     torch.rms_norm computes in — float32 for bfloat16 and float32 inputs (the documented
@@ -31,8 +136,9 @@ class AddRMSNormFunction(torch.autograd.Function):
     residual_out = x + residual_in in fp32, y = RMSNorm(residual_out cast to x's dtype)."""
 
     @staticmethod
-    def forward(ctx, x, residual_in, weight, eps):
+    def forward(ctx, x, residual_in, weight, eps, unit_group=None):
         H = hasty_pytorch_lib
+        ctx.unit_group = unit_group   # this op opens a (layer, chunk) unit: its backward closes it
         xs = x.contiguous()
         y, res_out, rstd = H.add_rmsnorm_forward(
             xs, None if residual_in is None else residual_in.contiguous(), weight.contiguous(), eps)
@@ -58,7 +164,9 @@ class AddRMSNormFunction(torch.autograd.Function):
         dres_in, dx, dw = H.add_rmsnorm_backward(
             dy.contiguous(), None if dres_out is None else dres_out.contiguous(), res_out, rstd,
             weight.contiguous(), want_dres_in=ctx.has_residual, want_dx=True)
-        return dx, dres_in, dw, None
+        if ctx.unit_group is not None and _sink is not None:
+            _sink.unit_done(ctx.unit_group)
+        return dx, dres_in, dw, None, None
 
 
 class InProjSplitSiluFunction(torch.autograd.Function):
@@ -91,7 +199,7 @@ class InProjSplitSiluFunction(torch.autograd.Function):
             dz.record_stream(here)
         dxz = H.silu_backward_concat(d_act.contiguous().view(M, d), x_raw, dz.contiguous().view(M, d))
         du = H.gemm(H.GEMM_NN, dxz, W_in.contiguous())
-        dW = H.gemm(H.GEMM_TN, dxz, u2)
+        dW = weight_grad_tn(W_in, dxz, u2)
         return du.view(*ctx.lead, u2.shape[-1]), dW
 
 

@@ -74,18 +74,23 @@ class LadderLM(nn.Module):
             inp, target = x[:, :-1], x[:, 1:]
         else:
             inp = x
-        h = self.embedding(inp)
         if prev_hiddens is None:
             prev_hiddens = [None] * self.depth
+        sink = fused_ops.get_grad_sink()
+        if sink is not None and torch.is_grad_enabled():
+            sink.begin_pass()
         time_major = False
-        if self._can_pipeline(h):
+        if self._can_pipeline(inp):
+            # the pipeline is time-major throughout: gather the embedding rows in that order
+            h = self.embedding(inp.t())
             h, residual, new_hiddens = self._pipelined_layers(h, prev_hiddens)
             time_major = True
         else:
+            h = self.embedding(inp)
             new_hiddens = []
             residual = None
             for i, (ln, layer) in enumerate(zip(self.layer_norms, self.layers)):
-                h, residual = self._add_norm(ln, h, residual)
+                h, residual = self._add_norm(ln, h, residual, group=i)
                 h, h_final = layer(h, prev_hiddens[i])
                 new_hiddens.append(h_final)
         h, _ = self._add_norm(self.norm, h, residual, last=True)
@@ -118,13 +123,19 @@ class LadderLM(nn.Module):
                                    ignore_index=-100)
         return (loss, (new_hiddens, None)) if return_prev_hiddens else loss
 
-    def _add_norm(self, norm, h, residual, last=False):
+    def _add_norm(self, norm, h, residual, last=False, group=None):
         """residual = h + residual (fp32 stream); h = norm(residual in the layer's dtype).
-        Returns (h, residual); with `last` the residual is not needed any more."""
+        Returns (h, residual); with `last` the residual is not needed any more.  `group`: the
+        layer whose (layer, chunk) unit this op opens (told to the gradient sink, if any)."""
         if self.fused_ops and self.residual_in_fp32 and fused_ops.library_handles(h) \
                 and h.dtype == norm.weight.dtype:
+            sink = fused_ops.get_grad_sink()
+            if group is not None and sink is not None and torch.is_grad_enabled():
+                sink.expect_unit(group)
+            else:
+                group = None
             return fused_ops.AddRMSNormFunction.apply(
-                h, residual, norm.weight, fused_ops.rmsnorm_eps(norm, h.dtype))
+                h, residual, norm.weight, fused_ops.rmsnorm_eps(norm, h.dtype), group)
         residual = (h + residual) if residual is not None else h
         h = norm(residual.to(dtype=norm.weight.dtype))
         if self.residual_in_fp32 and not last:
@@ -150,7 +161,8 @@ class LadderLM(nn.Module):
     # wavefront by itself.  Chained chunks reproduce the unchunked layer exactly
     # (state carried forward, pre-activation gradient carried backward).
 
-    def _can_pipeline(self, h):
+    def _can_pipeline(self, inp):
+        h = inp
         return (self.pipeline_chunks > 1 and h.is_cuda and h.size(1) >= 2 * self.pipeline_chunks
                 and all(getattr(layer, "supports_time_chunks", False) for layer in self.layers))
 
@@ -170,7 +182,7 @@ class LadderLM(nn.Module):
         if self.pipeline_streams > 0:
             return self.pipeline_streams
         # layers may differ in width and plan: the widest launch decides
-        blocks = max(layer.chunk_recurrence_blocks(h.dtype, chunk_len, h.size(0),
+        blocks = max(layer.chunk_recurrence_blocks(h.dtype, chunk_len, h.size(1),
                                                    self.pipeline_flags) for layer in self.layers)
         sms = torch.cuda.get_device_properties(h.device).multi_processor_count
         n = sms // blocks if blocks > 0 else 2
@@ -192,15 +204,16 @@ class LadderLM(nn.Module):
 
     def _pipelined_layers(self, h, prev_hiddens):
         from .mamba_gated_elman import ChunkLink
-        B, T, _ = h.shape
+        T, B, _ = h.shape          # time-major [T,B,D]
         edges = self._chunk_edges(T)
         C = len(edges) - 1
         main = torch.cuda.current_stream(h.device)
         pre_streams, rec_streams, post_streams = self._pipeline_streams(
             h.device, self._recurrence_stream_count(h, edges[1] - edges[0]))
         shared, shared_t = [None] * self.depth, [None] * self.depth
-        # time-major chunks [Tc,B,D]: the cell's own layout, so no layer transposes anything
-        h_chunks = [h[:, edges[c]:edges[c + 1]].transpose(0, 1).contiguous() for c in range(C)]
+        # time-major chunks [Tc,B,D]: the cell's own layout, so no layer transposes anything;
+        # slices along the leading dimension are contiguous views, nothing is copied
+        h_chunks = [h[edges[c]:edges[c + 1]] for c in range(C)]
         start = torch.cuda.Event()   # everything the side streams read is enqueued before this
         start.record(main)
         for s in pre_streams + rec_streams + post_streams:
@@ -244,7 +257,7 @@ class LadderLM(nn.Module):
                     hin.record_stream(sp)
                     if rin is not None:
                         rin.record_stream(sp)
-                    hn, residual = self._add_norm(ln, hin, rin)
+                    hn, residual = self._add_norm(ln, hin, rin, group=i)
                     link = ChunkLink()
                     pre, z = layer.chunk_pre(hn, shared[i], link)
                     return pre, z, link, residual, record(sp)

@@ -100,6 +100,7 @@ class E1ChunkProjectionFunction(torch.autograd.Function):
         pre = hasty_pytorch_lib.gemm(hasty_pytorch_lib.GEMM_NT, x.view(T * B, d), W_x, b)
         ctx.save_for_backward(x, W_x)
         ctx.link = link
+        ctx.W_h_key = W_h     # only its identity is used: where its gradient goes
         return pre.view(T, B, d)
 
     @staticmethod
@@ -115,8 +116,10 @@ class E1ChunkProjectionFunction(torch.autograd.Function):
                 t.record_stream(here)
         G = hasty_pytorch_lib
         dx = G.gemm(G.GEMM_NN, dv, W_x).view(T, B, d)
-        dW_x = G.gemm(G.GEMM_TN, dv, x.view(T * B, d))
-        dW_h = G.gemm(G.GEMM_TN, dv, h[:T].view(T * B, d))
+        # weight gradients: into the gradient sink's buffers on a side stream when one is
+        # installed (only dx stays on the chain that the preceding layer waits for)
+        dW_x = fused_ops.weight_grad_tn(W_x, dv, x.view(T * B, d))
+        dW_h = fused_ops.weight_grad_tn(ctx.W_h_key, dv, h[:T].view(T * B, d))
         link.h = link.db = None
         return dx, dW_x, db, dW_h, None
 
@@ -139,7 +142,7 @@ class LinearFunction(torch.autograd.Function):
         G = hasty_pytorch_lib
         dy2 = dy.contiguous().view(-1, W.shape[0])
         dx = G.gemm(G.GEMM_NN, dy2, W).view(x.shape)
-        dW = G.gemm(G.GEMM_TN, dy2, x.reshape(-1, x.shape[-1]))
+        dW = fused_ops.weight_grad_tn(W, dy2, x.reshape(-1, x.shape[-1]))
         return dx, dW, (G.column_sum(dy2) if ctx.has_bias else None)
 
 

@@ -139,7 +139,10 @@ class FlatGradients:
     Per step: zero() -> forward/backward -> finish() -> clip_() -> optimizer.
     """
 
-    def __init__(self, buckets, group=None):
+    def __init__(self, buckets, group=None, direct=(), bucket_groups=None):
+        """`direct`: parameters whose gradient the library's GEMMs accumulate straight into
+        this buffer through a fused_ops.GradSink (installed here) instead of autograd;
+        `bucket_groups[i]`: the sink's unit group (layer index) that completes bucket i."""
         import torch.distributed as dist
         self.group = group
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
@@ -172,12 +175,49 @@ class FlatGradients:
                 p.grad = self.flat[off:off + p.numel()].view_as(p)
                 off += p.numel()
                 self._bucket_of[id(p)] = bi
-                if self.world > 1:
+                if self.world > 1 and id(p) not in {id(q) for q in direct}:
                     self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad_final))
             self._pending.append(len(b))
+        self.sink = None
+        direct_ids = {id(p) for p in direct}
+        if direct_ids:
+            from . import fused_ops
+            self.sink = fused_ops.GradSink()
+            for p in params:
+                if id(p) in direct_ids:
+                    self.sink.register(p, p.grad)
+            self.sink.on_group_done = self._on_group_done
+            fused_ops.set_grad_sink(self.sink)
+            # a bucket with direct parameters is complete when its remaining parameters' hooks
+            # have fired AND the sink reports its group done (one extra pending count)
+            groups = list(bucket_groups) if bucket_groups is not None else [None] * len(buckets)
+            self._group_bucket = {}
+            for bi, b in enumerate(buckets):
+                n_direct = sum(1 for p in b if id(p) in direct_ids)
+                if n_direct:
+                    self._pending[bi] += 1 - n_direct
+                    if groups[bi] is not None:
+                        self._group_bucket[groups[bi]] = bi
+        self._direct_ids = direct_ids
         self._sizes = list(self._pending)
         self.comm_stream = torch.cuda.Stream(device=device) if (device.type == "cuda" and self.world > 1) else None
         self._launched = 0
+
+    def close(self):
+        """Removes this object's gradient sink from the autograd nodes (they return their weight
+        gradients to autograd again) and its hooks."""
+        from . import fused_ops
+        if self.sink is not None and fused_ops.get_grad_sink() is self.sink:
+            fused_ops.set_grad_sink(None)
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
     def describe(self):
         if self.world == 1:
@@ -199,6 +239,14 @@ class FlatGradients:
         if self._pending[bi] == 0:
             self._reduce_bucket(bi)
 
+    def _on_group_done(self, group):
+        bi = getattr(self, "_group_bucket", {}).get(group)
+        if bi is None or self.world == 1:
+            return
+        self._pending[bi] -= 1
+        if self._pending[bi] == 0:
+            self._reduce_bucket(bi)
+
     def _reduce_bucket(self, bi):
         import torch.distributed as dist
         self._launched += 1
@@ -210,6 +258,8 @@ class FlatGradients:
         ready = torch.cuda.Event()
         ready.record(here)
         self.comm_stream.wait_event(ready)
+        if self.sink is not None:      # ... and the weight-gradient GEMMs on their side streams
+            self.sink.join(self.comm_stream)
         with torch.cuda.stream(self.comm_stream):
             dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
 
@@ -217,6 +267,8 @@ class FlatGradients:
         """After backward: buckets whose hooks did not all fire (a parameter without a
         gradient this step) are reduced now; the caller's stream then waits for the
         communication stream and the sums become means."""
+        if self.sink is not None:
+            self.sink.join()          # the caller's stream waits for the accumulating GEMMs
         if self.world == 1:
             return
         for bi, left in enumerate(self._pending):
@@ -247,6 +299,11 @@ class FlatGradients:
                     view.copy_(p.data)
                     p.data = view
             self.flat_params = flat
+            if self.sink is not None:     # the sink finds a weight by its address: re-register
+                self.sink.targets.clear()
+                for p in self.params:
+                    if id(p) in self._direct_ids:
+                        self.sink.register(p, p.grad)
         return self.flat_params
 
     def clip_(self, max_norm, eps=1e-6):
@@ -335,5 +392,34 @@ def ladder_buckets(model):
     return buckets
 
 
-def make_gradient_reducer(model, group=None):
-    return FlatGradients(ladder_buckets(model), group=group)
+def direct_weights(model):
+    """Weights of a LadderLM whose gradient contributions the library's GEMMs can accumulate
+    in place: the layers' projection matrices reached only through this package's autograd
+    nodes (not the tied embedding / head weight, which also receives an autograd gradient)."""
+    out = []
+    for layer in getattr(model, "layers", []):
+        if not getattr(layer, "fused", True) or getattr(layer, "use_conv", False):
+            continue
+        for name in ("in_proj", "out_proj"):
+            lin = getattr(layer, name, None)
+            if lin is not None and getattr(lin, "bias", None) is None:
+                out.append(lin.weight)
+        cell = getattr(layer, "cell", None)
+        if cell is not None and hasattr(cell, "W_x") and hasattr(layer, "in_proj"):
+            out.append(cell.W_x)
+            if getattr(cell, "w_h_mode", "none") in ("none", "free") and hasattr(cell, "W_h"):
+                out.append(cell.W_h)
+            if hasattr(cell, "W_gate"):
+                out.append(cell.W_gate)
+    return out
+
+
+def make_gradient_reducer(model, group=None, direct=True):
+    buckets = ladder_buckets(model)
+    layers = getattr(model, "layers", None)
+    groups = None
+    if layers is not None and len(buckets) >= len(layers):
+        groups = [len(layers) - 1 - bi if bi < len(layers) else None for bi in range(len(buckets))]
+    use_direct = direct and getattr(model, "fused_ops", False) and next(model.parameters()).is_cuda
+    return FlatGradients(buckets, group=group, direct=direct_weights(model) if use_direct else (),
+                         bucket_groups=groups)

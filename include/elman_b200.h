@@ -331,7 +331,8 @@ int elman_projection(int dtype, int M, int N, int K,
  * recurrence launches back to back on one stream and run the time-parallel GEMMs
  * of other chunks or layers beside them on another.
  *
- * elman_gemm: dense row-major operands, C[M,N] overwritten unless accumulate.
+ * elman_gemm: dense row-major operands, C[M,N] overwritten unless accumulate (then the
+ *   product is added to C: a weight gradient summed over several calls).
  *   ELMAN_GEMM_NT  C = A[M,K] B[N,K]^T (+ bias[N])     (blas<T>::gemm call sites of the
  *   ELMAN_GEMM_NN  C = A[M,K] B[K,N]                     reference: elman/cuda/lib/
  *   ELMAN_GEMM_TN  C = A[K,M]^T B[K,N]                   mamba_gated_elman_gpu.cu.cc:440-448,

@@ -187,3 +187,34 @@ def test_flat_gradient_buckets_are_averaged_over_two_gloo_ranks_as_they_complete
             assert views_ok and unused_sum == 0.0
             for a, b in zip(grads, want):
                 assert torch.allclose(a, b, atol=1e-6)
+
+
+def test_lm_gradients_with_the_gradient_sink_match_reference_fixture(monkeypatch):
+    """Weight gradients accumulated in place by the nodes that produce them (GradSink, through
+    FlatGradients(direct=...)) instead of returned to autograd: same loss, same gradients as
+    the reference fixture, for the whole sequence and for chained time chunks."""
+    from elman_b200 import fused_ops
+    from elman_b200.train_step import FlatGradients, direct_weights, ladder_buckets
+    fix = np.load(os.path.join(GOLDEN, "ladder_lm.npz"))
+    model = _build(fix, monkeypatch.setattr)
+    direct = direct_weights(model)
+    assert len(direct) == 3 * model.depth          # in_proj, out_proj, W_x (W_h is spectral-normed)
+    fg = FlatGradients(ladder_buckets(model), direct=direct)
+    try:
+        assert fused_ops.get_grad_sink() is fg.sink
+        tokens = torch.from_numpy(fix["in_tokens"])
+        for _ in range(2):                          # twice: zero() must reset the sums
+            for i, layer in enumerate(model.layers):    # the power iteration advances its vector
+                layer.cell._spectral_u = torch.from_numpy(fix[f"in_spectral_u_{i}"]).clone()
+            fg.zero()
+            loss = model(tokens, return_loss=True)
+            loss.backward()
+            fg.finish()
+            assert abs(float(loss) - float(fix["out_loss"][0])) < 1e-5
+            assert fg.check_views()
+            for k, p in model.named_parameters():
+                want = torch.from_numpy(fix["out_g_" + k])
+                assert orc.rel_err(p.grad, want) < 1e-4, k
+    finally:
+        fg.close()
+    assert fused_ops.get_grad_sink() is None
