@@ -210,7 +210,7 @@ static size_t carve_e1_bwd(int dtype, int T, int B, int d, void* ws, E1BwdWs* o)
   size_t es = esize(dtype);
   o->Wt = c.take((size_t)d * d * es);
   o->dv = c.take((size_t)(T + 1) * B * d * es);  // slot T: zero "gradient from the future"
-  o->db = (float*)c.take((size_t)d * sizeof(float));
+  o->db = (float*)c.take((size_t)REC_MAX_REPLICAS * d * sizeof(float));
   size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
   o->sync = (int*)c.take(sb);
   o->WxT = nullptr;  // the GEMMs read transposed operands in place
@@ -297,6 +297,7 @@ int elman_b200_set_option(const char* name, long value) {
   else if (!strcmp(name, "rec_fin_groups")) o.rec_fin_groups = value;
   else if (!strcmp(name, "gemm_persistent")) o.gemm_persistent = value;
   else if (!strcmp(name, "test_stall_step")) o.test_stall_step = value;
+  else if (!strcmp(name, "rec_replicas")) o.rec_replicas = value;
   else return set_error(ELMAN_ERR_ARG, "unknown option '%s'", name);
   return ELMAN_OK;
 }
@@ -317,6 +318,7 @@ long elman_b200_get_option(const char* name) {
   if (!strcmp(name, "rec_fin_groups")) return o.rec_fin_groups;
   if (!strcmp(name, "gemm_persistent")) return o.gemm_persistent;
   if (!strcmp(name, "test_stall_step")) return o.test_stall_step;
+  if (!strcmp(name, "rec_replicas")) return o.rec_replicas;
   return -1;
 }
 
@@ -558,7 +560,7 @@ static size_t carve_e0_bwd(int dtype, int T, int B, int d, void* ws, E0BwdWs* o)
   o->Wt = c.take((size_t)d * d * es);
   o->dv = c.take((size_t)(T + 1) * B * d * es);  // slot T: zero "gradient from the future"
   o->dg = c.take((size_t)T * B * d * es);
-  o->db = (float*)c.take((size_t)d * sizeof(float));
+  o->db = (float*)c.take((size_t)REC_MAX_REPLICAS * d * sizeof(float));
   o->cs = (float*)c.take(column_sum_scratch_bytes(d));
   size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
   o->sync = (int*)c.take(sb);
@@ -624,6 +626,7 @@ static inline int e5_rank_alloc(int dtype, int r) { return dtype == ELMAN_BF16 ?
 static inline int e5_rank_run(int dtype, int r) { return use_tc(dtype) ? (r + 63) / 64 * 64 : r; }
 
 struct E5FwdWs {
+  long long* trace;
   void* Vx; void* pre; void* Vz; void* gate; float* tmp; int* sync; void* UP; void* VP;
   void* UxP; void* VxP; void* UzP; void* VzP;
 };
@@ -637,6 +640,7 @@ static size_t carve_e5_fwd(int dtype, int T, int B, int d, int r, void* ws, E5Fw
   o->gate = c.take((size_t)T * B * d * es);
   o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
   o->sync = (int*)c.take(rec_sync_bytes());
+  o->trace = (long long*)c.take(kTraceBytes);
   o->UP = o->VP = o->UxP = o->VxP = o->UzP = o->VzP = nullptr;
   if (dtype == ELMAN_BF16) {  // zero-padded factors
     size_t up = 0, vp = 0;
@@ -697,7 +701,7 @@ int elman_e5_forward(int dtype, int training, int T, int B, int d, int r, const 
     ta.Urole = U_h; ta.Vrole = V_h;
     ta.in0 = w.pre; ta.in1 = w.gate;
     ta.state = h; ta.out0 = training ? v : nullptr; ta.out1 = output;
-    ta.UP = w.UP; ta.VP = w.VP; ta.sync = w.sync;
+    ta.UP = w.UP; ta.VP = w.VP; ta.sync = w.sync; ta.trace = w.trace;
     return lowrank_tc(ta, st);
   }
   LowRankFwdArgs a{T, B, d, r, U_h, V_h, w.pre, w.gate, h, output, training ? v : nullptr, w.tmp,
@@ -711,6 +715,8 @@ struct E5BwdWs {
   void* UP; void* VP;
   void* P[6];    // zero-padded U_h, V_h, U_x, V_x, U_z, V_z
   void* dUP; void* dVP;  // padded weight-gradient scratch
+  long long* trace;
+  float* splitk; size_t splitk_bytes;   // fp32 partial sums of the weight-gradient GEMMs
 };
 static size_t carve_e5_bwd(int dtype, int T, int B, int d, int r, void* ws, E5BwdWs* o) {
   Carver c(ws);
@@ -726,6 +732,9 @@ static size_t carve_e5_bwd(int dtype, int T, int B, int d, int r, void* ws, E5Bw
   o->db = (float*)c.take((size_t)d * sizeof(float));
   o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
   o->sync = (int*)c.take(rec_sync_bytes());
+  o->trace = (long long*)c.take(kTraceBytes);
+  o->splitk_bytes = splitk_scratch_bytes(dtype, d, ra);
+  o->splitk = o->splitk_bytes ? (float*)c.take(o->splitk_bytes) : nullptr;
   o->Vx = c.take(TBr);
   o->Vh = c.take(TBr);
   o->dVx = c.take(TBr);
@@ -833,7 +842,7 @@ int elman_e5_backward_carry(int dtype, int T, int B, int d, int r, const void* U
     ta.Urole = w.Vt; ta.Vrole = w.Ut;
     ta.in0 = w.gate; ta.in1 = d_output; ta.in2 = h; ta.in3 = v;
     ta.state = w.dv; ta.out0 = w.dg; ta.out1 = nullptr; ta.db = w.db;
-    ta.UP = w.UP; ta.VP = w.VP; ta.sync = w.sync;
+    ta.UP = w.UP; ta.VP = w.VP; ta.sync = w.sync; ta.trace = w.trace;
     ELMAN_RETURN_IF(lowrank_tc(ta, st));
   } else {
     LowRankBwdArgs a{T, B, d, r, w.Ut, w.Vt, h, v, w.gate, d_output, w.dv, w.dg, w.db, w.tmp,
@@ -859,11 +868,11 @@ int elman_e5_backward_carry(int dtype, int T, int B, int d, int r, const void* U
   for (const Job& jb : jobs) {
     if (jb.is_u) {  // dU [d, r] = A^T [d, TB] * Bm [TB, rp]
       void* out = padded ? w.dUP : jb.dU_or_dV;
-      ELMAN_RETURN_IF(gemm_tn(dtype, d, rp, TB, jb.A, jb.Bm, out, st));
+      ELMAN_RETURN_IF(gemm_tn(dtype, d, rp, TB, jb.A, jb.Bm, out, st, w.splitk, w.splitk_bytes));
       if (padded) ELMAN_RETURN_IF(resize2d(dtype, out, d, rp, jb.dU_or_dV, d, r, st));
     } else {        // dV [r, d] = A^T [rp, TB] * Bm [TB, d]
       void* out = padded ? w.dVP : jb.dU_or_dV;
-      ELMAN_RETURN_IF(gemm_tn(dtype, rp, d, TB, jb.A, jb.Bm, out, st));
+      ELMAN_RETURN_IF(gemm_tn(dtype, rp, d, TB, jb.A, jb.Bm, out, st, w.splitk, w.splitk_bytes));
       if (padded) ELMAN_RETURN_IF(copy_rows(dtype, out, jb.dU_or_dV, (long)r * d, st));
     }
   }
@@ -927,7 +936,7 @@ struct E1RecWs { void* Wt; float* db; int* sync; };
 static size_t carve_e1_rec(int dtype, int d, void* ws, E1RecWs* o) {
   Carver c(ws);
   o->Wt = c.take((size_t)d * d * esize(dtype));
-  o->db = (float*)c.take((size_t)d * sizeof(float));
+  o->db = (float*)c.take((size_t)REC_MAX_REPLICAS * d * sizeof(float));
   size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
   o->sync = (int*)c.take(sb);
   return c.total();

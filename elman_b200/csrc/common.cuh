@@ -56,6 +56,7 @@ struct Options {
   // Failure-detection test hook: >= 1 makes thread block 0 of the tensor-core kernels wait, at
   // that step (GEMM: K iteration), for something nothing will deliver, so that a real bounded
   // wait runs out and the give-up path of every role executes.  -1 = off.
+  long rec_replicas = 0;       // batch replicas of the throughput plan: 0 auto, 1 off, n = at most n
   long test_stall_step = -1;
 };
 Options& options();
@@ -225,6 +226,9 @@ int lowrank_fwd_generic(int dtype, const LowRankFwdArgs& a, cudaStream_t stream)
 int lowrank_bwd_generic(int dtype, const LowRankBwdArgs& a, cudaStream_t stream);
 
 // Dense recurrence, bf16, tcgen05 + TMA persistent cluster kernel.
+// Batch replicas of a recurrence grid (throughput plan); the backward kernel writes one row of
+// bias-gradient sums per replica, so callers give its `db` REC_MAX_REPLICAS * d floats.
+constexpr int REC_MAX_REPLICAS = 4;
 bool rec_tc_supported(int T, int B, int d, int bwd);   // per direction: the plans differ
 // resident thread blocks of one launch (compact: smallest-footprint plan), 0 if unsupported
 int rec_tc_blocks(int T, int B, int d, int compact);
@@ -233,6 +237,8 @@ int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream);
 int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream);
 // Copies the cycle stamps of the last traced launch (option rec_trace) to the host.
 int rec_tc_copy_trace(long long* dst, int max_entries);
+void set_last_trace(long long* device_buffer);   // the buffer the next copy reads
+constexpr size_t kTraceBytes = 64 * 16 * sizeof(long long);
 
 // Low-rank (E5) recurrence, bf16, tcgen05: one cluster of d/128 CTAs, the rank-r
 // intermediate exchanged through distributed shared memory only.
@@ -248,6 +254,7 @@ struct LowRankTcArgs {
   void* state; void* out0; void* out1; float* db;
   void* UP; void* VP;  // scratch for the zero-padded factors (lowrank_tc_pad_bytes)
   int* sync;           // 256 bytes
+  long long* trace = nullptr;   // optional 64 x 16 cycle stamps (option rec_trace)
 };
 bool lowrank_tc_supported(int T, int B, int d, int r, int bwd);
 int lowrank_tc_blocks(int T, int B, int d, int r);   // resident blocks (one cluster), 0 if unsupported

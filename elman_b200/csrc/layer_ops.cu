@@ -125,6 +125,147 @@ add_rmsnorm_bwd_kernel(long M, int D, const T* __restrict__ dy, const float* __r
   }
 }
 
+// ---- bf16 rows whose length is a multiple of 8: 16-byte accesses, each row read once ----
+constexpr int VCH = 2;   // 8-element chunks a thread keeps in registers: rows up to VCH*NT*8 wide
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 t = __bfloat1622float2(h[q]);
+    f[2 * q] = t.x;
+    f[2 * q + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+  return u;
+}
+
+__global__ void __launch_bounds__(NT)
+add_rmsnorm_fwd_bf16x8_kernel(long M, int D, const uint4* __restrict__ x, const float4* __restrict__ res_in,
+                              const uint4* __restrict__ w, float eps, float4* __restrict__ res_out,
+                              uint4* __restrict__ y, float* __restrict__ rstd_out) {
+  __shared__ float red[NT / 32];
+  const int nch = D / 8;
+  for (long row = blockIdx.x; row < M; row += gridDim.x) {
+    float v[VCH][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VCH; ++k) {
+      const int c = threadIdx.x + k * NT;
+      if (c < nch) {
+        float r[8];
+        unpack8(x[row * nch + c], r);
+        if (res_in != nullptr) {
+          const float4 a = res_in[(row * nch + c) * 2], b = res_in[(row * nch + c) * 2 + 1];
+          r[0] += a.x; r[1] += a.y; r[2] += a.z; r[3] += a.w;
+          r[4] += b.x; r[5] += b.y; r[6] += b.z; r[7] += b.w;
+        }
+        res_out[(row * nch + c) * 2] = make_float4(r[0], r[1], r[2], r[3]);
+        res_out[(row * nch + c) * 2 + 1] = make_float4(r[4], r[5], r[6], r[7]);
+        unpack8(pack8(r), v[k]);          // the norm sees the residual rounded to bf16
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += v[k][e] * v[k][e];
+      }
+    }
+    const float rs = rsqrtf(block_sum(ss, red) / (float)D + eps);
+    if (threadIdx.x == 0) rstd_out[row] = rs;
+#pragma unroll
+    for (int k = 0; k < VCH; ++k) {
+      const int c = threadIdx.x + k * NT;
+      if (c < nch) {
+        float wf[8], o[8];
+        unpack8(w[c], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = v[k][e] * rs * wf[e];
+        y[row * nch + c] = pack8(o);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(NT)
+add_rmsnorm_bwd_bf16x8_kernel(long M, int D, const uint4* __restrict__ dy, const float4* __restrict__ dres_out,
+                              const float4* __restrict__ res_out, const float* __restrict__ rstd,
+                              const uint4* __restrict__ w, float4* __restrict__ dres_in,
+                              uint4* __restrict__ dx, float* __restrict__ dw_partial) {
+  __shared__ float red[NT / 32];
+  const int nch = D / 8;
+  float dwacc[VCH][8];
+  float wf[VCH][8];
+#pragma unroll
+  for (int k = 0; k < VCH; ++k) {
+    const int c = threadIdx.x + k * NT;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { dwacc[k][e] = 0.f; wf[k][e] = 0.f; }
+    if (c < nch) unpack8(w[c], wf[k]);
+  }
+  for (long row = blockIdx.x; row < M; row += gridDim.x) {
+    const float rs = rstd[row];
+    float dyv[VCH][8], xh[VCH][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < VCH; ++k) {
+      const int c = threadIdx.x + k * NT;
+      if (c < nch) {
+        unpack8(dy[row * nch + c], dyv[k]);
+        const float4 a = res_out[(row * nch + c) * 2], b = res_out[(row * nch + c) * 2 + 1];
+        const float r[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        unpack8(pack8(r), xh[k]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[k][e] *= rs;
+          dot += dyv[k][e] * wf[k][e] * xh[k][e];
+        }
+      }
+    }
+    const float cmean = block_sum(dot, red) / (float)D;
+#pragma unroll
+    for (int k = 0; k < VCH; ++k) {
+      const int c = threadIdx.x + k * NT;
+      if (c < nch) {
+        float g[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          g[e] = rs * (dyv[k][e] * wf[k][e] - xh[k][e] * cmean);
+          dwacc[k][e] += dyv[k][e] * xh[k][e];
+        }
+        if (dres_out != nullptr) {
+          const float4 a = dres_out[(row * nch + c) * 2], b = dres_out[(row * nch + c) * 2 + 1];
+          g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+          g[4] += b.x; g[5] += b.y; g[6] += b.z; g[7] += b.w;
+        }
+        if (dres_in != nullptr) {
+          dres_in[(row * nch + c) * 2] = make_float4(g[0], g[1], g[2], g[3]);
+          dres_in[(row * nch + c) * 2 + 1] = make_float4(g[4], g[5], g[6], g[7]);
+        }
+        if (dx != nullptr) dx[row * nch + c] = pack8(g);
+      }
+    }
+  }
+  float4* dwp = reinterpret_cast<float4*>(dw_partial + (long)blockIdx.x * D);
+#pragma unroll
+  for (int k = 0; k < VCH; ++k) {
+    const int c = threadIdx.x + k * NT;
+    if (c < nch) {
+      dwp[c * 2] = make_float4(dwacc[k][0], dwacc[k][1], dwacc[k][2], dwacc[k][3]);
+      dwp[c * 2 + 1] = make_float4(dwacc[k][4], dwacc[k][5], dwacc[k][6], dwacc[k][7]);
+    }
+  }
+}
+
+bool rows_vectorisable(int dtype, int D, const void* a, const void* b, const void* c, const void* d,
+                       const void* e, const void* f) {
+  if (dtype != ELMAN_BF16 || (D & 7) != 0 || D > VCH * NT * 8) return false;
+  const uintptr_t bits = (uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d | (uintptr_t)e |
+                         (uintptr_t)f;
+  return (bits & 15) == 0;
+}
+
 // out[j] = sum over the rows of partial[rows, D]: 32 columns per block, 8 row lanes that are
 // combined in a fixed order (deterministic)
 template <typename T>
@@ -214,7 +355,11 @@ int add_rmsnorm_fwd(int dtype, long M, int D, const void* x, const float* res_in
                     float eps, float* res_out, void* y, float* rstd, cudaStream_t st) {
   if (M == 0 || D == 0) return ELMAN_OK;
   const int grid = (int)(M < MAX_BLOCKS ? M : MAX_BLOCKS);
-  if (dtype == ELMAN_F32)
+  if (rows_vectorisable(dtype, D, x, res_in, w, res_out, y, nullptr))
+    add_rmsnorm_fwd_bf16x8_kernel<<<grid, NT, 0, st>>>(M, D, (const uint4*)x, (const float4*)res_in,
+                                                      (const uint4*)w, eps, (float4*)res_out,
+                                                      (uint4*)y, rstd);
+  else if (dtype == ELMAN_F32)
     add_rmsnorm_fwd_kernel<float><<<grid, NT, 0, st>>>(M, D, (const float*)x, res_in, (const float*)w,
                                                       eps, res_out, (float*)y, rstd);
   else
@@ -234,7 +379,13 @@ int add_rmsnorm_bwd(int dtype, long M, int D, const void* dy, const float* dres_
     return ELMAN_OK;
   }
   const int grid = (int)(M < BWD_BLOCKS ? M : BWD_BLOCKS);
-  if (dtype == ELMAN_F32) {
+  if (rows_vectorisable(dtype, D, dy, dres_out, res_out, w, dres_in, dx) &&
+      ((uintptr_t)scratch & 15) == 0) {
+    add_rmsnorm_bwd_bf16x8_kernel<<<grid, NT, 0, st>>>(
+        M, D, (const uint4*)dy, (const float4*)dres_out, (const float4*)res_out, rstd, (const uint4*)w,
+        (float4*)dres_in, (uint4*)dx, scratch);
+    rows_sum_kernel<bf16><<<(D + 31) / 32, 256, 0, st>>>(grid, D, scratch, (bf16*)dw);
+  } else if (dtype == ELMAN_F32) {
     add_rmsnorm_bwd_kernel<float><<<grid, NT, 0, st>>>(M, D, (const float*)dy, dres_out, res_out, rstd,
                                                       (const float*)w, dres_in, (float*)dx, scratch);
     rows_sum_kernel<float><<<(D + 31) / 32, 256, 0, st>>>(grid, D, scratch, (float*)dw);

@@ -53,6 +53,7 @@ struct LowRankTcParams {
   int* abort_word;
   int* status;
   long spin_limit;
+  long long* trace;   // optional cycle stamps of CTA 0 ([64 steps][16 slots]), or null
   int stall_step;   // test hook: block 0 withholds its share of the rank vector at this step (-1 off)
 };
 
@@ -68,6 +69,14 @@ __device__ __forceinline__ bool lr_bar_or(bool pred) {
       : "r"((uint32_t)pred), "n"(LR_EPI_THREADS)
       : "memory");
   return r != 0;
+}
+
+// Cycle stamps of CTA 0 for its first 64 steps (diagnostics, option rec_trace): 0 state ready,
+// 1 phase-1 MMAs issued, 2 phase-1 accumulators complete, 3 partials sent, 4 partials of my
+// chunk landed, 5 chunk summed, 6 chunk gathered out, 7 rank vector landed, 8 phase-2 MMAs
+// issued, 9 phase-2 accumulators complete, 10 new state written
+__device__ __forceinline__ void lr_stamp(long long* trace, int c, int s, int slot) {
+  if (trace != nullptr && c == 0 && s < 64) trace[s * 16 + slot] = clock64();
 }
 
 // byte offset of element (row b, column k) in a K-major bf16 operand made of
@@ -108,7 +117,10 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
   uint8_t* sU = smem;                                   // nku tiles [128 x 64] (A of phase 2)
   const int h_tile = Npad * 128;                        // bytes of one [Npad x 64] tile
   uint8_t* sH = sU + nku * 16384;                       // 2 tiles: my slice of the state
-  uint8_t* sVh = sH + 2 * h_tile;                       // nku tiles: the rank-r vector
+  // the rank-r vector as phase 2 reads it: one [Npad x 32 columns] tile per owner chunk, rows of
+  // 64 bytes with 64-byte swizzle, so that each owner's piece is one contiguous block
+  uint8_t* sVh = sH + 2 * h_tile;
+  const int vh_tile = Npad * 64;
   uint8_t* sStage = sVh + nku * h_tile;                 // [NC][Npad/4][32 rows][4] fp32 partials
   const int stage_src_bytes = 32 * Npad * 4;
   uint8_t* sGather = sStage + NC * stage_src_bytes;     // [Npad][32 rank columns] bf16
@@ -210,6 +222,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
         // ---- phase 1: partial[rank, batch] = V[:, my block] * state[my block] ----
         ok = (s == 0) ? waiter.wait(&h0_bar, 0) : waiter.wait(&h_ready, (uint32_t)(s - 1) & 1u);
         if (!ok) break;
+        if (mw == 0) lr_stamp(p.trace, c, s, 0);
         ptx::tc_fence_after();
         for (int ch = mw; ch < nch1; ch += LR_MMA_WARPS) {
           const int mt = ch >> 1, half = ch & 1;
@@ -221,21 +234,24 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
                               db0 + 2 * k, idesc, k > 0 ? 1u : 0u);
         }
         if (mw < nch1) ptx::umma_commit(&acc1_full);
+        if (mw == 0) lr_stamp(p.trace, c, s, 1);
         // ---- phase 2: out[my block, batch] = U[my block, :] * Vh ----
         ok = waiter.wait_cluster(&vh_full, (uint32_t)s & 1u);
         if (!ok) break;
-        ptx::fence_proxy_async_smem();
+        if (mw == 0) lr_stamp(p.trace, c, s, 7);
         ptx::tc_fence_after();
         if (mw < nmw2) {
           const uint32_t d_tmem = tmem_base + acc_col0 + (uint32_t)(mw * Npad);
           for (int m = mw; m < p.r_pad / 16; m += nmw2) {
             const int kk = m >> 2, k = m & 3;
             const uint64_t da = ptx::umma_desc_k_sw128(sU_a + kk * 16384) + 2 * k;
-            const uint64_t db = ptx::umma_desc_k_sw128(sVh_a + kk * h_tile) + 2 * k;
+            // 16 rank columns = half of owner chunk m/2's tile
+            const uint64_t db = ptx::umma_desc_k_sw64(sVh_a + (m >> 1) * vh_tile) + 2 * (m & 1);
             ptx::umma_bf16(d_tmem, da, db, idesc, m >= nmw2 ? 1u : 0u);
           }
           ptx::umma_commit(&acc2_full);
         }
+        if (mw == 0) lr_stamp(p.trace, c, s, 8);
       }
       if (!ok) {
         if (abort_flag == 0 && atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, kid, 0xFFFFF1);
@@ -265,6 +281,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
       // ---- drain phase 1 and send every 32-row chunk of the partial to its owner ----
       bool good = waiter.wait(&acc1_full, par);
       good = __all_sync(0xffffffffu, good);
+      if (et == 0) lr_stamp(p.trace, c, s, 2);
       if (good) {
         ptx::tc_fence_after();
         for (int mt = 0; mt < Mr; ++mt) {
@@ -290,10 +307,12 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
           }
         }
         ptx::tc_fence_before();
+        if (et == 0) lr_stamp(p.trace, c, s, 3);
         // ---- owner: add the NC partials of my chunk, round to bf16 ----
         if (is_owner) {
           good = waiter.wait_cluster(&part_full, par);
           good = __all_sync(0xffffffffu, good);
+          if (et == 0) lr_stamp(p.trace, c, s, 4);
           if (good) {
             const int rl = et & 31, bgrp = et >> 5;
             for (int q4 = bgrp; q4 < Npad / 4; q4 += 4) {
@@ -302,15 +321,22 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
                 const float4 x = lds_f4(stage_a + (uint32_t)(src * stage_src_bytes + (q4 * 32 + rl) * 16));
                 acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
               }
-              const uint32_t g0 = gather_a + (uint32_t)((4 * q4) * 64 + rl * 2);
-              sts_u16(g0, f_to_bf16_bits(acc.x));
-              sts_u16(g0 + 64, f_to_bf16_bits(acc.y));
-              sts_u16(g0 + 128, f_to_bf16_bits(acc.z));
-              sts_u16(g0 + 192, f_to_bf16_bits(acc.w));
+              // batch rows 4 q4 .. 4 q4 + 3, rank column rl of my chunk, in the 64-byte-swizzled
+              // tile layout phase 2 reads: chunk (rl / 8) ^ ((row / 2) % 4) of the 64-byte row
+              const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int b = 4 * q4 + u;
+                sts_u16(gather_a + (uint32_t)(b * 64 + ((((rl >> 3) ^ ((b >> 1) & 3))) << 4) +
+                                              ((rl & 7) << 1)),
+                        f_to_bf16_bits(vals[u]));
+              }
             }
+            ptx::fence_proxy_async_smem();   // these writes are read by the bulk copies below
           }
         }
       }
+      if (et == 0) lr_stamp(p.trace, c, s, 5);
       if (!good) {
         if (abort_flag == 0 && atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, kid, s);
         abort_flag = 1;
@@ -319,17 +345,15 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
       // barrier also orders last step's bulk-store reads before this step's tile writes
       if (lr_bar_or(!good || abort_flag != 0)) { abort_flag = 1; break; }
       // ---- owner: all-gather my bf16 chunk into every CTA's phase-2 operand tile ----
-      if (is_owner && et < Npad * 4 && !(s == p.stall_step && c == 0)) {
-        const int b = et >> 2, ch = et & 3;
-        const uint4 v = lds_u4(gather_a + (uint32_t)(b * 64 + ch * 16));
-        const uint32_t off = (uint32_t)((c >> 1) * h_tile + b * 128 + (((((c & 1) << 2) + ch) ^ (b & 7)) << 4));
-        for (int dst = 0; dst < NC; ++dst)
-          st_async_v4(mapa(sVh_a + off, (uint32_t)dst), v.x, v.y, v.z, v.w,
-                      mapa(ptx::smem_u32(&vh_full), (uint32_t)dst));
-      }
+      // one bulk copy of the whole [Npad x 32] tile per destination CTA (slot c of its operand)
+      if (is_owner && et < NC && !(s == p.stall_step && c == 0))
+        bulk_copy_to_peer(mapa(sVh_a + (uint32_t)(c * vh_tile), (uint32_t)et), gather_a,
+                          (uint32_t)vh_tile, mapa(ptx::smem_u32(&vh_full), (uint32_t)et));
+      if (et == 0) lr_stamp(p.trace, c, s, 6);
       // ---- drain phase 2, fused tanh / gate epilogue for my feature, all batch rows ----
       good = waiter.wait(&acc2_full, par) && waiter.wait(&in_full, par);
       good = __all_sync(0xffffffffu, good);
+      if (et == 0) lr_stamp(p.trace, c, s, 9);
       if (good) {
         ptx::tc_fence_after();
         for (int cb = 0; cb < Npad; cb += 16) {
@@ -385,6 +409,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
           ptx::mbar_arrive(&h_ready);
           ptx::mbar_arrive(&in_empty);
         }
+        if (et == 0) lr_stamp(p.trace, c, s, 10);
       } else {
         if (abort_flag == 0 && atomicExch(p.abort_word, 1) == 0) report_timeout(p.status, kid, s);
         abort_flag = 1;
@@ -603,6 +628,12 @@ int lowrank_tc(const LowRankTcArgs& a, cudaStream_t stream) {
   p.status = device_status_ptr();
   p.spin_limit = options().spin_limit;
   p.stall_step = (int)options().test_stall_step;
+  p.trace = nullptr;
+  if (options().rec_trace != 0 && a.trace != nullptr) {
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(a.trace, 0, 64 * 16 * sizeof(long long), stream));
+    p.trace = a.trace;
+    set_last_trace(a.trace);
+  }
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr;
   if (bwd) {

@@ -68,6 +68,8 @@ struct RecTcParams {
   int Npad;     // Ng rounded up to 16 (MMA N)
   int nstages;  // state ring depth
   int R;        // d / 128: producers per K slice and step
+  int reps;     // batch replicas of the whole grid (independent: they never wait on each other)
+  int Brep;     // batch rows per replica (= G * Ng)
   int direct_publish;  // 1: each epilogue warp releases the step counter itself
   int w_tmem;          // 1: the resident tile of W lives in tensor memory (A operand from TMEM)
   uint32_t w_col0;     // first TMEM column of that tile
@@ -308,7 +310,14 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
   const int S = p.S, Kc = p.Kc, Npad = p.Npad, Ng = p.Ng, G = p.G, nmw = p.nmw;
   const int rows_own = TILE_M / S;
   const uint32_t j = cluster_ctarank();   // K slice index == rank in cluster
-  const int i = blockIdx.x / S;           // row block index
+  // Batch replicas: the grid is `reps` copies of the (d/128) x S arrangement, copy r working
+  // on batch rows [r * Brep, (r+1) * Brep) with step counters of its own.  Sequences are
+  // independent, so the copies share nothing but the weights they each load once.
+  const int per_rep = (p.d / TILE_M) * S;
+  const int rep = blockIdx.x / per_rep;
+  const int i = (blockIdx.x - rep * per_rep) / S;   // row block index
+  const int b0 = rep * p.Brep;                      // first batch row of this replica
+  int* const ready = p.ready + rep * G * MAX_S * COUNTER_STRIDE;
   const int nkt = Kc / 64;                // 64-column tiles per K slice
   const int total_q = p.T * G;
 
@@ -413,16 +422,16 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
           const int f0 = i * TILE_M + (int)j * rows_own;
           uint8_t* dst = sIn + (q & 1) * NIN * in_tile_bytes;
           ptx::mbar_arrive_expect_tx(&in_full[q & 1], (uint32_t)(NIN * in_tile_bytes));
-          tma_load_3d(dst, &tmI0, f0, grp * Ng, t, &in_full[q & 1]);
-          tma_load_3d(dst + in_tile_bytes, &tmI1, f0, grp * Ng, t, &in_full[q & 1]);
+          tma_load_3d(dst, &tmI0, f0, b0 + grp * Ng, t, &in_full[q & 1]);
+          tma_load_3d(dst + in_tile_bytes, &tmI1, f0, b0 + grp * Ng, t, &in_full[q & 1]);
           if (BWD) {
-            tma_load_3d(dst + 2 * in_tile_bytes, &tmI2, f0, grp * Ng, t + 1, &in_full[q & 1]);
-            tma_load_3d(dst + 3 * in_tile_bytes, &tmI3, f0, grp * Ng, t, &in_full[q & 1]);
+            tma_load_3d(dst + 2 * in_tile_bytes, &tmI2, f0, b0 + grp * Ng, t + 1, &in_full[q & 1]);
+            tma_load_3d(dst + 3 * in_tile_bytes, &tmI3, f0, b0 + grp * Ng, t, &in_full[q & 1]);
           }
         }
         ok = ok && waiter.wait(&empty_bar[s], ph ^ 1u);
         if (ok && step > 0)
-          ok = waiter.wait_counter(p.ready + (grp * MAX_S + (int)j) * COUNTER_STRIDE,
+          ok = waiter.wait_counter(ready + (grp * MAX_S + (int)j) * COUNTER_STRIDE,
                                    step * p.R * (p.direct_publish ? NUM_EPI_THREADS / 32 : 1) +
                                        ((step == p.stall_step && blockIdx.x == 0) ? (1 << 28) : 0));
         if (!ok) {
@@ -437,7 +446,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const int slot = BWD ? (p.T - step) : step;  // time index of the input state
         ptx::mbar_arrive_expect_tx(&full_bar[s], (uint32_t)state_stage_bytes);
         // one 4-D box: all nkt 64-column tiles of my K slice for this batch group
-        tma_load_4d(sState + s * state_stage_bytes, &tmState, 0, grp * Ng, (int)j * nkt, slot,
+        tma_load_4d(sState + s * state_stage_bytes, &tmState, 0, b0 + grp * Ng, (int)j * nkt, slot,
                     &full_bar[s]);
         stamp(p.trace, q, 1);  // loads issued
       }
@@ -585,7 +594,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     auto block_base = [&](int q) -> long {
       const int step = q / G, grp = q - step * G;
       const int t = BWD ? (p.T - 1 - step) : step;
-      return ((long)t * p.B + (long)grp * Ng) * p.d;
+      return ((long)t * p.B + b0 + (long)grp * Ng) * p.d;
     };
     // everything that does not depend on the recurrent term
     auto premath = [&](int q) {
@@ -695,7 +704,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
       __syncwarp();
       if (lane == 0 && good) {
         if (p.direct_publish)  // one gpu-scope release per epilogue warp, no hand-off
-          red_release_gpu_add(p.ready + ((q - step * G) * MAX_S + my_kslice) * COUNTER_STRIDE, 1);
+          red_release_gpu_add(ready + ((q - step * G) * MAX_S + my_kslice) * COUNTER_STRIDE, 1);
         else
           ptx::mbar_arrive(&stored_bar[a]);
       }
@@ -742,7 +751,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const int a = q & 1;
         const uint32_t aph = (uint32_t)(q >> 1) & 1u;
         if (!waiter.wait(&stored_bar[a], aph)) break;   // the failing role reports the abort
-        red_release_gpu_add(p.ready + (grp * MAX_S + my_kslice) * COUNTER_STRIDE, 1);
+        red_release_gpu_add(ready + (grp * MAX_S + my_kslice) * COUNTER_STRIDE, 1);
         stamp(p.trace, q, 9);  // published
       }
     }
@@ -761,11 +770,20 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     const int pairs = rows_own / 2;
     float ssum = 0.f;
     for (int k = tid / 2; k < FG * NUM_EPI_THREADS; k += pairs) ssum += db_part[tid & 1][k];
-    p.db[i * TILE_M + (int)j * rows_own + tid] = ssum;
+    p.db[(long)rep * p.d + i * TILE_M + (int)j * rows_own + tid] = ssum;   // one row of sums per replica
   }
   // no CTA may exit while a peer can still address its shared memory
   cluster_sync_all();
   if (warp == 1) ptx::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// db[j] += db[r * d + j] for r = 1 .. reps-1, in that order
+__global__ void fold_rows_kernel(float* db, int d, int reps) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= d) return;
+  float s = db[j];
+  for (int r = 1; r < reps; ++r) s += db[(long)r * d + j];
+  db[j] = s;
 }
 
 // ---------------------------------------------------------------------------
@@ -831,6 +849,7 @@ int make_io_tmap(CUtensorMap* out, const void* base, int slots, int B, int d, in
 }
 
 struct RecPlan {
+  int reps = 1;   // batch replicas of the grid; G then counts the groups of ONE replica
   int S, Kc, G, Ng, Npad, nstages, nmw, w_tmem;
   int fg;   // finalising warp groups (kernel instantiation)
   uint32_t tmem_cols;
@@ -917,12 +936,29 @@ bool plan_is_coresident(const RecPlan& pl, int d, bool bwd) {
                     : kernel_is_coresident(rec_tc_kernel<false, 1>, pl, d);
 }
 
+// How many clusters of this plan's kernel fit on the device at once (0 on error).
+template <typename Kernel>
+int kernel_max_clusters(Kernel kern, const RecPlan& pl, int d);
+
+int plan_max_clusters(const RecPlan& pl, int d, bool bwd) {
+  if (bwd)
+    return pl.fg == 2 ? kernel_max_clusters(rec_tc_kernel<true, 2>, pl, d)
+                      : kernel_max_clusters(rec_tc_kernel<true, 1>, pl, d);
+  return pl.fg == 2 ? kernel_max_clusters(rec_tc_kernel<false, 2>, pl, d)
+                    : kernel_max_clusters(rec_tc_kernel<false, 1>, pl, d);
+}
+
 template <typename Kernel>
 bool kernel_is_coresident(Kernel kern, const RecPlan& pl, int d) {
+  return kernel_max_clusters(kern, pl, d) * pl.S >= (d / TILE_M) * pl.S * pl.reps;
+}
+
+template <typename Kernel>
+int kernel_max_clusters(Kernel kern, const RecPlan& pl, int d) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem) !=
       cudaSuccess) {
     cudaGetLastError();
-    return false;
+    return 0;
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((d / TILE_M) * pl.S);
@@ -938,9 +974,9 @@ bool kernel_is_coresident(Kernel kern, const RecPlan& pl, int d) {
   int max_clusters = 0;
   if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess) {
     cudaGetLastError();
-    return false;
+    return 0;
   }
-  return max_clusters * pl.S >= (int)cfg.gridDim.x;
+  return max_clusters;
 }
 
 // Largest K split first (most CTAs, smallest resident tile); a split whose clusters do
@@ -955,12 +991,12 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
   if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = 0; }
   // co-residency depends on the device; callers may come from several host threads
   // (autograd's) and use several GPUs
-  typedef std::tuple<int, int, int, int, long, long, long, long, long, long> Key;
+  typedef std::tuple<int, int, int, int, long, long, long, long, long, long, long> Key;
   static std::map<Key, RecPlan> cache;
   std::lock_guard<std::mutex> lock(g_rec_mutex);
   const Key key(dev, B, d, compact, options().rec_ksplit, options().rec_groups,
                 options().rec_mma_warps, options().rec_w_tmem, options().rec_large_batch,
-                options().rec_fin_groups);
+                options().rec_fin_groups, options().rec_replicas);
   {
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
@@ -1000,6 +1036,25 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
             found = pl;
         }
       }
+    // Batch replicas: when the grid leaves most of the device idle, run several copies of it,
+    // each on its own share of the batch groups (sequences are independent, the copies never
+    // wait on each other).  Fewer groups pass through each block per step.
+    if (found.ok && options().rec_replicas != 1) {
+      const int clusters_one = d / TILE_M;
+      const int fit = plan_max_clusters(found, d, bwd) / clusters_one;
+      int want = (int)options().rec_replicas;          // 0 = as many as fit
+      int reps = want > 0 ? want : REC_MAX_REPLICAS;
+      if (reps > REC_MAX_REPLICAS) reps = REC_MAX_REPLICAS;
+      if (reps > fit) reps = fit;
+      while (reps > 1 && found.G % reps != 0) --reps;
+      if (reps > 1) {
+        RecPlan rp = plan_for(B / reps, d, found.S, found.Ng, found.w_tmem != 0, nin);
+        if (rp.ok && rp.S == found.S && rp.Ng == found.Ng && rp.w_tmem == found.w_tmem) {
+          rp.reps = reps;
+          if (plan_is_coresident(rp, d, bwd)) found = rp;
+        }
+      }
+    }
   }
   cache[key] = found;
   return found;
@@ -1026,7 +1081,7 @@ int launch_rec_tc_fg(const RecPlan& pl, RecTcParams& p, const void* W, const voi
   ELMAN_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)pl.smem));
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((p.d / TILE_M) * pl.S);
+  cfg.gridDim = dim3((p.d / TILE_M) * pl.S * pl.reps);
   cfg.blockDim = dim3(threads_for(FG));
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
@@ -1062,6 +1117,8 @@ void fill_plan(const RecPlan& pl, RecTcParams& p) {
   p.w_tmem = pl.w_tmem;
   p.w_col0 = (uint32_t)(2 * pl.nmw * pl.Npad);
   p.R = p.d / TILE_M;
+  p.reps = pl.reps;
+  p.Brep = pl.G * pl.Ng;
   p.spin_limit = options().spin_limit;
   p.stall_step = (int)options().test_stall_step;
   p.status = device_status_ptr();
@@ -1075,7 +1132,8 @@ int rec_tc_blocks(int T, int B, int d, int compact) {
   // batch groups are pipelined through the same blocks, so they do not add any
   RecPlan f = make_plan(T, B, d, compact, false), b = make_plan(T, B, d, compact, true);
   if (!f.ok || !b.ok) return 0;
-  return (d / TILE_M) * (f.S > b.S ? f.S : b.S);
+  const int nf = f.S * f.reps, nb = b.S * b.reps;
+  return (d / TILE_M) * (nf > nb ? nf : nb);
 }
 
 size_t rec_tc_sync_bytes() {
@@ -1089,6 +1147,7 @@ static long long* trace_area(int* sync) {
   g_last_trace = (long long*)(sync + MAX_GROUPS * MAX_S * COUNTER_STRIDE + 64);
   return g_last_trace;
 }
+void set_last_trace(long long* device_buffer) { g_last_trace = device_buffer; }
 int rec_tc_copy_trace(long long* dst, int max_entries) {
   if (g_last_trace == nullptr) return set_error(ELMAN_ERR_ARG, "no trace was recorded");
   int n = TRACE_STEPS * TRACE_SLOTS;
@@ -1137,7 +1196,13 @@ int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream) {
   p.trace = trace_area(a.sync);
   p.Wg = (const bf16*)a.Wt;
   p.direct_publish = options().rec_direct_publish == 1 ? 1 : 0;
-  return launch_rec_tc<true>(pl, p, a.Wt, a.dv, stream);
+  ELMAN_RETURN_IF(launch_rec_tc<true>(pl, p, a.Wt, a.dv, stream));
+  if (pl.reps > 1) {   // fold the replicas' bias-gradient rows into the first
+    fold_rows_kernel<<<(a.d + 255) / 256, 256, 0, stream>>>(a.db, a.d, pl.reps);
+    count_launch(false);
+    ELMAN_CUDA_CHECK(cudaGetLastError());
+  }
+  return ELMAN_OK;
 }
 
 }  // namespace elman

@@ -157,6 +157,19 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
   return d;
 }
 
+// K-major bf16 tile whose rows are 64 bytes (32 elements) with 64-byte swizzle: groups of 8
+// rows are 512 bytes apart; within a row the 16-byte chunk index is XORed with bits 1..2 of
+// the row index.  Used for operands assembled on chip from 32-column pieces.
+__device__ __forceinline__ uint64_t umma_desc_k_sw64(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;                      // SWIZZLE_64B
+  return d;
+}
+
 // Instruction descriptor: kind::f16, A and B bf16 K-major, fp32 accumulate.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) |

@@ -81,6 +81,15 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(ptx::smem_u32(smem_dst)), "l"(m), "r"(ptx::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Bulk copy from this CTA's shared memory into a cluster peer's, crediting `bytes` to an
+// mbarrier of that peer when the data has landed (16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uint32_t src_cta_addr,
+                                                  uint32_t bytes, uint32_t peer_bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst_cluster_addr), "r"(src_cta_addr), "r"(bytes), "r"(peer_bar_cluster_addr)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

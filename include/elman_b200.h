@@ -78,6 +78,10 @@ int elman_b200_device_status(int* detail, int clear);
  *   "rec_large_batch" 1 (default) = batches over 32 rows take the throughput plan of
  *                    the tensor-core recurrence (widest batch group first), 0 = the
  *                    latency plan for every batch size
+ *   "rec_replicas"   batch replicas of the tensor-core recurrence's grid for batches over 32:
+ *                    0 (default) = as many copies of the grid as fit on the device, each on
+ *                    its own share of the batch (they never wait on each other), 1 = one
+ *                    copy, n = at most n.  Results do not depend on it.
  *   "test_stall_step" failure-detection test hook, -1 (default) = off.  With a value k >= 1
  *                    thread block 0 of the next tensor-core launches (recurrences: at time
  *                    step k; projection GEMMs: at K iteration k) waits for something that

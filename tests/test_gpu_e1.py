@@ -263,3 +263,24 @@ def test_large_batch_plans_match_oracle(T, B, d):
         other, _ = run_e1(inp, torch.bfloat16)
     for k in ("h", "output", "dx", "dz"):
         assert orc.rel_err(got[k].float().cpu(), other[k].float().cpu()) < 1e-2, k
+
+
+@pytest.mark.parametrize("T,B,d", [(5, 128, 512), (4, 256, 256), (3, 192, 384), (6, 256, 2048)])
+def test_batch_replicas_of_the_grid_change_nothing(T, B, d):
+    """Large batches run several independent copies of the recurrence grid, each on its own
+    share of the batch groups (option rec_replicas).  Every sequence is computed by the same
+    program either way: outputs and data gradients are bit-identical to the single-copy
+    launch, weight gradients too, the bias gradient up to its order of summation."""
+    inp = orc.make_e1_inputs(T, B, d, seed=B + d + 1)
+    with option("rec_replicas", 1):
+        one, ref = run_e1(inp, torch.bfloat16)
+    many, _ = run_e1(inp, torch.bfloat16)          # default: as many copies as fit
+    assert _lib.device_status()[0] == 0
+    for k in ("h", "output", "v", "dx", "dz", "dW_x", "dW_h"):
+        assert torch.equal(one[k], many[k]), k
+    assert orc.rel_err(many["db"].float().cpu(), one["db"].float().cpu()) < 1e-2
+    assert_close(errors(many, oracle_e1(ref)), TOL[torch.bfloat16], "replicated grid vs oracle")
+    blocks_one = None
+    with option("rec_replicas", 1):
+        blocks_one = H.recurrence_blocks(torch.bfloat16, T, B, d)
+    assert H.recurrence_blocks(torch.bfloat16, T, B, d) >= 2 * blocks_one, "replicas were not used"
