@@ -1,5 +1,6 @@
 // C ABI of the library: argument checks, workspace carving and the sequence of
 // kernels behind each entry point declared in include/elman_b200.h.
+#include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -1004,6 +1005,143 @@ int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d, cons
   ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, Wt, h, v, z, d_output, dv, dz, w.db, w.sync, dv_in,
                               st, (flags & ELMAN_FLAG_COMPACT) ? 1 : 0));
   return float_to_dtype(dtype, w.db, db, d, st);
+}
+
+// ---------------- E1 with the gate on [h; x] (extension of the reference's E1) ----------------
+//   h_t = tanh(W_x x_t + W_h h_{t-1} + b),   y_t = h_t * silu(z_t + W_gh h_t)
+// where z_t = W_gx x_t + b_g is the caller's time-parallel gate projection.  h never feeds
+// back through the gate, so W_gh h_t is one more time-parallel GEMM over the stored states
+// with the gate in its epilogue; backward adds dW_gh = dzg^T h and injects dzg W_gh into the
+// gradient BPTT starts from.
+
+// The BPTT kernels take the direct gradient of h_t as dy_t * silu(g_t).  Here it is
+// dy_t silu(zg_t) + (dzg_t W_gh), which is handed to the same kernels as "dy" beside a
+// constant gate g0 (silu(g0) is then a known scalar that is divided out beforehand).
+static constexpr float kGateConst = 1.28125f;   // exact in bf16 and fp32
+static float gate_const_inv_silu() {
+  const double g = (double)kGateConst;
+  return (float)(1.0 / (g / (1.0 + exp(-g))));
+}
+
+struct HxFwdWs { void* pre; void* y0; int* sync; };
+static size_t carve_hx_fwd(int dtype, int T, int B, int d, void* ws, HxFwdWs* o) {
+  Carver c(ws);
+  o->pre = c.take((size_t)T * B * d * esize(dtype));
+  o->y0 = c.take((size_t)T * B * d * esize(dtype));   // the recurrence's own (x-only) gate output
+  size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
+  o->sync = (int*)c.take(sb);
+  return c.total();
+}
+
+size_t elman_e1_hx_forward_workspace(int dtype, int T, int B, int d) {
+  HxFwdWs w;
+  return carve_hx_fwd(dtype, T, B, d, nullptr, &w);
+}
+
+int elman_e1_hx_forward(int dtype, int training, int T, int B, int d, const void* x, const void* z,
+                        const void* h0, const void* W_x, const void* W_h, const void* b,
+                        const void* W_gh, void* h, void* output, void* v, void* z_gate,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (B == 0 || d == 0) return ELMAN_OK;
+  REQUIRE_PTR(h0); REQUIRE_PTR(h);
+  cudaStream_t st = (cudaStream_t)stream;
+  ELMAN_RETURN_IF(copy_rows(dtype, h0, h, (long)B * d, st));
+  if (T == 0) return ELMAN_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(z); REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(b);
+  REQUIRE_PTR(W_gh); REQUIRE_PTR(output); REQUIRE_PTR(z_gate); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(!training || v != nullptr, "v must be provided when training");
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  HxFwdWs w;
+  size_t need = carve_hx_fwd(dtype, T, B, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  const int TB = T * B;
+  const size_t es = esize(dtype);
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, d, x, d, W_x, d, b, w.pre, d, 0, st));
+  ELMAN_RETURN_IF(run_rec_fwd(dtype, T, B, d, W_h, w.pre, z, h, w.y0, training ? v : nullptr,
+                              w.sync, st));
+  const void* h1 = (const char*)h + (size_t)B * d * es;   // h_1 .. h_T
+  if (use_tc(dtype) && (d & 31) == 0 && gemm_tc_supported(TB, d, d, h1, d, W_gh, d, z_gate, d, 0) &&
+      ((((uintptr_t)z_gate | (uintptr_t)output | (uintptr_t)z | (uintptr_t)h1) & 15) == 0)) {
+    GemmSplit ep{d, output, const_cast<void*>(z), 1, h1};   // sum with z, gate with h in the epilogue
+    return gemm_tc(TB, d, d, (const bf16*)h1, d, 0, (const bf16*)W_gh, d, 0, nullptr, z_gate, d, 0,
+                   0, st, nullptr, 0, &ep);
+  }
+  ELMAN_RETURN_IF(copy_rows(dtype, z, z_gate, (long)TB * d, st));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, d, d, h1, d, W_gh, d, nullptr, z_gate, d, 1, st));
+  return gate_apply(dtype, (long)TB * d, h1, z_gate, output, st);
+}
+
+struct HxBwdWs {
+  void* Wt; void* dv; float* db; int* sync; float* splitk; size_t splitk_bytes;
+  void* t; void* g0; void* dg0; void* Ws;
+};
+static size_t carve_hx_bwd(int dtype, int T, int B, int d, void* ws, HxBwdWs* o) {
+  Carver c(ws);
+  const size_t es = esize(dtype), TBd = (size_t)T * B * d * es;
+  o->Wt = c.take((size_t)d * d * es);
+  o->dv = c.take(TBd + (size_t)B * d * es);
+  o->db = (float*)c.take((size_t)REC_MAX_REPLICAS * d * sizeof(float));
+  size_t sb = rec_sync_bytes() > rec_tc_sync_bytes() ? rec_sync_bytes() : rec_tc_sync_bytes();
+  o->sync = (int*)c.take(sb);
+  o->splitk_bytes = splitk_scratch_bytes(dtype, d, d);
+  o->splitk = o->splitk_bytes ? (float*)c.take(o->splitk_bytes) : nullptr;
+  o->t = c.take(TBd);      // the gradient BPTT starts from, scaled for the constant gate
+  o->g0 = c.take(TBd);     // the constant gate
+  o->dg0 = c.take(TBd);    // the kernel's gate gradient for the constant gate (unused)
+  o->Ws = c.take((size_t)d * d * es);   // W_gh / silu(g0)
+  return c.total();
+}
+
+size_t elman_e1_hx_backward_workspace(int dtype, int T, int B, int d) {
+  HxBwdWs w;
+  return carve_hx_bwd(dtype, T, B, d, nullptr, &w);
+}
+
+int elman_e1_hx_backward(int dtype, int T, int B, int d, const void* W_x, const void* W_h,
+                         const void* W_gh, const void* x, const void* z_gate, const void* h,
+                         const void* v, const void* d_output, void* dx, void* dz, void* dW_x,
+                         void* dW_h, void* db, void* dW_gh, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (d == 0) return ELMAN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  REQUIRE_PTR(dW_x); REQUIRE_PTR(dW_h); REQUIRE_PTR(db); REQUIRE_PTR(dW_gh);
+  const size_t es = esize(dtype);
+  if (T == 0 || B == 0) {
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_x, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_h, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_gh, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    return ELMAN_OK;
+  }
+  REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(W_gh); REQUIRE_PTR(x); REQUIRE_PTR(z_gate);
+  REQUIRE_PTR(h); REQUIRE_PTR(v); REQUIRE_PTR(d_output); REQUIRE_PTR(dx); REQUIRE_PTR(dz);
+  REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  HxBwdWs w;
+  size_t need = carve_hx_bwd(dtype, T, B, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  const int TB = T * B;
+  const long n = (long)TB * d;
+  const float inv_s = gate_const_inv_silu();
+  const void* h1 = (const char*)h + (size_t)B * d * es;
+  // dz = dy h silu'(zg);  t = dy silu(zg) / silu(g0);  t += dz (W_gh / silu(g0))
+  ELMAN_RETURN_IF(gate_backward_prep(dtype, n, d_output, h1, z_gate, inv_s, dz, w.t, st));
+  ELMAN_RETURN_IF(scale_copy(dtype, (long)d * d, W_gh, inv_s, w.Ws, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, dz, d, w.Ws, d, nullptr, w.t, d, 1, st));
+  ELMAN_RETURN_IF(fill_value(dtype, n, kGateConst, w.g0, st));
+  ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
+  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, w.g0, w.t, w.dv, w.dg0, w.db, w.sync,
+                              nullptr, st));
+  ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, nullptr, dx, d, 0, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, dW_h, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, dz, h1, dW_gh, st, w.splitk, w.splitk_bytes));
+  return ELMAN_OK;
 }
 
 // ------------------ the layer's time-parallel ops around the cell ------------------

@@ -131,10 +131,15 @@ constexpr int GEMM_MAX_KSPLIT = 4;
 // Optional epilogue of the layer's input projection: the N = 2*split output columns are not
 // stored as one matrix but as three dense [M, split] ones — columns [0, split) raw into C and
 // silu-activated into C_act, columns [split, 2*split) into C_hi.  split % 32 == 0, bf16 out.
+// mode 1 (the [h;x] gate of the E1 extension): N = split; the epilogue adds the matrix C_hi
+// (the x-part of the gate pre-activation, dense [M, N]) to the product, stores the sum to C and
+// aux * silu(sum) to C_act, with aux (the hidden states) dense [M, N].
 struct GemmSplit {
   int split;
   void* C_act;
   void* C_hi;
+  int mode = 0;
+  const void* aux = nullptr;
 };
 int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
             int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
@@ -152,6 +157,13 @@ int split_silu(int dtype, long M, int d, const void* xz, void* x_raw, void* x_ac
                cudaStream_t st);
 int silu_bwd_concat(int dtype, long M, int d, const void* d_act, const void* x_raw, const void* dz,
                     void* dxz, cudaStream_t st);
+// [h;x]-gate extension: y = h * silu(zg);  dzg = dy * h * silu'(zg), t = dy * silu(zg) * scale;
+// dst = src * scale;  dst = value
+int gate_apply(int dtype, long n, const void* h, const void* zg, void* y, cudaStream_t st);
+int gate_backward_prep(int dtype, long n, const void* dy, const void* h, const void* zg, float scale,
+                       void* dzg, void* t, cudaStream_t st);
+int scale_copy(int dtype, long n, const void* src, float scale, void* dst, cudaStream_t st);
+int fill_value(int dtype, long n, float value, void* dst, cudaStream_t st);
 // AdamW over flat buffers (train_ops.cu); advances *step by one first.
 int adamw_step(int dtype, long n, void* p, const void* g, void* m, void* v, float lr, float beta1,
                float beta2, float eps, float weight_decay, float* step, const float* grad_scale,

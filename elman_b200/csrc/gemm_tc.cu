@@ -61,6 +61,8 @@ struct GemmParams {
   int split = 0;              // > 0: the input projection's three-output epilogue (GemmSplit)
   void* C_act = nullptr;
   void* C_hi = nullptr;
+  int split_mode = 0;         // 1: the [h;x]-gate epilogue (sum with C_hi, gate with aux)
+  const void* aux = nullptr;
   int stall_step = -1;        // test hook: block 0 arms a stage at this K iteration but loads nothing
   int ksplit = 1;             // persistent kernel: K range cut into this many work items per tile
   float* partial = nullptr;   // [ksplit][M][N] fp32 partial sums when ksplit > 1
@@ -76,6 +78,37 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ void store_chunk(const GemmParams& p, int gm, int gn0,
                                             const uint32_t (&r)[32], bool vec_ok,
                                             const bf16* bias32) {
+  if (p.split > 0 && p.split_mode == 1) {
+    // [h;x] gate: zg = product + z (dense [M, N] in C_hi) -> C;  y = h * silu(zg) -> C_act,
+    // h dense [M, N] in aux.  N % 32 == 0: whole chunks only.
+    if (gm < p.M && gn0 < p.N) {
+      const long off = (long)gm * p.split + gn0;
+      const bf16* zin = (const bf16*)p.C_hi + off;
+      const bf16* hin = (const bf16*)p.aux + off;
+      bf16* zout = (bf16*)p.C + off;
+      bf16* yout = (bf16*)p.C_act + off;
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        const uint4 zv = *reinterpret_cast<const uint4*>(zin + j);
+        const uint4 hv = *reinterpret_cast<const uint4*>(hin + j);
+        const __nv_bfloat162* z2 = reinterpret_cast<const __nv_bfloat162*>(&zv);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hv);
+        uint4 o, y;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+        uint32_t* yw = reinterpret_cast<uint32_t*>(&y);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 zf = __bfloat1622float2(z2[q]), hf = __bfloat1622float2(h2[q]);
+          ow[q] = pack_bf16(__uint_as_float(r[j + 2 * q]) + zf.x, __uint_as_float(r[j + 2 * q + 1]) + zf.y);
+          const float2 gf = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&ow[q]));
+          yw[q] = pack_bf16(hf.x * siluf_(gf.x), hf.y * siluf_(gf.y));
+        }
+        *reinterpret_cast<uint4*>(zout + j) = o;
+        *reinterpret_cast<uint4*>(yout + j) = y;
+      }
+    }
+    return;
+  }
   if (p.split > 0) {
     // input projection of the layer: columns left of `split` are the recurrence's input —
     // stored raw (for the backward pass) and silu-activated — the others the gate input.
@@ -612,9 +645,11 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
             int b_mn, const bf16* bias, void* C, int ldc, int c_is_f32, int accumulate,
             cudaStream_t stream, float* splitk, size_t splitk_bytes, const GemmSplit* split) {
   if (split != nullptr) {
-    if (split->split <= 0 || (split->split & 31) != 0 || N != 2 * split->split || c_is_f32 ||
-        accumulate || bias != nullptr || (((uintptr_t)C | (uintptr_t)split->C_act |
-                                           (uintptr_t)split->C_hi) & 15) != 0)
+    const int want_n = split->mode == 1 ? split->split : 2 * split->split;
+    if (split->split <= 0 || (split->split & 31) != 0 || N != want_n || c_is_f32 ||
+        accumulate || bias != nullptr || (split->mode == 1 && split->aux == nullptr) ||
+        (((uintptr_t)C | (uintptr_t)split->C_act | (uintptr_t)split->C_hi |
+          (uintptr_t)split->aux) & 15) != 0)
       return set_error(ELMAN_ERR_UNSUPPORTED, "split epilogue: shape or alignment not supported");
     splitk = nullptr;   // the three-output epilogue has no partial-sum form
   }
@@ -644,7 +679,10 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
       q.stall_step = (int)options().test_stall_step;
       q.status = device_status_ptr();
       q.a_mn = a_mn; q.b_mn = b_mn;
-      if (split != nullptr) { q.split = split->split; q.C_act = split->C_act; q.C_hi = split->C_hi; }
+      if (split != nullptr) {
+        q.split = split->split; q.C_act = split->C_act; q.C_hi = split->C_hi;
+        q.split_mode = split->mode; q.aux = split->aux;
+      }
       return gemm_tc_persistent(M, N, K, A, lda, a_mn, W, ldw, b_mn, q, stream);
     }
   }
@@ -666,7 +704,10 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
   p.stall_step = (int)options().test_stall_step;
   p.status = device_status_ptr();
   p.a_mn = a_mn; p.b_mn = b_mn;
-  if (split != nullptr) { p.split = split->split; p.C_act = split->C_act; p.C_hi = split->C_hi; }
+  if (split != nullptr) {
+    p.split = split->split; p.C_act = split->C_act; p.C_hi = split->C_hi;
+    p.split_mode = split->mode; p.aux = split->aux;
+  }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, p);
   count_launch(true);

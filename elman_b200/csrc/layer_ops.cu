@@ -341,6 +341,33 @@ __global__ void silu_bwd_concat_bf16x8_kernel(long M, int d, const uint4* __rest
   }
 }
 
+template <typename T>
+__global__ void gate_apply_kernel(long n, const T* __restrict__ h, const T* __restrict__ zg, T* __restrict__ y) {
+  for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long)gridDim.x * blockDim.x)
+    y[e] = from_f<T>(to_f(h[e]) * siluf_(to_f(zg[e])));
+}
+template <typename T>
+__global__ void gate_backward_prep_kernel(long n, const T* __restrict__ dy, const T* __restrict__ h,
+                                          const T* __restrict__ zg, float scale, T* __restrict__ dzg,
+                                          T* __restrict__ t) {
+  for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long)gridDim.x * blockDim.x) {
+    const float g = to_f(zg[e]), d = to_f(dy[e]);
+    dzg[e] = from_f<T>(d * to_f(h[e]) * dsiluf_(g));
+    t[e] = from_f<T>(d * siluf_(g) * scale);
+  }
+}
+template <typename T>
+__global__ void scale_copy_kernel(long n, const T* __restrict__ src, float scale, T* __restrict__ dst) {
+  for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long)gridDim.x * blockDim.x)
+    dst[e] = from_f<T>(to_f(src[e]) * scale);
+}
+template <typename T>
+__global__ void fill_value_kernel(long n, float value, T* __restrict__ dst) {
+  const T v = from_f<T>(value);
+  for (long e = (long)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (long)gridDim.x * blockDim.x)
+    dst[e] = v;
+}
+
 int grid_for(long n_items) {
   long g = (n_items + NT - 1) / NT;
   if (g < 1) g = 1;
@@ -410,6 +437,51 @@ int split_silu(int dtype, long M, int d, const void* xz, void* x_raw, void* x_ac
   else
     split_silu_kernel<bf16><<<grid, NT, 0, st>>>(M, d, (const bf16*)xz, (bf16*)x_raw, (bf16*)x_act,
                                                 (bf16*)z);
+  count_launch(false);
+  ELMAN_CUDA_CHECK(cudaGetLastError());
+  return ELMAN_OK;
+}
+
+int gate_apply(int dtype, long n, const void* h, const void* zg, void* y, cudaStream_t st) {
+  if (dtype == ELMAN_F32) {
+    if (n > 0) gate_apply_kernel<float><<<grid_for(n), NT, 0, st>>>(n, (const float*)h, (const float*)zg, (float*)y);
+  } else {
+    if (n > 0) gate_apply_kernel<bf16><<<grid_for(n), NT, 0, st>>>(n, (const bf16*)h, (const bf16*)zg, (bf16*)y);
+  }
+  if (n > 0) count_launch(false);
+  ELMAN_CUDA_CHECK(cudaGetLastError());
+  return ELMAN_OK;
+}
+
+int gate_backward_prep(int dtype, long n, const void* dy, const void* h, const void* zg, float scale,
+                       void* dzg, void* t, cudaStream_t st) {
+  if (n <= 0) return ELMAN_OK;
+  if (dtype == ELMAN_F32)
+    gate_backward_prep_kernel<float><<<grid_for(n), NT, 0, st>>>(
+        n, (const float*)dy, (const float*)h, (const float*)zg, scale, (float*)dzg, (float*)t);
+  else
+    gate_backward_prep_kernel<bf16><<<grid_for(n), NT, 0, st>>>(
+        n, (const bf16*)dy, (const bf16*)h, (const bf16*)zg, scale, (bf16*)dzg, (bf16*)t);
+  count_launch(false);
+  ELMAN_CUDA_CHECK(cudaGetLastError());
+  return ELMAN_OK;
+}
+
+int scale_copy(int dtype, long n, const void* src, float scale, void* dst, cudaStream_t st) {
+  if (n <= 0) return ELMAN_OK;
+  if (dtype == ELMAN_F32)
+    scale_copy_kernel<float><<<grid_for(n), NT, 0, st>>>(n, (const float*)src, scale, (float*)dst);
+  else
+    scale_copy_kernel<bf16><<<grid_for(n), NT, 0, st>>>(n, (const bf16*)src, scale, (bf16*)dst);
+  count_launch(false);
+  ELMAN_CUDA_CHECK(cudaGetLastError());
+  return ELMAN_OK;
+}
+
+int fill_value(int dtype, long n, float value, void* dst, cudaStream_t st) {
+  if (n <= 0) return ELMAN_OK;
+  if (dtype == ELMAN_F32) fill_value_kernel<float><<<grid_for(n), NT, 0, st>>>(n, value, (float*)dst);
+  else fill_value_kernel<bf16><<<grid_for(n), NT, 0, st>>>(n, value, (bf16*)dst);
   count_launch(false);
   ELMAN_CUDA_CHECK(cudaGetLastError());
   return ELMAN_OK;

@@ -534,3 +534,55 @@ def silu_backward_concat(d_act, x_raw, dz):
                                                     _ptr(dxz), _stream(d_act.device))
         _lib.check(rc, fn)
     return dxz
+
+
+# ------------------------- E1 with the gate on [h; x] (extension; README formula of the reference)
+
+def mamba_gated_elman_hx_forward(training, x, z, h0, W_x, W_h, b, W_gh):
+    """y_t = h_t * silu(z_t + W_gh h_t) -> [h[T+1,B,d], output, v (empty if not training), z_gate]
+    through elman_e1_hx_forward.  Not a function of the reference's extension module."""
+    fn = "mamba_gated_elman_hx_forward"
+    dt = _check_inputs(fn, x, x=x, z=z, h0=h0, W_x=W_x, W_h=W_h, b=b, W_gh=W_gh)
+    if x.dim() != 3:
+        raise RuntimeError(f"{fn}: x must be [T, B, dim]")
+    T, B, d = x.shape
+    _shape(fn, z, (T, B, d), "z"); _shape(fn, h0, (B, d), "h0"); _shape(fn, b, (d,), "b")
+    for name, w in (("W_x", W_x), ("W_h", W_h), ("W_gh", W_gh)):
+        _shape(fn, w, (d, d), name)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        h = torch.empty(T + 1, B, d, dtype=x.dtype, device=x.device)
+        out = torch.empty(T, B, d, dtype=x.dtype, device=x.device)
+        zg = torch.empty(T, B, d, dtype=x.dtype, device=x.device)
+        v = torch.empty((T, B, d) if training else (0,), dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e1_hx_forward_workspace(dt, T, B, d), x.device)
+        rc = lib.elman_e1_hx_forward(dt, 1 if training else 0, T, B, d, _ptr(x), _ptr(z), _ptr(h0),
+                                     _ptr(W_x), _ptr(W_h), _ptr(b), _ptr(W_gh), _ptr(h), _ptr(out),
+                                     _ptr(v), _ptr(zg), ws.data_ptr(), ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [h, out, v, zg]
+
+
+def mamba_gated_elman_hx_backward(W_x, W_h, W_gh, x, z_gate, h, v, d_output):
+    """-> [dx, dz, dW_x, dW_h, db, dW_gh] through elman_e1_hx_backward."""
+    fn = "mamba_gated_elman_hx_backward"
+    dt = _check_inputs(fn, x, W_x=W_x, W_h=W_h, W_gh=W_gh, x=x, z_gate=z_gate, h=h, v=v,
+                       d_output=d_output)
+    T, B, d = x.shape
+    _shape(fn, z_gate, (T, B, d), "z_gate"); _shape(fn, h, (T + 1, B, d), "h")
+    _shape(fn, v, (T, B, d), "v"); _shape(fn, d_output, (T, B, d), "d_output")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        dx = torch.empty_like(x)
+        dz = torch.empty_like(x)
+        dW_x, dW_h, dW_gh = (torch.empty(d, d, dtype=x.dtype, device=x.device) for _ in range(3))
+        db = torch.empty(d, dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e1_hx_backward_workspace(dt, T, B, d), x.device)
+        rc = lib.elman_e1_hx_backward(dt, T, B, d, _ptr(W_x), _ptr(W_h), _ptr(W_gh), _ptr(x),
+                                      _ptr(z_gate), _ptr(h), _ptr(v), _ptr(d_output), _ptr(dx),
+                                      _ptr(dz), _ptr(dW_x), _ptr(dW_h), _ptr(db), _ptr(dW_gh),
+                                      ws.data_ptr(), ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [dx, dz, dW_x, dW_h, db, dW_gh]

@@ -40,6 +40,46 @@ class MambaGatedElmanFunction(torch.autograd.Function):
         return None, dx, dz, None, dW_x, dW_h, db
 
 
+class MambaGatedElmanHXFunction(torch.autograd.Function):
+    """E1 with the output gate on [h_t ; x_t] — an extension: the reference has no such class;
+    the formula is the one in its README (README.md:25-29),
+
+        y_t = h_t * silu(W_g [h_t ; x_t] + b_g),   W_g = [W_gh | W_gx].
+
+    forward(training, x, z, h0, W_x, W_h, b, W_gh) -> (h, output) with z = W_gx x + b_g the
+    caller's time-parallel gate projection, exactly the `z` input of MambaGatedElmanFunction.
+    The gradient of the returned h is dropped, as there."""
+
+    @staticmethod
+    def forward(ctx, training, x, z, h0, W_x, W_h, b, W_gh):
+        h, output, v, zg = hasty_pytorch_lib.mamba_gated_elman_hx_forward(
+            training, x, z, h0, W_x, W_h, b, W_gh)
+        ctx.save_for_backward(W_x, W_h, W_gh, x, zg, h, v)
+        return h, output
+
+    @staticmethod
+    def backward(ctx, _dh, d_output):
+        W_x, W_h, W_gh, x, zg, h, v = ctx.saved_tensors
+        if v.numel() == 0:
+            raise RuntimeError("backward needs the pre-activations: run forward with training=True")
+        dx, dz, dW_x, dW_h, db, dW_gh = hasty_pytorch_lib.mamba_gated_elman_hx_backward(
+            W_x, W_h, W_gh, x, zg, h, v, d_output.contiguous())
+        return None, dx, dz, None, dW_x, dW_h, db, dW_gh
+
+
+def e1_hx_gate_cell(x, h0, W_x, W_h, b, W_g, b_g, training=True):
+    """The whole README cell on time-major x [T,B,d]: gate projection z = W_gx x + b_g through
+    the library's GEMM (bias in its epilogue), then MambaGatedElmanHXFunction.
+    W_g: [d, 2d] = [W_gh | W_gx].  Returns (output [T,B,d], h [T+1,B,d])."""
+    d = x.shape[-1]
+    W_gh, W_gx = W_g[:, :d].contiguous(), W_g[:, d:].contiguous()
+    z = LinearFunction.apply(x, W_gx, b_g)
+    h, output = MambaGatedElmanHXFunction.apply(training, x.contiguous(), z.contiguous(),
+                                                h0.contiguous(), W_x.contiguous(),
+                                                W_h.contiguous(), b.contiguous(), W_gh)
+    return output, h
+
+
 class MambaGatedElmanChunkFunction(torch.autograd.Function):
     """One time chunk of a longer sequence (no counterpart in the reference).
 

@@ -242,6 +242,31 @@ int elman_e1_forward_static(int dtype, int training, int T, int B, int d,
                             void* h, void* output, void* v, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * E1 with the output gate on [h_t ; x_t] — an EXTENSION: no class or kernel of the reference
+ * implements it; its only specification is the formula in the reference's README.md:25-29,
+ *     h_t = tanh(W_x x_t + W_h h_{t-1} + b),   y_t = h_t * silu(W_g [h_t ; x_t] + b_g).
+ * With W_g = [W_gh | W_gx] the x-part z_t = W_gx x_t + b_g is the caller's time-parallel gate
+ * projection (the same input `z` as the reference's E1 takes); this entry point adds
+ * W_gh h_t: one more time-parallel GEMM over the stored states with the gate in its epilogue.
+ *   z_gate [T,B,d] receives z_t + W_gh h_t (the backward pass needs it).
+ * Backward returns dx (through W_x only; the caller adds dz W_gx for its projection),
+ * dz (= gradient of z and of z_gate), dW_x, dW_h, db and dW_gh; the gradient of h is
+ * dropped as in elman_e1_backward.  Parity of this pair is checked against a restatement of
+ * the README formula, not against reference code.
+ * ------------------------------------------------------------------------- */
+size_t elman_e1_hx_forward_workspace(int dtype, int T, int B, int d);
+int elman_e1_hx_forward(int dtype, int training, int T, int B, int d, const void* x, const void* z,
+                        const void* h0, const void* W_x, const void* W_h, const void* b,
+                        const void* W_gh, void* h, void* output, void* v, void* z_gate,
+                        void* workspace, size_t workspace_bytes, void* stream);
+size_t elman_e1_hx_backward_workspace(int dtype, int T, int B, int d);
+int elman_e1_hx_backward(int dtype, int T, int B, int d, const void* W_x, const void* W_h,
+                         const void* W_gh, const void* x, const void* z_gate, const void* h,
+                         const void* v, const void* d_output, void* dx, void* dz, void* dW_x,
+                         void* dW_h, void* db, void* dW_gh, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
  * E0 — stock Elman cell with a learned, x-only output gate.
  *   h_t as E1,  y_t = h_t * silu(W_gate x_t + b_gate)
  * Replaces stock_elman_forward / stock_elman_backward
