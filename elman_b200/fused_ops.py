@@ -34,6 +34,7 @@ class GradSink:
     def __init__(self):
         self.targets = {}       # data_ptr of the weight -> gradient buffer shaped like it
         self.streams = {}       # compute stream id -> companion stream
+        self.used = []          # companions that carry work since the last complete join
         self.units_expected = {}
         self.units_done = {}
         self.on_group_done = None   # callback(group) once all units of a group ran backward
@@ -61,18 +62,24 @@ class GradSink:
         ready = torch.cuda.Event()
         ready.record(cur)
         side.wait_event(ready)
+        if side not in self.used:
+            self.used.append(side)
         A.record_stream(side)
         B.record_stream(side)
         with torch.cuda.stream(side):
             H.gemm(H.GEMM_TN, A, B, out=grad, accumulate=True)
 
-    def join(self, stream=None):
-        """Makes `stream` (default: the current one) wait for every accumulation issued so far."""
-        for side in self.streams.values():
-            stream = stream or torch.cuda.current_stream(side.device)
+    def join(self, stream=None, final=False):
+        """Makes `stream` (default: the current one) wait for every accumulation issued since
+        the last final join.  Only companions that carry such work are touched: under stream
+        capture an idle companion is not part of the capture and must not be waited on."""
+        for side in self.used:
+            target = stream or torch.cuda.current_stream(side.device)
             done = torch.cuda.Event()
             done.record(side)
-            stream.wait_event(done)
+            target.wait_event(done)
+        if final:
+            self.used = []
 
     # units: a group (one layer) is complete once all of its (layer, chunk) units have issued
     # their backward work; the owner then may start reducing that group's gradients

@@ -268,7 +268,7 @@ class FlatGradients:
         gradient this step) are reduced now; the caller's stream then waits for the
         communication stream and the sums become means."""
         if self.sink is not None:
-            self.sink.join()          # the caller's stream waits for the accumulating GEMMs
+            self.sink.join(final=True)   # the caller's stream waits for the accumulating GEMMs
         if self.world == 1:
             return
         for bi, left in enumerate(self._pending):
