@@ -71,6 +71,10 @@ SIGNATURES = {
     "elman_e1_hx_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 7 + [_P] * 4 + [_P, _Z, _P]),
     "elman_e1_hx_backward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e1_hx_backward": (_I, [_I, _I, _I, _I] + [_P] * 8 + [_P] * 6 + [_P, _Z, _P]),
+    "elman_e33_forward_workspace": (_Z, [_I, _I, _I, _I]),
+    "elman_e33_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 5 + [_P] * 3 + [_P, _Z, _P]),
+    "elman_e33_backward_workspace": (_Z, [_I, _I, _I, _I]),
+    "elman_e33_backward": (_I, [_I, _I, _I, _I] + [_P] * 6 + [_P] * 4 + [_P, _Z, _P]),
     "elman_adamw_step": (_I, [_I, _L, _P, _P, _P, _P] + [_c.c_float] * 5 + [_P, _P, _P]),
     "elman_projection": (_I, [_I, _I, _I, _I, _P, _I, _P, _I, _P, _P, _I, _I, _P]),
 }

@@ -1144,6 +1144,73 @@ int elman_e1_hx_backward(int dtype, int T, int B, int d, const void* W_x, const 
   return ELMAN_OK;
 }
 
+// ------------------------------- E33: self-gated E1 -------------------------------
+//   h_t = tanh(W_x x_t + W_h h_{t-1} + b),   y_t = h_t * silu(h_t)
+// The same recurrence kernels with no gate input (the state gates itself in the epilogue).
+
+size_t elman_e33_forward_workspace(int dtype, int T, int B, int d) {
+  return elman_e1_forward_workspace(dtype, T, B, d);
+}
+
+int elman_e33_forward(int dtype, int training, int T, int B, int d, const void* x, const void* h0,
+                      const void* W_x, const void* W_h, const void* b, void* h, void* output,
+                      void* v, void* workspace, size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (B == 0 || d == 0) return ELMAN_OK;
+  REQUIRE_PTR(h0); REQUIRE_PTR(h);
+  cudaStream_t st = (cudaStream_t)stream;
+  ELMAN_RETURN_IF(copy_rows(dtype, h0, h, (long)B * d, st));
+  if (T == 0) return ELMAN_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(b); REQUIRE_PTR(output);
+  REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(!training || v != nullptr, "v must be provided when training");
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E1FwdWs w;
+  size_t need = carve_e1_fwd(dtype, T, B, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  ELMAN_RETURN_IF(proj_nt(dtype, T * B, d, d, x, d, W_x, d, b, w.pre, d, 0, st));
+  return run_rec_fwd(dtype, T, B, d, W_h, w.pre, nullptr, h, output, training ? v : nullptr, w.sync,
+                     st);
+}
+
+size_t elman_e33_backward_workspace(int dtype, int T, int B, int d) {
+  return elman_e1_backward_workspace(dtype, T, B, d);
+}
+
+int elman_e33_backward(int dtype, int T, int B, int d, const void* W_x, const void* W_h,
+                       const void* x, const void* h, const void* v, const void* d_output, void* dx,
+                       void* dW_x, void* dW_h, void* db, void* workspace, size_t workspace_bytes,
+                       void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  if (d == 0) return ELMAN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  REQUIRE_PTR(dW_x); REQUIRE_PTR(dW_h); REQUIRE_PTR(db);
+  const size_t es = esize(dtype);
+  if (T == 0 || B == 0) {
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_x, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_h, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    return ELMAN_OK;
+  }
+  REQUIRE_PTR(W_x); REQUIRE_PTR(W_h); REQUIRE_PTR(x); REQUIRE_PTR(h); REQUIRE_PTR(v);
+  REQUIRE_PTR(d_output); REQUIRE_PTR(dx); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E1BwdWs w;
+  size_t need = carve_e1_bwd(dtype, T, B, d, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  const int TB = T * B;
+  ELMAN_RETURN_IF(transpose2d(dtype, d, d, W_h, w.Wt, st));
+  ELMAN_RETURN_IF(run_rec_bwd(dtype, T, B, d, w.Wt, h, v, nullptr, d_output, w.dv, nullptr, w.db,
+                              w.sync, nullptr, st));
+  ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, w.WxT, dx, d, 0, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, dW_h, st, w.splitk, w.splitk_bytes));
+  return ELMAN_OK;
+}
+
 // ------------------ the layer's time-parallel ops around the cell ------------------
 
 size_t elman_add_rmsnorm_backward_workspace(int D) {

@@ -191,7 +191,7 @@ struct RecFwdArgs {
   int T, B, d;
   const void* W;      // [d,d] recurrent matrix ([out,in])
   const void* pre;    // [T,B,d] W_x x_t + b
-  const void* g;      // [T,B,d] gate pre-activation
+  const void* g;      // [T,B,d]; null: self gate (dg is then not written and may be null) gate pre-activation; null: the state gates itself, y = h silu(h)
   void* h;            // [T+1,B,d], h[0] already holds h0
   void* y;            // [T,B,d]
   void* v;            // [T,B,d] or null

@@ -122,7 +122,9 @@ struct FwdEpilogue {
     float hv = tanhf(val);
     if (v != nullptr) v[idx] = from_f<T>(val);
     h[idx + (long)B * d] = from_f<T>(hv);
-    y[idx] = from_f<T>(hv * siluf_(to_f(g[idx])));
+    // no gate input: the state gates itself, y = h silu(h), with h as stored
+    const float gz = g != nullptr ? to_f(g[idx]) : to_f(from_f<T>(hv));
+    y[idx] = from_f<T>(hv * siluf_(gz));
   }
 };
 
@@ -130,11 +132,16 @@ struct FwdEpilogue {
 template <typename T>
 __device__ __forceinline__ float bwd_element(const T* h, const T* v, const T* g, const T* dy,
                                              T* dv, T* dg, long idx, long BD, float acc) {
-  float gz = to_f(g[idx]);
   float dyv = to_f(dy[idx]);
   float hv = to_f(h[idx + BD]);
-  float dh = dyv * siluf_(gz) + acc;
-  dg[idx] = from_f<T>(dyv * hv * dsiluf_(gz));
+  float dh;
+  if (g != nullptr) {
+    float gz = to_f(g[idx]);
+    dh = dyv * siluf_(gz) + acc;
+    dg[idx] = from_f<T>(dyv * hv * dsiluf_(gz));
+  } else {   // self gate y = h silu(h): d y / d h = silu(h) + h silu'(h)
+    dh = dyv * (siluf_(hv) + hv * dsiluf_(hv)) + acc;
+  }
   float th = tanhf(to_f(v[idx]));
   float dvv = dh * (1.f - th * th);
   dv[idx] = from_f<T>(dvv);

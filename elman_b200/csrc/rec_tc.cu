@@ -84,6 +84,7 @@ struct RecTcParams {
   int* abort_word;  // global abort flag
   int* status;
   long spin_limit;
+  int self_gate;      // 1: no gate input, the new state gates itself (y = h silu(h))
   int stall_step;     // test hook: block 0 waits at this step for a count nobody publishes (-1 off)
   long long* trace;   // optional [TRACE_STEPS][TRACE_SLOTS] cycle stamps of CTA 0, or null
 };
@@ -610,14 +611,20 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               const float2 gz = bf16x2_to_f2(lds_u32(ia + in_tile_bytes));
               e1[e][u] = make_float2(gz.x * sigmoid_fast(gz.x), gz.y * sigmoid_fast(gz.y));
             } else {
-              const float2 gz = bf16x2_to_f2(lds_u32(ia));
+              float2 gz = bf16x2_to_f2(lds_u32(ia));
               const float2 dy = bf16x2_to_f2(lds_u32(ia + in_tile_bytes));
               const float2 hv = bf16x2_to_f2(lds_u32(ia + 2 * in_tile_bytes));
               const float2 vv = bf16x2_to_f2(lds_u32(ia + 3 * in_tile_bytes));
+              if (p.self_gate) gz = hv;
               const float sx = sigmoid_fast(gz.x), sy = sigmoid_fast(gz.y);
-              late0[e][u] = f2_to_bf16x2(dy.x * hv.x * sx * (1.f + gz.x * (1.f - sx)),
-                                         dy.y * hv.y * sy * (1.f + gz.y * (1.f - sy)));
+              const float gx = dy.x * hv.x * sx * (1.f + gz.x * (1.f - sx));
+              const float gy = dy.y * hv.y * sy * (1.f + gz.y * (1.f - sy));
+              late0[e][u] = f2_to_bf16x2(gx, gy);
               e0[e][u] = make_float2(dy.x * gz.x * sx, dy.y * gz.y * sy);
+              if (p.self_gate) {   // d(h silu(h))/dh = silu(h) + h silu'(h)
+                e0[e][u].x += gx;
+                e0[e][u].y += gy;
+              }
               e1[e][u] = make_float2(dtanh_from_v(vv.x), dtanh_from_v(vv.y));
             }
           }
@@ -684,7 +691,12 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 const float h0 = tanh_fast(v0), h1 = tanh_fast(v1);
                 stg_u32(p.h + idx + BD, f2_to_bf16x2(h0, h1));
                 late0[e][u] = f2_to_bf16x2(v0, v1);
-                late1[e][u] = f2_to_bf16x2(h0 * e1[e][u].x, h1 * e1[e][u].y);
+                if (p.self_gate) {   // the gate is the state as stored
+                  const float2 hs = bf16x2_to_f2(f2_to_bf16x2(h0, h1));
+                  late1[e][u] = f2_to_bf16x2(h0 * hs.x * sigmoid_fast(hs.x), h1 * hs.y * sigmoid_fast(hs.y));
+                } else {
+                  late1[e][u] = f2_to_bf16x2(h0 * e1[e][u].x, h1 * e1[e][u].y);
+                }
               } else {
                 const float d0 = (e0[e][u].x + a0[u]) * e1[e][u].x;
                 const float d1 = (e0[e][u].y + a1[u]) * e1[e][u].y;
@@ -730,7 +742,7 @@ rec_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
               if (p.v != nullptr) stg_u32(p.v + idx, late0[e][u]);
               stg_u32(p.y + idx, late1[e][u]);
             } else {
-              stg_u32(p.dg + idx, late0[e][u]);
+              if (p.dg != nullptr) stg_u32(p.dg + idx, late0[e][u]);
             }
           }
         }
@@ -1164,7 +1176,9 @@ int rec_fwd_tc(const RecFwdArgs& a, cudaStream_t stream) {
   RecTcParams p{};
   p.T = a.T; p.B = a.B; p.d = a.d;
   fill_plan(pl, p);
-  p.pre = (const bf16*)a.pre; p.g = (const bf16*)a.g; p.h = (bf16*)a.h; p.y = (bf16*)a.y;
+  p.pre = (const bf16*)a.pre; p.h = (bf16*)a.h; p.y = (bf16*)a.y;
+  p.self_gate = a.g == nullptr ? 1 : 0;     // the gate tile is then fetched from `pre`, unused
+  p.g = (const bf16*)(a.g != nullptr ? a.g : a.pre);
   p.v = (bf16*)a.v;
   ELMAN_CUDA_CHECK(cudaMemsetAsync(a.sync, 0, rec_tc_sync_bytes(), stream));
   p.ready = a.sync;
@@ -1187,7 +1201,9 @@ int rec_bwd_tc(const RecBwdArgs& a, cudaStream_t stream) {
   RecTcParams p{};
   p.T = a.T; p.B = a.B; p.d = a.d;
   fill_plan(pl, p);
-  p.h_in = (const bf16*)a.h; p.v_in = (const bf16*)a.v; p.g = (const bf16*)a.g;
+  p.h_in = (const bf16*)a.h; p.v_in = (const bf16*)a.v;
+  p.self_gate = a.g == nullptr ? 1 : 0;
+  p.g = (const bf16*)(a.g != nullptr ? a.g : a.dy);
   p.dy = (const bf16*)a.dy; p.dv = (bf16*)a.dv; p.dg = (bf16*)a.dg; p.db = a.db;
   ELMAN_CUDA_CHECK(cudaMemsetAsync(a.sync, 0, rec_tc_sync_bytes(), stream));
   // slot T of dv (the gradient carried in from later steps, or zeros) is filled by the caller

@@ -586,3 +586,50 @@ def mamba_gated_elman_hx_backward(W_x, W_h, W_gh, x, z_gate, h, v, d_output):
         _lib.check(rc, fn)
         ws.record_stream(torch.cuda.current_stream(x.device))
     return [dx, dz, dW_x, dW_h, db, dW_gh]
+
+
+# --------------------------------------------------------------------------- E33
+
+def e33_self_gate_forward(training, x, h0, W_x, W_h, b):
+    """y_t = h_t * silu(h_t) -> [h, output, v (empty if not training)]; the reference's
+    e33_self_gate_forward (elman/cuda/pytorch/elman_ladder.cc:444-497)."""
+    fn = "e33_self_gate_forward"
+    dt = _check_inputs(fn, x, x=x, h0=h0, W_x=W_x, W_h=W_h, b=b)
+    if x.dim() != 3:
+        raise RuntimeError(f"{fn}: x must be [T, B, dim]")
+    T, B, d = x.shape
+    _shape(fn, h0, (B, d), "h0"); _shape(fn, W_x, (d, d), "W_x"); _shape(fn, W_h, (d, d), "W_h")
+    _shape(fn, b, (d,), "b")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        h = torch.empty(T + 1, B, d, dtype=x.dtype, device=x.device)
+        out = torch.empty(T, B, d, dtype=x.dtype, device=x.device)
+        v = torch.empty((T, B, d) if training else (0,), dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e33_forward_workspace(dt, T, B, d), x.device)
+        rc = lib.elman_e33_forward(dt, 1 if training else 0, T, B, d, _ptr(x), _ptr(h0), _ptr(W_x),
+                                   _ptr(W_h), _ptr(b), _ptr(h), _ptr(out), _ptr(v), ws.data_ptr(),
+                                   ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [h, out, v]
+
+
+def e33_self_gate_backward(W_x, W_h, x, h, v, d_output):
+    """-> [dx, dW_x, dW_h, db]; the reference's e33_self_gate_backward (:499-557)."""
+    fn = "e33_self_gate_backward"
+    dt = _check_inputs(fn, x, W_x=W_x, W_h=W_h, x=x, h=h, v=v, d_output=d_output)
+    T, B, d = x.shape
+    _shape(fn, h, (T + 1, B, d), "h"); _shape(fn, v, (T, B, d), "v")
+    _shape(fn, d_output, (T, B, d), "d_output")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        dx = torch.empty_like(x)
+        dW_x, dW_h = (torch.empty(d, d, dtype=x.dtype, device=x.device) for _ in range(2))
+        db = torch.empty(d, dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e33_backward_workspace(dt, T, B, d), x.device)
+        rc = lib.elman_e33_backward(dt, T, B, d, _ptr(W_x), _ptr(W_h), _ptr(x), _ptr(h), _ptr(v),
+                                    _ptr(d_output), _ptr(dx), _ptr(dW_x), _ptr(dW_h), _ptr(db),
+                                    ws.data_ptr(), ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [dx, dW_x, dW_h, db]

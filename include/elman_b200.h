@@ -267,6 +267,24 @@ int elman_e1_hx_backward(int dtype, int T, int B, int d, const void* W_x, const 
                          size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * E33 — E1 with a self gate:  h_t as E1,  y_t = h_t * silu(h_t)  (no gate input).
+ * Replaces e33_self_gate_forward / e33_self_gate_backward
+ * (elman/cuda/pytorch/elman_ladder.cc:444-497, :499-557; module
+ * elman/models/e33_self_gate.py:30-50).  Same recurrence kernels as E1; the gate is taken
+ * from the new state in their epilogue.  Backward returns dx, dW_x, dW_h, db.
+ * (E32 and E57 of the reference call the E1 entry points directly and need nothing else.)
+ * ------------------------------------------------------------------------- */
+size_t elman_e33_forward_workspace(int dtype, int T, int B, int d);
+int elman_e33_forward(int dtype, int training, int T, int B, int d, const void* x, const void* h0,
+                      const void* W_x, const void* W_h, const void* b, void* h, void* output,
+                      void* v, void* workspace, size_t workspace_bytes, void* stream);
+size_t elman_e33_backward_workspace(int dtype, int T, int B, int d);
+int elman_e33_backward(int dtype, int T, int B, int d, const void* W_x, const void* W_h,
+                       const void* x, const void* h, const void* v, const void* d_output, void* dx,
+                       void* dW_x, void* dW_h, void* db, void* workspace, size_t workspace_bytes,
+                       void* stream);
+
+/* ---------------------------------------------------------------------------
  * E0 — stock Elman cell with a learned, x-only output gate.
  *   h_t as E1,  y_t = h_t * silu(W_gate x_t + b_gate)
  * Replaces stock_elman_forward / stock_elman_backward

@@ -23,6 +23,8 @@ Reference lines each function follows (paths relative to the reference repo):
                 elman/cuda/lib/stock_elman_gpu.cu.cc:322-472.
 * E5 forward  : elman/models/pure_lowrank_elman.py:214-248; backward
                 elman/cuda/lib/pure_lowrank_elman_fused_gpu.cu.cc:295-505.
+* E33 forward : elman/models/e33_self_gate.py:170-193 (self gate y = h silu(h)); backward
+                by the chain rule of that loop (its CUDA pair: elman_ladder.cc:444-557).
 
 All functions take time-major tensors x[T,B,d] and return dictionaries of
 tensors in the dtype they were given (use float64 inputs for error bars).
@@ -214,6 +216,41 @@ def e5_backward(U_h: Tensor, V_h: Tensor, U_x: Tensor, V_x: Tensor, U_z: Tensor,
         "db": dv2.sum(0),
         "dv0": dv_all[0] if T > 0 else dv_in,
     }
+
+
+# ----------------------------------------------------------------------------
+# E33 : h_t as E1,  y_t = h_t · silu(h_t)   (elman/models/e33_self_gate.py:144-193;
+#       its CUDA pair e33_self_gate_forward/backward, elman_ladder.cc:444-557)
+# ----------------------------------------------------------------------------
+
+def e33_forward(x: Tensor, h0: Tensor, W_x: Tensor, W_h: Tensor, b: Tensor) -> Dict[str, Tensor]:
+    T = x.shape[0]
+    h = [h0]
+    ys, vs = [], []
+    for t in range(T):
+        raw = x[t] @ W_x.T + h[-1] @ W_h.T + b
+        hn = torch.tanh(raw)
+        h.append(hn)
+        vs.append(raw)
+        ys.append(hn * silu(hn))
+    return {"h": torch.stack(h), "output": torch.stack(ys), "v": torch.stack(vs)}
+
+
+def e33_backward(W_x: Tensor, W_h: Tensor, x: Tensor, h: Tensor, v: Tensor,
+                 d_output: Tensor) -> Dict[str, Tensor]:
+    T, B, d = x.shape
+    dv_all = torch.zeros_like(x)
+    dh_rec = torch.zeros(B, d, dtype=x.dtype)
+    for t in range(T - 1, -1, -1):
+        h_t = h[t + 1]
+        dh = d_output[t] * (silu(h_t) + h_t * dsilu(h_t)) + dh_rec
+        th = torch.tanh(v[t])
+        dv = dh * (1.0 - th * th)
+        dv_all[t] = dv
+        dh_rec = dv @ W_h
+    dv2 = dv_all.reshape(T * B, d)
+    return {"dx": (dv2 @ W_x).reshape(T, B, d), "dW_x": dv2.T @ x.reshape(T * B, d),
+            "dW_h": dv2.T @ h[:T].reshape(T * B, d), "db": dv2.sum(0)}
 
 
 # ----------------------------------------------------------------------------

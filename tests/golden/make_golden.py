@@ -128,6 +128,26 @@ def run_e1_layer(mod, B, T, dim, seed):
     return inp, res
 
 
+def run_sibling_layer(mod, cls_name, B, T, dim, seed, **kw):
+    """A whole sibling layer of E1 (E32 / E33 / E57) from the reference's own file, default
+    init, power-iteration start vector pinned where the cell normalises W_h."""
+    torch.manual_seed(seed)
+    layer = getattr(mod, cls_name)(dim, **kw)
+    g = torch.Generator().manual_seed(seed + 1)
+    x = torch.randn(B, T, dim, generator=g)
+    r = torch.randn(B, T, dim, generator=g)
+    u = torch.randn(layer.d_inner, generator=g)
+    layer.cell._spectral_u = u / u.norm()
+    inp = {"x": x, "d_output": r, "spectral_u": layer.cell._spectral_u.clone()}
+    inp.update({"p_" + k: v.detach().clone() for k, v in layer.state_dict().items()})
+    xin = x.clone().requires_grad_(True)
+    out, h_final = layer(xin)
+    (out * r).sum().backward()
+    res = {"output": out, "h_final": h_final, "dx": xin.grad}
+    res.update({"g_" + k: p.grad for k, p in layer.named_parameters()})
+    return inp, res
+
+
 def run_ladder_lm(reference_root, seed):
     """The reference's LadderLM (level 1, spectral-norm W_h as it defaults to) on seeded
     token ids: loss and every parameter gradient.  Importing it pulls in the whole
@@ -157,7 +177,16 @@ def main():
     ap.add_argument("--reference",
                     default=os.environ.get("ELMAN_REFERENCE_DIR", os.path.join(os.sep, "root", "reference")))
     ap.add_argument("--only-lm", action="store_true")
+    ap.add_argument("--only-siblings", action="store_true")
     args = ap.parse_args()
+    if args.only_siblings:
+        for name, cls, seed, kw in (("e32_no_presilu", "E32NoPresilu", 61, {}),
+                                    ("e33_self_gate", "E33SelfGate", 62, {"r_h_mode": "spectral_norm"}),
+                                    ("e57_learned_radius", "E57LearnedRadius", 63, {"expansion": 1.0})):
+            mod = load_ref(args.reference, name)
+            inp, res = run_sibling_layer(mod, cls, 2, 8, 64, seed, **kw)
+            save(name.split("_")[0] + "_layer", True, inp, res, [2, 8, 64, seed])
+        return
     if args.only_lm:
         inp, res = run_ladder_lm(args.reference, seed=51)
         save("ladder_lm", True, inp, res, [3, 12, 32, 51])
@@ -197,6 +226,13 @@ def main():
 
     inp, res = run_ladder_lm(args.reference, seed=51)
     save("ladder_lm", True, inp, res, [3, 12, 32, 51])
+
+    for name, cls, seed, kw in (("e32_no_presilu", "E32NoPresilu", 61, {}),
+                                ("e33_self_gate", "E33SelfGate", 62, {"r_h_mode": "spectral_norm"}),
+                                ("e57_learned_radius", "E57LearnedRadius", 63, {"expansion": 1.0})):
+        mod = load_ref(args.reference, name)
+        inp, res = run_sibling_layer(mod, cls, 2, 8, 64, seed, **kw)
+        save(name.split("_")[0] + "_layer", True, inp, res, [2, 8, 64, seed])
 
 
 if __name__ == "__main__":

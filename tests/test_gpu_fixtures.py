@@ -184,3 +184,44 @@ def test_ladder_lm_bf16_gradients_match_the_fp32_model(chunks):
         # W_h's gradient passes through the spectral-norm scale (a near-cancelling sum): wider
         tol = 0.12 if n.endswith("W_h") else 4e-2
         assert orc.rel_err(p.grad.float().cpu(), q.grad.cpu()) < tol, n
+
+
+@pytest.mark.parametrize("name,cls,kw", [("e32_layer", "E32NoPresilu", {}),
+                                         ("e33_layer", "E33SelfGate", {"r_h_mode": "spectral_norm"}),
+                                         ("e57_layer", "E57LearnedRadius", {"expansion": 1.0})])
+def test_sibling_layers_on_gpu_match_reference_fixtures(golden_dir, name, cls, kw):
+    """E32 / E33 / E57 on the GPU (fp32) against the fixtures of the reference's own files."""
+    from elman_b200 import siblings
+    inp, want = load(golden_dir, name)
+    layer = getattr(siblings, cls)(inp["x"].shape[-1], **kw)
+    layer.load_state_dict({k[2:]: v for k, v in inp.items() if k.startswith("p_")})
+    layer = layer.cuda()
+    layer.cell._spectral_u = inp["spectral_u"].clone().cuda()
+    x = inp["x"].cuda().requires_grad_(True)
+    before = _lib.launch_count()
+    out, h_final = layer(x)
+    (out * inp["d_output"].cuda()).sum().backward()
+    torch.cuda.synchronize()
+    assert _lib.launch_count() > before
+    got = {"output": out, "h_final": h_final, "dx": x.grad}
+    for k, p in layer.named_parameters():
+        got["g_" + k] = p.grad
+    check(got, want, name)
+
+
+@pytest.mark.parametrize("T,B,d", [(12, 16, 128), (20, 32, 256), (9, 64, 256)])
+def test_e33_self_gate_bf16_tensor_core_path_matches_oracle(T, B, d):
+    from elman_b200 import hasty_pytorch_lib as H
+    inp = orc.make_e1_inputs(T, B, d, seed=333 + d)
+    dev = {k: v.to(torch.bfloat16).cuda().contiguous() for k, v in inp.items()}
+    ref = {k: v.to(torch.bfloat16).float() for k, v in inp.items()}
+    before = _lib.tc_launch_count()
+    h, out, v = H.e33_self_gate_forward(True, dev["x"], dev["h0"], dev["W_x"], dev["W_h"], dev["b"])
+    dx, dWx, dWh, db = H.e33_self_gate_backward(dev["W_x"], dev["W_h"], dev["x"], h, v, dev["d_output"])
+    torch.cuda.synchronize()
+    assert _lib.tc_launch_count() >= before + 2 and _lib.device_status()[0] == 0
+    f = orc.e33_forward(ref["x"], ref["h0"], ref["W_x"], ref["W_h"], ref["b"])
+    g = orc.e33_backward(ref["W_x"], ref["W_h"], ref["x"], f["h"], f["v"], ref["d_output"])
+    got = {"h": h, "output": out, "v": v, "dx": dx, "dW_x": dWx, "dW_h": dWh, "db": db}
+    for k, w in {**f, **g}.items():
+        assert orc.rel_err(got[k].float().cpu(), w) < 2e-2, k

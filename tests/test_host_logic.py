@@ -91,6 +91,16 @@ class OracleBackend:
         return [torch.cat([g["dx"], carry]), g["dz"], g["db"]]
 
     @staticmethod
+    def e33_self_gate_forward(training, x, h0, W_x, W_h, b):
+        o = orc.e33_forward(x, h0, W_x, W_h, b)
+        return [o["h"], o["output"], o["v"] if training else x.new_empty(0)]
+
+    @staticmethod
+    def e33_self_gate_backward(W_x, W_h, x, h, v, d_output):
+        g = orc.e33_backward(W_x, W_h, x, h, v, d_output)
+        return [g["dx"], g["dW_x"], g["dW_h"], g["db"]]
+
+    @staticmethod
     def stock_elman_forward(training, x, h0, W_x, W_h, W_gate, b, b_gate):
         o = orc.e0_forward(x, h0, W_x, W_h, W_gate, b, b_gate)
         e = x.new_empty(0)
@@ -134,8 +144,8 @@ def as_fake_cuda(t):
 
 @pytest.fixture()
 def oracle_backend(monkeypatch):
-    from elman_b200 import fused_ops
-    for mod in (e1mod, e0mod, e5mod, fused_ops):
+    from elman_b200 import fused_ops, siblings
+    for mod in (e1mod, e0mod, e5mod, fused_ops, siblings):
         monkeypatch.setattr(mod, "hasty_pytorch_lib", OracleBackend)
 
 
@@ -380,3 +390,37 @@ def test_graphed_step_raises_when_the_status_word_reports_a_timeout(monkeypatch)
     monkeypatch.setattr(_lib, "device_status", lambda clear=False: (0, 0))
     step(torch.ones(2))
     assert step.graph.replays == 1 and step.loss_value() == 1.0
+
+
+@pytest.mark.parametrize("name,cls,kw", [("e32_layer", "E32NoPresilu", {}),
+                                         ("e33_layer", "E33SelfGate", {"r_h_mode": "spectral_norm"}),
+                                         ("e57_layer", "E57LearnedRadius", {"expansion": 1.0})])
+def test_sibling_layers_against_reference_fixtures(golden_dir, oracle_backend, name, cls, kw):
+    """E32 / E33 / E57 (the reference's ladder levels that run on the E1 recurrence) against
+    what the reference's own files computed: outputs, state, every parameter gradient."""
+    from elman_b200 import siblings
+    inp, want = load(golden_dir, name)
+    layer = getattr(siblings, cls)(inp["x"].shape[-1], **kw)
+    sd = {k[2:]: v for k, v in inp.items() if k.startswith("p_")}
+    assert set(sd) == set(layer.state_dict()), "parameter names differ from the reference's"
+    layer.load_state_dict(sd)
+    layer.cell._spectral_u = inp["spectral_u"].clone()
+    x = as_fake_cuda(inp["x"].clone()).requires_grad_(True)
+    out, h_final = layer(x)
+    (out * inp["d_output"]).sum().backward()
+    assert orc.rel_err(out, want["output"]) < 2e-5
+    assert orc.rel_err(h_final, want["h_final"]) < 2e-5
+    assert orc.rel_err(x.grad, want["dx"]) < 2e-5
+    for k, p in layer.named_parameters():
+        assert orc.rel_err(p.grad, want["g_" + k]) < 5e-5, k
+
+
+def test_oracle_e33_explicit_backward_equals_autograd():
+    inp = orc.make_e1_inputs(7, 3, 24, seed=4)
+    f = orc.e33_forward(inp["x"], inp["h0"], inp["W_x"], inp["W_h"], inp["b"])
+    g = orc.e33_backward(inp["W_x"], inp["W_h"], inp["x"], f["h"], f["v"], inp["d_output"])
+    leaves = [inp[k].clone().requires_grad_(True) for k in ("x", "W_x", "W_h", "b")]
+    o = orc.e33_forward(leaves[0], inp["h0"], leaves[1], leaves[2], leaves[3])
+    (o["output"] * inp["d_output"]).sum().backward()
+    for k, t in zip(("dx", "dW_x", "dW_h", "db"), leaves):
+        assert orc.rel_err(g[k], t.grad) < 1e-5, k

@@ -28,6 +28,7 @@ REFERENCE_FUNCTIONS = {
     "mamba_gated_elman_forward": (7, 3), "mamba_gated_elman_backward": (7, 5),
     "pure_lowrank_elman_forward": (10, 3), "pure_lowrank_elman_backward": (10, 8),
     "pure_lowrank_elman_forward_fused": (10, 3), "pure_lowrank_elman_backward_fused": (10, 8),
+    "e33_self_gate_forward": (6, 3), "e33_self_gate_backward": (6, 4),
 }
 
 
@@ -64,6 +65,9 @@ def test_reference_model_files_find_the_extension_unchanged():
     assert _load_reference("mamba_gated_elman").MAMBA_CUDA_AVAILABLE is True
     assert _load_reference("stock_elman").HASTE_AVAILABLE is True
     assert _load_reference("pure_lowrank_elman").HASTY_AVAILABLE is True
+    # siblings that run on the same functions (E32, E57: the E1 pair; E33: its own pair)
+    assert _load_reference("e32_no_presilu").MAMBA_CUDA_AVAILABLE is True
+    assert _load_reference("e33_self_gate").E33_CUDA_AVAILABLE is True
 
 
 @needs_reference
