@@ -299,6 +299,7 @@ int elman_b200_set_option(const char* name, long value) {
   else if (!strcmp(name, "gemm_persistent")) o.gemm_persistent = value;
   else if (!strcmp(name, "test_stall_step")) o.test_stall_step = value;
   else if (!strcmp(name, "rec_replicas")) o.rec_replicas = value;
+  else if (!strcmp(name, "rec_group_cap")) o.rec_group_cap = value;
   else return set_error(ELMAN_ERR_ARG, "unknown option '%s'", name);
   return ELMAN_OK;
 }
@@ -320,6 +321,7 @@ long elman_b200_get_option(const char* name) {
   if (!strcmp(name, "gemm_persistent")) return o.gemm_persistent;
   if (!strcmp(name, "test_stall_step")) return o.test_stall_step;
   if (!strcmp(name, "rec_replicas")) return o.rec_replicas;
+  if (!strcmp(name, "rec_group_cap")) return o.rec_group_cap;
   return -1;
 }
 

@@ -56,6 +56,7 @@ struct Options {
   // Failure-detection test hook: >= 1 makes thread block 0 of the tensor-core kernels wait, at
   // that step (GEMM: K iteration), for something nothing will deliver, so that a real bounded
   // wait runs out and the give-up path of every role executes.  -1 = off.
+  long rec_group_cap = 0;      // widest batch group of the throughput plan: 0 auto (64), 16 / 32 / 64
   long rec_replicas = 0;       // batch replicas of the throughput plan: 0 auto, 1 off, n = at most n
   long test_stall_step = -1;
 };

@@ -1003,12 +1003,12 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
   if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = 0; }
   // co-residency depends on the device; callers may come from several host threads
   // (autograd's) and use several GPUs
-  typedef std::tuple<int, int, int, int, long, long, long, long, long, long, long> Key;
+  typedef std::tuple<int, int, int, int, long, long, long, long, long, long, long, long> Key;
   static std::map<Key, RecPlan> cache;
   std::lock_guard<std::mutex> lock(g_rec_mutex);
   const Key key(dev, B, d, compact, options().rec_ksplit, options().rec_groups,
                 options().rec_mma_warps, options().rec_w_tmem, options().rec_large_batch,
-                options().rec_fin_groups, options().rec_replicas);
+                options().rec_fin_groups, options().rec_replicas, options().rec_group_cap);
   {
     auto it = cache.find(key);
     if (it != cache.end()) return it->second;
@@ -1038,7 +1038,9 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
     // throughput plan for batches that need several groups anyway: the widest group
     // first (fixed per-group costs are paid fewer times per step), the weight tile in
     // tensor memory when shared memory cannot hold it beside the wider state tiles
-    for (int ng_cap = 64; ng_cap >= 16 && !found.ok; ng_cap >>= 1)
+    const int cap0 = options().rec_group_cap >= 16 && options().rec_group_cap <= 64
+                         ? (int)options().rec_group_cap : 64;
+    for (int ng_cap = cap0; ng_cap >= 16 && !found.ok; ng_cap >>= 1)
       for (int S = MAX_S; S >= 1 && !found.ok; S >>= 1) {
         if (want_S > 0 && S != want_S) continue;
         for (int wt = 0; wt <= 1 && !found.ok; ++wt) {

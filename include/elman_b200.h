@@ -82,6 +82,8 @@ int elman_b200_device_status(int* detail, int clear);
  *                    0 (default) = as many copies of the grid as fit on the device, each on
  *                    its own share of the batch (they never wait on each other), 1 = one
  *                    copy, n = at most n.  Results do not depend on it.
+ *   "rec_group_cap"  widest batch group (16, 32 or 64 rows) the large-batch plan may form;
+ *                    0 (default) = 64
  *   "test_stall_step" failure-detection test hook, -1 (default) = off.  With a value k >= 1
  *                    thread block 0 of the next tensor-core launches (recurrences: at time
  *                    step k; projection GEMMs: at K iteration k) waits for something that
