@@ -2,6 +2,7 @@
 
     python -m elman_b200.build            # build if sources are newer than the .so
     python -m elman_b200.build --force
+    python -m elman_b200.build --microbench   # also the standalone program under csrc/microbench
 
 The result, elman_b200/lib/libelman_b200.so, is a plain C-ABI shared library
 (see include/elman_b200.h); it does not link against PyTorch.
@@ -37,7 +38,7 @@ def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh", ".h"))]
     deps.append(os.path.join(HERE, "..", "include", "elman_b200.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 
@@ -78,5 +79,20 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_microbench() -> str:
+    """The standalone measurement program under csrc/microbench (MMA issue rate, cluster exchange)."""
+    src = os.path.join(CSRC, "microbench", "mma_issue_and_cluster_exchange.cu")
+    exe = os.path.join(LIBDIR, "mma_issue_and_cluster_exchange")
+    if os.path.exists(exe) and os.path.getmtime(exe) >= max(
+            os.path.getmtime(src), os.path.getmtime(os.path.join(CSRC, "sm100_ptx.cuh"))):
+        return exe
+    os.makedirs(LIBDIR, exist_ok=True)
+    subprocess.check_call([find_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3",
+                           "-std=c++17", "-lineinfo", "-o", exe, src])
+    return exe
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--microbench" in sys.argv:
+        print(build_microbench())
