@@ -42,6 +42,16 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NCU_TRAFFIC_BYTES = {"rec_tc_kernel<fwd>": 170.1e6, "rec_tc_kernel<bwd>": 231.1e6}  # profiles/rec_tc_kernel_e1_c1.md
 
 
+def host_topology():
+    """What the ranks share on the host side: CPUs this process may run on and NUMA nodes visible."""
+    import glob
+    try:
+        cpus = len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        cpus = os.cpu_count()
+    return {"cpus": cpus, "numa_nodes": len(glob.glob("/sys/devices/system/node/node[0-9]*"))}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -731,9 +741,14 @@ def main():
     if _lib.device_status()[0] != 0:
         raise SystemExit("a device-side wait timed out: " + str(_lib.device_status()))
 
+    # every rank's own end-to-end time: the host's PCIe / memory system is shared by the ranks
+    e2e_each = torch.zeros(world, dtype=torch.float64, device=dev)
+    e2e_each[rank] = e2e_ms
     t_all = torch.tensor([total_ms, e2e_ms, e2e_serial_ms], dtype=torch.float64, device=dev)
     if world > 1:
+        dist.all_reduce(e2e_each, op=dist.ReduceOp.SUM)
         dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+    e2e_each = [float(v) / args.steps for v in e2e_each.cpu()]
     total_ms, e2e_ms, e2e_serial_ms = (float(v) for v in t_all.cpu())
 
     # Beside the headline, outside its timed region (as the CPU baseline is): the same cell
@@ -798,6 +813,12 @@ def main():
                     "h2d_bytes_per_step": 3 * T * B * D * 2,
                     "d2h_bytes_per_step": 3 * T * B * D * 2 + 2 * D * D * 2 + D * 2,
                     "ms_per_step": e2e_ms / args.steps,
+                    "per_rank": {
+                        "ms_per_step": e2e_each,
+                        "h2d_gbs": [3 * T * B * D * 2 / (ms * 1e6) for ms in e2e_each],
+                        "d2h_gbs": [(3 * T * B * D * 2 + 2 * D * D * 2 + D * 2) / (ms * 1e6)
+                                    for ms in e2e_each],
+                        "host": host_topology()},
                     "how": "E1HostPipeline: pinned host buffers in and out every step; upload, "
                            "kernels and download of consecutive steps overlap on 3 streams",
                     "one_call_at_a_time": {"value": tokens / (e2e_serial_ms / 1e3),

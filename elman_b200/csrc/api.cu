@@ -297,6 +297,7 @@ int elman_b200_set_option(const char* name, long value) {
   else if (!strcmp(name, "rec_large_batch")) o.rec_large_batch = value;
   else if (!strcmp(name, "rec_fin_groups")) o.rec_fin_groups = value;
   else if (!strcmp(name, "gemm_persistent")) o.gemm_persistent = value;
+  else if (!strcmp(name, "gemm_pair")) o.gemm_pair = value;
   else if (!strcmp(name, "test_stall_step")) o.test_stall_step = value;
   else if (!strcmp(name, "rec_replicas")) o.rec_replicas = value;
   else if (!strcmp(name, "rec_group_cap")) o.rec_group_cap = value;
@@ -319,6 +320,7 @@ long elman_b200_get_option(const char* name) {
   if (!strcmp(name, "rec_large_batch")) return o.rec_large_batch;
   if (!strcmp(name, "rec_fin_groups")) return o.rec_fin_groups;
   if (!strcmp(name, "gemm_persistent")) return o.gemm_persistent;
+  if (!strcmp(name, "gemm_pair")) return o.gemm_pair;
   if (!strcmp(name, "test_stall_step")) return o.test_stall_step;
   if (!strcmp(name, "rec_replicas")) return o.rec_replicas;
   if (!strcmp(name, "rec_group_cap")) return o.rec_group_cap;

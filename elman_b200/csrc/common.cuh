@@ -51,6 +51,7 @@ struct Options {
   long rec_direct_publish = 0;
   long rec_w_tmem = 0;
   long gemm_persistent = 0;    // 0 auto, 1 never, 2 always: the persistent 128x256 GEMM kernel
+  long gemm_pair = 0;          // 0 auto, 1 never, 2 whenever possible: 256x256 tiles on CTA pairs
   long rec_fin_groups = 0;     // 0 auto (two finalising groups from four batch groups on), 1 = always one
   long rec_large_batch = 1;    // 1: batches over 32 take the wide-group throughput plan
   // Failure-detection test hook: >= 1 makes thread block 0 of the tensor-core kernels wait, at

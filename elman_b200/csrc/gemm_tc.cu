@@ -14,6 +14,7 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "tc_helpers.cuh"
 
 namespace elman {
 
@@ -555,6 +556,245 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
 }
 
+// ---------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs computes one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2 (M = 256).  CTA r of the pair loads its own 128 rows of A and
+// its own 128 of the 256 columns' worth of W per K step (32 KB per stage and CTA instead
+// of 48 KB for the same flops per SM: a deeper ring in the same shared memory, a third
+// less L2 traffic), holds rows [128 r, 128 r + 128) of the accumulator in its tensor
+// memory and runs the epilogue for them.  The even CTA's MMA thread issues for both;
+// every load credits the even CTA's stage barrier; commits arrive on both CTAs' barriers
+// (tcgen05.commit multicast); no load is multicast.  Roles, epilogue and K order per
+// output element are those of the persistent kernel above.
+// Persistent over the work items, one CTA per SM, six 32 KB stages, two accumulator
+// buffers.  (A three-stage, one-tile-per-pair instantiation with two CTAs per SM was
+// measured slower on every shape and is not built.)
+// ---------------------------------------------------------------------------
+constexpr int Q_BM = 256, Q_BN = 256;             // tile of the pair
+constexpr int Q_A_BYTES = 128 * BK * 2, Q_B_BYTES = 128 * BK * 2;   // per CTA and stage
+constexpr int Q_STAGE_BYTES = Q_A_BYTES + Q_B_BYTES;
+template <int STAGES> constexpr int pair_smem_bytes() { return STAGES * Q_STAGE_BYTES + 1024; }
+
+template <int STAGES, int ACC_BUFS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                    const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];    // used in the even CTA only
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full[ACC_BUFS];
+  __shared__ __align__(8) uint64_t acc_empty[ACC_BUFS]; // used in the even CTA only
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ __align__(16) bf16 s_bias[ACC_BUFS][Q_BN];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = tch::cluster_ctarank();          // 0 = even CTA (issues the MMAs)
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * Q_A_BYTES;
+  const int nk = (p.K + BK - 1) / BK;
+  const int tiles_n = (p.N + Q_BN - 1) / Q_BN;
+  const int tiles = ((p.M + Q_BM - 1) / Q_BM) * tiles_n;
+  const int items = tiles * p.ksplit;
+  constexpr uint32_t TCOLS = ACC_BUFS * Q_BN;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < ACC_BUFS; ++b) {
+      ptx::mbar_init(&acc_full[b], 1);
+      ptx::mbar_init(&acc_empty[b], 2 * P_EPI_WARPS);   // the epilogue warps of both CTAs
+    }
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(&tmA);
+    ptx::prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(&tmem_slot, TCOLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  tch::cluster_sync_all();   // the peer's barriers exist before anything arrives on them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+  const uint32_t peer_abort = tch::mapa(ptx::smem_u32(&abort_flag), rank ^ 1u);
+  // a CTA that gives up tells its peer, so that the pair ends together
+  auto give_up = [&](int where) {
+    abort_flag = 1;
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(peer_abort), "r"(1) : "memory");
+    report_timeout(p.status, KID_GEMM_TC, where);
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      struct Cursor { int w, i, k_hi, m0, n0; };
+      auto open_item = [&](Cursor& cu) {
+        if (cu.w >= items) return;
+        const int t = cu.w / p.ksplit, sp = cu.w - t * p.ksplit;
+        cu.m0 = (t / tiles_n) * Q_BM + 128 * (int)rank;
+        cu.n0 = (t % tiles_n) * Q_BN + 128 * (int)rank;
+        cu.i = (int)((long)sp * nk / p.ksplit);
+        cu.k_hi = (int)((long)(sp + 1) * nk / p.ksplit);
+      };
+      auto advance = [&](Cursor& cu) {
+        if (++cu.i >= cu.k_hi) { cu.w += npairs; open_item(cu); }
+      };
+      Cursor ld{pair, 0, 0, 0, 0};
+      open_item(ld);
+      for (int it = 0; ld.w < items; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1u, p.spin_limit, abortp)) {
+          give_up(ld.i);
+          break;
+        }
+        const uint32_t bar = tch::mapa(ptx::smem_u32(&full_bar[s]), 0);
+        if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * Q_STAGE_BYTES);
+        if (!(it == p.stall_step && blockIdx.x == 0)) {
+          const int i = ld.i, m0 = ld.m0, n0 = ld.n0;
+          if (p.a_mn) {
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk)
+              ptx::tma_load_2d_pair(sA + s * Q_A_BYTES + blk * P_BLOCK_BYTES, &tmA, m0 + 64 * blk,
+                                    i * BK, bar);
+          } else {
+            ptx::tma_load_2d_pair(sA + s * Q_A_BYTES, &tmA, i * BK, m0, bar);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk)
+              ptx::tma_load_2d_pair(sB + s * Q_B_BYTES + blk * P_BLOCK_BYTES, &tmB, n0 + 64 * blk,
+                                    i * BK, bar);
+          } else {
+            ptx::tma_load_2d_pair(sB + s * Q_B_BYTES, &tmB, i * BK, n0, bar);
+          }
+        }
+        advance(ld);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = ptx::umma_idesc_bf16(Q_BM, Q_BN) | (p.a_mn ? (1u << 15) : 0u) |
+                             (p.b_mn ? (1u << 16) : 0u);
+      const uint64_t a_step = p.a_mn ? 128 : 2, b_step = p.b_mn ? 128 : 2;
+      // descriptors of ring slot 0; slot s adds its byte offset / 16 to the address field
+      const uint64_t da0 = p.a_mn ? ptx::umma_desc_mn_sw128(ptx::smem_u32(sA), P_BLOCK_BYTES)
+                                  : ptx::umma_desc_k_sw128(ptx::smem_u32(sA));
+      const uint64_t db0 = p.b_mn ? ptx::umma_desc_mn_sw128(ptx::smem_u32(sB), P_BLOCK_BYTES)
+                                  : ptx::umma_desc_k_sw128(ptx::smem_u32(sB));
+      int lt = 0;
+      uint32_t s = 0, ph = 0;            // ring slot and phase of the next stage to consume
+      bool ready = false;                // its barrier already seen complete
+      bool ok = true;
+      for (int w = pair; w < items && ok; w += npairs, ++lt) {
+        const int sp = w % p.ksplit;
+        const int k_lo = (int)((long)sp * nk / p.ksplit), k_hi = (int)((long)(sp + 1) * nk / p.ksplit);
+        const int b = lt % ACC_BUFS;
+        const uint32_t use = (uint32_t)(lt / ACC_BUFS);
+        if (!ptx::mbar_wait(&acc_empty[b], (use & 1u) ^ 1u, p.spin_limit * 8, abortp)) {
+          give_up(0xFFFE);
+          ok = false;
+          break;
+        }
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * Q_BN);
+        for (int i = k_lo; i < k_hi; ++i) {
+          if (!ready && !ptx::mbar_wait(&full_bar[s], ph, p.spin_limit, abortp)) {
+            give_up(i);
+            ok = false;
+            break;
+          }
+          uint32_t s_next = s + 1, ph_next = ph;
+          if (s_next == STAGES) { s_next = 0; ph_next ^= 1u; }
+          ready = ptx::umma_stage_pair(d_tmem, da0 + (uint64_t)(s * (Q_A_BYTES / 16)),
+                                       db0 + (uint64_t)(s * (Q_B_BYTES / 16)), a_step, b_step, idesc,
+                                       i > k_lo ? 1u : 0u, &empty_bar[s], &full_bar[s_next], ph_next);
+          s = s_next;
+          ph = ph_next;
+        }
+        if (ok) ptx::umma_commit_pair(&acc_full[b], 3);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int et = tid - 64;
+    constexpr int CH = Q_BN / 32 / 2;
+    const bool vec_ok = ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0);
+    int lt = 0;
+    for (int w = pair; w < items; w += npairs, ++lt) {
+      const int t = w / p.ksplit, sp = w - t * p.ksplit;
+      const int b = lt % ACC_BUFS;
+      const uint32_t use = (uint32_t)(lt / ACC_BUFS);
+      const int m0 = (t / tiles_n) * Q_BM + 128 * (int)rank, n0 = (t % tiles_n) * Q_BN;
+      if (p.bias != nullptr) {
+        const int n = n0 + et;
+        s_bias[b][et] = n < p.N ? p.bias[n] : __float2bfloat16_rn(0.f);
+      }
+      bool ok = ptx::mbar_wait(&acc_full[b], use & 1u, p.spin_limit * 8, abortp);
+      if (!ok && abort_flag == 0) give_up(0xFFFF);
+      uint32_t stop;
+      asm volatile(
+          "{\n\t.reg .pred pp, qq;\n\t"
+          "setp.ne.b32 pp, %1, 0;\n\t"
+          "bar.red.or.pred qq, 1, %2, pp;\n\t"
+          "selp.b32 %0, 1, 0, qq;\n\t}"
+          : "=r"(stop)
+          : "r"((uint32_t)(!ok || abort_flag != 0)), "n"(32 * P_EPI_WARPS)
+          : "memory");
+      if (stop) break;
+      ptx::tc_fence_after();
+      const int gm = m0 + quarter * 32 + lane;
+      const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) +
+                            (uint32_t)(b * Q_BN + half * (Q_BN / 2));
+      uint32_t r[2][32];
+      ptx::tmem_ld32(tsrc, r[0]);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        ptx::tmem_ld_wait();
+        if (c + 1 < CH) ptx::tmem_ld32(tsrc + (uint32_t)((c + 1) * 32), r[(c + 1) & 1]);
+        const int col = half * (Q_BN / 2) + c * 32;
+        if (p.ksplit == 1) {
+          store_chunk(p, gm, n0 + col, r[c & 1], vec_ok,
+                      p.bias != nullptr ? &s_bias[b][col] : nullptr);
+        } else if (gm < p.M) {
+          float* dst = p.partial + ((long)sp * p.M + gm) * p.N + n0 + col;
+          if (n0 + col + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<uint4*>(dst + j) =
+                  make_uint4(r[c & 1][j], r[c & 1][j + 1], r[c & 1][j + 2], r[c & 1][j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + col + j < p.N) dst[j] = __uint_as_float(r[c & 1][j]);
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(tch::mapa(ptx::smem_u32(&acc_empty[b]), 0));
+    }
+  }
+  if (abort_flag != 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  // neither CTA may leave while the other can still read its shared memory (the MMAs read
+  // both CTAs' operand tiles) or arrive on its barriers
+  tch::cluster_sync_all();
+  if (warp == 1) ptx::tmem_dealloc_pair(tmem_base, TCOLS);
+}
+
 // C = sum over the K ranges of the partial sums (+ bias) (+ C), in a fixed order.
 __global__ void splitk_reduce_kernel(GemmParams p) {
   const long total = (long)p.M * p.N;
@@ -639,6 +879,8 @@ int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int l
 
 int gemm_tc_persistent(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
                        int b_mn, const GemmParams& p, cudaStream_t stream);
+int gemm_tc_pair(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
+                 int b_mn, GemmParams p, float* splitk, size_t splitk_bytes, cudaStream_t stream);
 namespace { int sm_count(); }
 
 int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
@@ -652,6 +894,31 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
           (uintptr_t)split->aux) & 15) != 0)
       return set_error(ELMAN_ERR_UNSUPPORTED, "split epilogue: shape or alignment not supported");
     splitk = nullptr;   // the three-output epilogue has no partial-sum form
+  }
+  {
+    // option gemm_pair: 0 = CTA pairs (256x256 tiles) for shapes they tile well and fill the
+    // device with (at least two tiles per SM pair, or a K split over the pairs) — a launch
+    // that shares the SMs with others, like the per-chunk GEMMs of the layer pipeline, is
+    // better served by the small one-tile CTAs; 1 = never; 2 = whenever the shape allows
+    const long pair = options().gemm_pair;
+    const long tiles256 = (long)((M + Q_BM - 1) / Q_BM) * ((N + Q_BN - 1) / Q_BN);
+    const bool tiles_well = M >= Q_BM && N >= Q_BN && (N % Q_BN == 0 || N >= 4 * Q_BN) &&
+                            (tiles256 >= sm_count() ||
+                             (splitk != nullptr && split == nullptr && tiles256 * 4 <= sm_count()));
+    if (pair != 1 && M >= 128 && N >= 128 && (pair == 2 || tiles_well)) {
+      GemmParams q;
+      q.M = M; q.N = N; q.K = K;
+      q.bias = bias; q.C = C; q.ldc = ldc; q.c_is_f32 = c_is_f32; q.accumulate = accumulate;
+      q.spin_limit = options().spin_limit;
+      q.stall_step = (int)options().test_stall_step;
+      q.status = device_status_ptr();
+      q.a_mn = a_mn; q.b_mn = b_mn;
+      if (split != nullptr) {
+        q.split = split->split; q.C_act = split->C_act; q.C_hi = split->C_hi;
+        q.split_mode = split->mode; q.aux = split->aux;
+      }
+      return gemm_tc_pair(M, N, K, A, lda, a_mn, W, ldw, b_mn, q, splitk, splitk_bytes, stream);
+    }
   }
   {
     // option gemm_persistent: 0 = the persistent 128x256 kernel once its tiles fill the SMs,
@@ -753,6 +1020,49 @@ int gemm_tc_persistent(int M, int N, int K, const bf16* A, int lda, int a_mn, co
   count_launch(true);
   ELMAN_CUDA_CHECK(cudaGetLastError());
   if (p.ksplit > 1) {
+    const long total = (long)M * N;
+    const int rgrid = (int)((total + 255) / 256 < 148L * 8 ? (total + 255) / 256 : 148L * 8);
+    splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(p);
+    count_launch(false);
+    ELMAN_CUDA_CHECK(cudaGetLastError());
+  }
+  return ELMAN_OK;
+}
+
+// The CTA-pair kernel; K is cut into ranges when the tiles alone would leave SM pairs idle.
+int gemm_tc_pair(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
+                 int b_mn, GemmParams p, float* splitk, size_t splitk_bytes, cudaStream_t stream) {
+  constexpr int PAIR_STAGES = 6;
+  static bool attr_set[kMaxDev] = {false};
+  const int pairs = sm_count() / 2;
+  const int tiles = ((M + Q_BM - 1) / Q_BM) * ((N + Q_BN - 1) / Q_BN);
+  int ksplit = 1;
+  if (splitk != nullptr && tiles * 2 <= pairs) {
+    const int nk = (K + BK - 1) / BK;
+    ksplit = pairs / tiles;
+    if (ksplit > GEMM_MAX_KSPLIT) ksplit = GEMM_MAX_KSPLIT;
+    while (ksplit > 1 && (nk / ksplit < 8 || (size_t)ksplit * M * N * sizeof(float) > splitk_bytes))
+      --ksplit;
+  }
+  p.ksplit = ksplit;
+  p.partial = splitk;
+  CUtensorMap tmA, tmB;
+  if (a_mn)
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK));
+  else
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 128));
+  if (b_mn)
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, BK));
+  else
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128));
+  const int items = tiles * ksplit;
+  auto kern = gemm_tc_pair_kernel<PAIR_STAGES, 2>;
+  ELMAN_RETURN_IF(ensure_dynamic_smem(kern, pair_smem_bytes<PAIR_STAGES>(), attr_set));
+  const int grid = 2 * (items < pairs ? items : pairs);
+  kern<<<grid, P_THREADS, pair_smem_bytes<PAIR_STAGES>(), stream>>>(tmA, tmB, p);
+  count_launch(true);
+  ELMAN_CUDA_CHECK(cudaGetLastError());
+  if (ksplit > 1) {
     const long total = (long)M * N;
     const int rgrid = (int)((total + 255) / 256 < 148L * 8 ? (total + 255) / 256 : 148L * 8);
     splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(p);

@@ -35,7 +35,7 @@ namespace {
 using namespace tch;
 
 constexpr int LR_MMA_WARPS = 6;
-constexpr int LR_EPI_THREADS = 128;
+constexpr int LR_EPI_THREADS = 256;   // two warps per quarter of the TMEM lanes, each takes half of the batch columns
 constexpr int LR_THREADS = 32 * (1 + LR_MMA_WARPS) + LR_EPI_THREADS;  // loader + MMA + epilogue
 constexpr int LR_MAX_NC = 16;
 constexpr int LR_MAX_MT = 4;   // 128-row tiles of the padded rank (r_pad <= 512)
@@ -57,7 +57,7 @@ struct LowRankTcParams {
   int stall_step;   // test hook: block 0 withholds its share of the rank vector at this step (-1 off)
 };
 
-// Barrier over the 128 epilogue threads that also ORs a predicate.
+// Barrier over the epilogue threads that also ORs a predicate.
 __device__ __forceinline__ bool lr_bar_or(bool pred) {
   uint32_t r;
   asm volatile(
@@ -105,6 +105,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
   __shared__ __align__(8) uint64_t in_empty;     // ... and were consumed
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ float s_db[128];                    // backward: bias-gradient sums of the upper column half
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NC = p.NC, Npad = p.Npad, B = p.B, T = p.T, Mr = p.Mr;
@@ -161,7 +162,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
 
   // One-time load of my tile of V into tensor memory: padded rank row rho goes to lane
   // rho % 128 of row tile rho / 128, its 128 bf16 (my feature block) into 64 columns.
-  if (warp > LR_MMA_WARPS) {
+  if (warp > LR_MMA_WARPS && warp <= LR_MMA_WARPS + 4) {
     const int quarter = warp & 3;
     const int m = quarter * 32 + lane;
     for (int mt = 0; mt < Mr; ++mt) {
@@ -261,8 +262,9 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
     __syncwarp();
   } else {
     // ============================== epilogue ==================================
-    const int et = tid - 32 * (1 + LR_MMA_WARPS);   // 0..127
+    const int et = tid - 32 * (1 + LR_MMA_WARPS);   // 0..255
     const int quarter = warp & 3;                    // TMEM lane quarter of this warp
+    const int half = et >> 7;                        // which 16 batch columns of every 32 this warp takes
     const int m = quarter * 32 + lane;               // accumulator row / my feature in the block
     const bool is_owner = c < p.n_own;
     const uint32_t stage_a = ptx::smem_u32(sStage), gather_a = ptx::smem_u32(sGather);
@@ -290,7 +292,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
           const uint32_t remote = mapa(stage_a + (uint32_t)(c * stage_src_bytes + lane * 16), (uint32_t)k);
           const uint32_t remote_bar = mapa(ptx::smem_u32(&part_full), (uint32_t)k);
           const uint32_t ta = tmem_base + lane_base + acc_col0 + (uint32_t)(2 * mt * Npad);
-          for (int cb = 0; cb < Npad; cb += 16) {
+          for (int cb = 16 * half; cb < Npad; cb += 32) {
             uint32_t r0[16], r1[16];
             ptx::tmem_ld16(ta + (uint32_t)cb, r0);
             ptx::tmem_ld16(ta + (uint32_t)(Npad + cb), r1);
@@ -315,7 +317,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
           if (et == 0) lr_stamp(p.trace, c, s, 4);
           if (good) {
             const int rl = et & 31, bgrp = et >> 5;
-            for (int q4 = bgrp; q4 < Npad / 4; q4 += 4) {
+            for (int q4 = bgrp; q4 < Npad / 4; q4 += LR_EPI_THREADS / 32) {
               float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
               for (int src = 0; src < NC; ++src) {
                 const float4 x = lds_f4(stage_a + (uint32_t)(src * stage_src_bytes + (q4 * 32 + rl) * 16));
@@ -356,7 +358,7 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
       if (et == 0) lr_stamp(p.trace, c, s, 9);
       if (good) {
         ptx::tc_fence_after();
-        for (int cb = 0; cb < Npad; cb += 16) {
+        for (int cb = 16 * half; cb < Npad; cb += 32) {
           float acc[16];
 #pragma unroll
           for (int u = 0; u < 16; ++u) acc[u] = 0.f;
@@ -427,7 +429,11 @@ lowrank_tc_kernel(const __grid_constant__ CUtensorMap tmU, const __grid_constant
       }
     }
     if (et == 0) bulk_wait_all();
-    if (BWD && abort_flag == 0) p.db[c * 128 + m] = db_acc;
+    if (BWD) {   // the two column halves of a feature, summed in a fixed order
+      if (half == 1) s_db[m] = db_acc;
+      lr_bar_or(false);
+      if (half == 0 && abort_flag == 0) p.db[c * 128 + m] = db_acc + s_db[m];
+    }
   }
 
   // ------------------------------ teardown ---------------------------------

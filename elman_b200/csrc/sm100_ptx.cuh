@@ -247,6 +247,95 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ------------------------------ CTA pairs (cta_group::2) --------------------
+// Two CTAs of a cluster (ranks 2k, 2k+1) act as one MMA unit: M = 256 rows, each CTA holds
+// its 128 rows of A, its half of B's N columns and its 128 rows of the accumulator (same
+// TMEM columns in both).  One thread of the even CTA issues the MMAs and the commits.
+// The allocation calls are made by the same warp of BOTH CTAs.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_slot)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// 2D tile load into THIS CTA's shared memory whose byte count is credited to an mbarrier
+// given as a shared::cluster address (the even CTA's barrier, for both CTAs of the pair).
+// No multicast: each CTA fetches its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, int c0,
+                                                 int c1, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(m), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One ring stage of the CTA-pair main loop as a single instruction sequence: test the NEXT
+// stage's barrier first, issue this stage's four K=16 MMAs, commit them to this stage's
+// "free" barrier in both CTAs, and only then read the test's result.  An MMA costs its issuing
+// thread about as long as it runs, so whatever else that thread does between MMAs is time
+// the tensor pipe idles; the barrier test's latency is spent under the MMAs this way.
+__device__ __forceinline__ bool umma_stage_pair(uint32_t tmem_d, uint64_t da, uint64_t db,
+                                                uint64_t a_step, uint64_t b_step, uint32_t idesc,
+                                                uint32_t accumulate_first, uint64_t* free_bar,
+                                                uint64_t* next_full_bar, uint32_t next_parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n\t.reg .pred pw, pa, pt;\n\t"
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "tcgen05.fence::after_thread_sync;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 pw, [%9], %10;\n\t"
+      "setp.ne.b32 pa, %6, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "add.u64 a1, %2, %4;\n\t"
+      "add.u64 b1, %3, %5;\n\t"
+      "add.u64 a2, a1, %4;\n\t"
+      "add.u64 b2, b1, %5;\n\t"
+      "add.u64 a3, a2, %4;\n\t"
+      "add.u64 b3, b2, %5;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], %2, %3, %7, pa;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], a1, b1, %7, pt;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], a2, b2, %7, pt;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%1], a3, b3, %7, pt;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%8], %11;\n\t"
+      "selp.b32 %0, 1, 0, pw;\n\t}"
+      : "=r"(ready)
+      : "r"(tmem_d), "l"(da), "l"(db), "l"(a_step), "l"(b_step), "r"(accumulate_first),
+        "r"(idesc), "r"(smem_u32(free_bar)), "r"(smem_u32(next_full_bar)), "r"(next_parity),
+        "h"((uint16_t)3)
+      : "memory");
+  return ready != 0;
+}
+// Arrive on the mbarrier at the same shared-memory offset in every CTA of `cta_mask` when
+// all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(smem_u32(bar)), "h"(cta_mask)
+      : "memory");
+}
+// Arrive on an mbarrier of another CTA of the cluster (address from mapa).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(

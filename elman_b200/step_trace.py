@@ -51,9 +51,12 @@ def phase_table(trace, path, steps=range(8, 60)):
         d = [trace[s][b] - trace[s][a] for s in steps if trace[s][a] and trace[s][b]]
         if d:
             rows.append((f"{la} -> {lb}", statistics.median(d)))
-    first, last = path[0][0], path[-1][0]
+    # the last stamp of the path that this launch wrote (the forward dense kernel has no
+    # separate publishing stamp: its finalising warps release the counter themselves)
+    first = path[0][0]
+    last, last_label = next((k, lb) for k, lb in reversed(path) if trace[steps[0]][k])
     d = [trace[s + 1][first] - trace[s][last] for s in steps]
-    rows.append((f"{path[-1][1]} -> next step's {path[0][1]}", statistics.median(d)))
+    rows.append((f"{last_label} -> next step's {path[0][1]}", statistics.median(d)))
     per = statistics.median(trace[s + 1][first] - trace[s][first] for s in steps)
     return per, rows
 

@@ -96,14 +96,17 @@ def test_lowrank_kernel_gives_up_when_a_block_withholds_its_share_and_recovers()
     assert_close(errors(got, oracle_e5(ref)), TOL[torch.bfloat16], "after the give-up")
 
 
+@pytest.mark.parametrize("pair", [1, 2])
 @pytest.mark.parametrize("persistent", [1, 2])
-def test_projection_gemm_gives_up_when_a_stage_never_lands_and_recovers(persistent):
+def test_projection_gemm_gives_up_when_a_stage_never_lands_and_recovers(persistent, pair):
     M, N, K = 256, 256, 1024
     g = torch.Generator().manual_seed(43)
     A = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
     W = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
     _lib.device_status(clear=True)
-    with option("gemm_persistent", persistent):   # 1: one tile per block, 2: persistent kernel
+    # persistent 1: one tile per block, 2: persistent kernel; pair 2: the CTA-pair kernel, where
+    # the even CTA's stage barrier never completes and both CTAs must end
+    with option("gemm_persistent", persistent), option("gemm_pair", pair):
         with option("spin_limit", 5000), option("test_stall_step", 5):
             H.gemm(H.GEMM_NT, A, W)
             _expect_timeout(KID_GEMM_TC)

@@ -80,15 +80,26 @@ def test_tensor_core_and_cuda_core_paths_agree():
     assert rel_err(a, b.float().cpu()) < 4e-3
 
 
+KERNELS = {"tile": (1, 1), "persistent": (1, 2), "pair": (2, 0)}
+
+
 @pytest.fixture()
 def gemm_kernel_choice():
-    old = _lib.get_option("gemm_persistent")
-    yield lambda v: _lib.set_option("gemm_persistent", v)
-    _lib.set_option("gemm_persistent", old)
+    """Force one of the three tcgen05 GEMM kernels: 128x128 tiles, persistent 128x256 tiles, and the
+    CTA-pair kernel (persistent, 256x256 tiles over two CTAs)."""
+    old = _lib.get_option("gemm_pair"), _lib.get_option("gemm_persistent")
+
+    def choose(name):
+        pair, persistent = KERNELS[name]
+        _lib.set_option("gemm_pair", pair)
+        _lib.set_option("gemm_persistent", persistent)
+    yield choose
+    _lib.set_option("gemm_pair", old[0])
+    _lib.set_option("gemm_persistent", old[1])
 
 
-def test_both_gemm_kernels_agree_bit_for_bit(gemm_kernel_choice):
-    """Every output element is accumulated over K in the same order by both kernels."""
+def test_all_gemm_kernels_agree_bit_for_bit(gemm_kernel_choice):
+    """Every output element is accumulated over K in the same order by all three kernels."""
     g = torch.Generator().manual_seed(99)
     A = torch.randn(1000, 520, generator=g).bfloat16().cuda()
     W = (torch.randn(1304, 520, generator=g) / 22).bfloat16().cuda()
@@ -96,24 +107,26 @@ def test_both_gemm_kernels_agree_bit_for_bit(gemm_kernel_choice):
     Bn = (torch.randn(520, 1304, generator=g) / 22).bfloat16().cuda()
     bias = torch.randn(1304, generator=g).bfloat16().cuda()
     outs = []
-    for choice in (1, 2):
+    for choice in KERNELS:
         gemm_kernel_choice(choice)
         outs.append((H.gemm(H.GEMM_NT, A, W, bias), H.gemm(H.GEMM_NN, A, Bn),
                      H.gemm(H.GEMM_TN, At, Bn)))
     torch.cuda.synchronize()
-    for a, b in zip(*outs):
-        assert torch.equal(a, b)
+    assert _lib.device_status()[0] == 0
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("persistent", [1, 2])
+@pytest.mark.parametrize("kernel", list(KERNELS))
 @pytest.mark.parametrize("M,N,K", [(512, 512, 128), (304, 520, 136), (1280, 1280, 2048),
                                    (2048, 1280, 1280), (384, 392, 64), (8, 16, 8),
-                                   (4096, 2560, 320)])
-def test_every_gemm_form(M, N, K, persistent, request):
+                                   (4096, 2560, 320), (136, 264, 72)])
+def test_every_gemm_form(M, N, K, kernel, request):
     """NT (+bias, +accumulate), NN and TN through elman_gemm: K-major and MN-major operands of
-    both tcgen05 kernels (128x128 tiles; persistent 128x256 tiles, forced here for every
-    shape), ragged tile edges, against fp32 matmuls."""
-    request.getfixturevalue("gemm_kernel_choice")(persistent)
+    all three tcgen05 kernels (forced here for every shape they can take), ragged tile edges,
+    against fp32 matmuls."""
+    request.getfixturevalue("gemm_kernel_choice")(kernel)
     g = torch.Generator().manual_seed(7 * M + 3 * N + K)
     s = K ** -0.5
     A = torch.randn(M, K, generator=g).bfloat16().cuda()
