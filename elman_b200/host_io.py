@@ -54,7 +54,14 @@ class E1HostPipeline:
 
     def submit(self, x, z, d_output):
         """Enqueues one call; returns the slot's dict of pinned host result buffers, valid
-        after wait() (or after the returned dict's "done" event has completed)."""
+        after wait() (or after the returned dict's "done" event has completed).
+
+        The buffers belong to one of `depth` ring slots and are REUSED: the submission numbered
+        `valid_until_call` (also in the dict; calls are counted from 0) writes into the same
+        host memory.  Consume or copy the results before making that submission; the pipeline
+        cannot know when the caller is done reading, so it only orders the device side (the
+        slot's previous kernels finish before its inputs are replaced, and downloads into one slot
+        are ordered on one stream)."""
         for name, t in (("x", x), ("z", z), ("d_output", d_output)):
             if t.is_cuda or not t.is_pinned():
                 raise RuntimeError(f"E1HostPipeline.submit: {name} must be a pinned host tensor")
@@ -86,6 +93,7 @@ class E1HostPipeline:
         s.busy = True
         res = dict(s.host)
         res["done"] = s.downloaded
+        res["valid_until_call"] = self.calls - 1 + len(self.slots)
         return res
 
     def wait(self):

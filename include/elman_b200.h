@@ -75,6 +75,10 @@ int elman_b200_device_status(int* detail, int clear);
  *                    instantiation with two finalising warp groups, 1 = always one group
  *   "gemm_persistent" 0 (default) = the persistent 128x256 GEMM kernel once its tiles fill the
  *                    SMs (and for the split-K weight gradients), 1 = never, 2 = always
+ *   "gemm_pair"      0 (default) = GEMMs whose 256x256 tiles fill the device (two per SM
+ *                    pair, or a K split over the pairs) run on CTA pairs
+ *                    (tcgen05.mma.cta_group::2), 1 = never, 2 = whenever the shape allows.
+ *                    All GEMM kernels give bit-identical results.
  *   "rec_large_batch" 1 (default) = batches over 32 rows take the throughput plan of
  *                    the tensor-core recurrence (widest batch group first), 0 = the
  *                    latency plan for every batch size
@@ -116,13 +120,18 @@ int elman_b200_last_timing(int phase, float* ms);
 
 /*
  * Diagnostics hook (no counterpart in the reference).  With option "rec_trace"
- * set, CTA 0 of the tensor-core recurrence kernel stores SM cycle stamps for its
- * first 64 steps, 16 slots per step: 0 dependency satisfied, 1 TMA issued,
- * 2 state tile landed, 3 MMAs issued, 4 accumulator complete, 5 partials
- * scattered, 6 all partials landed, 7 new state stored, 8 epilogue threads met,
- * 9 step published, 10 next inputs requested.  This call synchronises and copies
- * up to max_entries stamps of the most recent traced launch into dst (host).
- * The buffer lives in that call's workspace, which must still be allocated.
+ * set, CTA 0 of the tensor-core recurrence kernels stores SM cycle stamps for its
+ * first 64 steps, 16 slots per step.  Dense kernel (E0/E1/E33): 0 dependency
+ * satisfied, 11 proxy fence done, 1 TMA issued, 2 state tile landed, 3 MMAs
+ * issued, 4 accumulator complete, 5 partials scattered, 6 all partials landed,
+ * 14 partial sums read, 7 new state stored, 8 epilogue threads met, 9 step
+ * published, 10 next inputs requested.  Low-rank kernel (E5): 0 state ready,
+ * 1 phase-1 MMAs issued, 2 rank accumulator complete, 3 partials sent, 4 partials
+ * landed, 5 summed, 6 rank vector sent, 7 rank vector landed, 8 phase-2 MMAs
+ * issued, 9 state accumulator complete, 10 state written.  This call
+ * synchronises and copies up to max_entries stamps of the most recent traced
+ * launch into dst (host).  The buffer lives in that call's workspace, which must
+ * still be allocated.  `python -m elman_b200.step_trace` prints them as a table.
  */
 int elman_b200_recurrence_trace(long long* dst, int max_entries);
 

@@ -217,9 +217,10 @@ def test_host_pipeline_delivers_the_device_results():
     w = {n: calls[0][n].cuda() for n in ("W_x", "W_h", "b", "h0")}
     pipe = E1HostPipeline(T, B, d, w["W_x"], w["W_h"], w["b"], w["h0"], depth=2)
     got = []
-    for c in calls:
+    for k, c in enumerate(calls):
         res = pipe.submit(c["x"], c["z"], c["d_output"])
-        res["done"].synchronize()          # results of a slot are reused two calls later
+        assert res["valid_until_call"] == k + 2   # the slot's host buffers are reused two calls later
+        res["done"].synchronize()
         got.append({n: res[n].clone() for n in ("output", "dx", "dz", "dW_x", "dW_h", "db")})
     pipe.wait()
     for c, g in zip(calls, got):
