@@ -27,7 +27,7 @@ __device__ __forceinline__ bool bwait(uint64_t* bar, uint32_t parity, int* bad) 
 }
 
 // ---------------------------------------------------------------- 1. MMA
-__global__ void __launch_bounds__(192) mma_bench(int N, int issuers, int a_tmem, int reps, long long* out) {
+__global__ void __launch_bounds__(320) mma_bench(int N, int issuers, int a_tmem, int reps, long long* out) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t done_bar;
   __shared__ uint32_t tmem_slot;
@@ -191,11 +191,11 @@ int main(int argc, char** argv) {
   const int Ns[] = {16, 32, 64, 128, 256};
   for (int a_tmem = 0; a_tmem <= 1; ++a_tmem)
     for (int ni = 0; ni < 5; ++ni)
-      for (int issuers = 1; issuers <= 4; issuers *= 2) {
+      for (int issuers = 1; issuers <= 8; issuers *= 2) {
         const int reps = 80;
         if (issuers * Ns[ni] > 256) continue;   // the accumulators must stay inside tensor memory
         for (int rep = 0; rep < 2; ++rep) {
-          mma_bench<<<1, 192, 64 * 1024>>>(Ns[ni], issuers, a_tmem, reps, out);
+          mma_bench<<<1, 320, 64 * 1024>>>(Ns[ni], issuers, a_tmem, reps, out);
           CK(cudaDeviceSynchronize());
         }
         printf("A=%s N=%3d issuers=%d reps=%d: issue %lld  complete %lld cycles  (%.1f cyc/MMA)\n",

@@ -1021,18 +1021,23 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
     for (int S = 1; S <= MAX_S && !found.ok; S <<= 1) {
       if (want_S > 0 && S != want_S) continue;
       for (int wt = 0; wt <= 1 && !found.ok; ++wt) {
+        if (wt == 1 && options().rec_w_tmem == 2) continue;
         RecPlan pl = plan_for(B, d, S, 32, wt != 0, nin);
         if (pl.ok && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d, bwd)) found = pl;
       }
     }
   } else if (B <= 32 || options().rec_groups > 0 || options().rec_large_batch == 0) {
-    // latency plan: the largest K split (shortest per-step chain)
+    // latency plan: the largest K split (shortest per-step chain); the weight tile in tensor
+    // memory when it fits beside the accumulators (the MMAs issue faster with the A operand
+    // there: 32 instead of 44 cycles per MMA with four issuing warps), else in shared memory
     for (int S = MAX_S; S >= 1 && !found.ok; S >>= 1) {
       if (want_S > 0 && S != want_S) continue;
-      for (int ng_cap = 32; ng_cap >= 16 && !found.ok; ng_cap >>= 1) {
-        RecPlan pl = plan_for(B, d, S, ng_cap, options().rec_w_tmem != 0, nin);
-        if (pl.ok && plan_is_coresident(pl, d, bwd)) found = pl;
-      }
+      for (int ng_cap = 32; ng_cap >= 16 && !found.ok; ng_cap >>= 1)
+        for (int wt = 1; wt >= 0 && !found.ok; --wt) {
+          if (wt == 1 && options().rec_w_tmem == 2) continue;
+          RecPlan pl = plan_for(B, d, S, ng_cap, wt != 0, nin);
+          if (pl.ok && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d, bwd)) found = pl;
+        }
     }
   } else {
     // throughput plan for batches that need several groups anyway: the widest group
@@ -1044,7 +1049,7 @@ RecPlan make_plan(int T, int B, int d, int compact, bool bwd) {
       for (int S = MAX_S; S >= 1 && !found.ok; S >>= 1) {
         if (want_S > 0 && S != want_S) continue;
         for (int wt = 0; wt <= 1 && !found.ok; ++wt) {
-          if (wt == 0 && options().rec_w_tmem != 0) continue;
+          if ((wt == 0 && options().rec_w_tmem == 1) || (wt == 1 && options().rec_w_tmem == 2)) continue;
           RecPlan pl = plan_for(B, d, S, ng_cap, wt != 0, nin);
           if (pl.ok && pl.Ng > ng_cap / 2 && (wt == 0 || pl.w_tmem) && plan_is_coresident(pl, d, bwd))
             found = pl;

@@ -69,8 +69,9 @@ int elman_b200_device_status(int* detail, int clear);
  *                    stores; backward: a dedicated publisher warp), 1 = epilogue
  *                    warps in both directions, 2 = publisher warp in both.  All
  *                    modes give bit-identical results.
- *   "rec_w_tmem"     1 = keep the recurrent weight tile in tensor memory instead
- *                    of shared memory (A operand read from TMEM); bit-identical
+ *   "rec_w_tmem"     where the recurrent weight tile lives: 0 (default) = in tensor memory
+ *                    (A operand read from TMEM) where the plan prefers it and it fits, 1 = in
+ *                    tensor memory whenever it fits, 2 = always in shared memory; bit-identical
  *   "rec_fin_groups" 0 (default) = launches with four or more batch groups use the kernel
  *                    instantiation with two finalising warp groups, 1 = always one group
  *   "gemm_persistent" 0 (default) = the persistent 128x256 GEMM kernel once its tiles fill the

@@ -197,12 +197,16 @@ def test_both_publication_modes_give_identical_results(mode):
 
 
 def test_weights_in_tensor_memory_variant_is_bit_identical():
+    """The recurrent weight tile as the MMAs' A operand from tensor memory (1, also the default
+    where it fits) or from shared memory (2)."""
     inp = orc.make_e1_inputs(20, 32, 512, seed=32)
-    a, _ = run_e1(inp, torch.bfloat16)
+    default, _ = run_e1(inp, torch.bfloat16)
     with option("rec_w_tmem", 1):
+        a, _ = run_e1(inp, torch.bfloat16)
+    with option("rec_w_tmem", 2):
         b, _ = run_e1(inp, torch.bfloat16)
     for k in FWD_BWD_KEYS:
-        assert torch.equal(a[k], b[k]), k
+        assert torch.equal(a[k], b[k]) and torch.equal(default[k], b[k]), k
 
 
 def test_host_pipeline_delivers_the_device_results():
