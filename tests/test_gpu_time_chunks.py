@@ -172,6 +172,28 @@ def test_graphed_train_step_matches_eager_steps():
         assert abs(a - b) < 3e-2 * abs(a), (eager, graphed)
 
 
+def test_full_size_pipelined_step_keeps_every_wait_satisfied():
+    """configs[2] at full size (d1280 x 6, B32, T512, bf16), eager and pipelined over 8 chunks: six
+    recurrence launches whose blocks wait on one another run beside the device-wide GEMMs of the
+    other streams.  Nothing may time out (status word stays clear), the loss is finite, and the
+    gradients agree with the layer-by-layer pass."""
+    from elman_b200 import _lib
+    from elman_b200.ladder_lm import LadderLM, zipf_tokens
+    torch.manual_seed(5)
+    model = LadderLM(vocab_size=256, dim=1280, depth=6, level=1, r_h_mode="none",
+                     pipeline_chunks=0).cuda().bfloat16()
+    tokens = zipf_tokens(32, 513, seed=9).cuda()
+    _lib.device_status(clear=True)
+    loss_seq, g_seq = _lm_step(model, tokens)
+    model.pipeline_chunks = 8
+    for _ in range(3):
+        loss_pipe, g_pipe = _lm_step(model, tokens)
+        assert _lib.device_status()[0] == 0, _lib.device_status()
+        assert loss_pipe == loss_pipe and abs(loss_pipe - loss_seq) < 2e-2 * abs(loss_seq)
+    for n in g_seq:
+        assert orc.rel_err(g_pipe[n].cpu(), g_seq[n].cpu()) < 2 * TOL[torch.bfloat16], n
+
+
 @pytest.mark.parametrize("dtype,T,B,d", [(torch.float32, 7, 3, 40), (torch.bfloat16, 16, 32, 256),
                                          (torch.bfloat16, 9, 5, 72)])
 def test_phase_entry_points_compose_to_the_whole_call(dtype, T, B, d):
