@@ -71,6 +71,10 @@ SIGNATURES = {
     "elman_e1_hx_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 7 + [_P] * 4 + [_P, _Z, _P]),
     "elman_e1_hx_backward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e1_hx_backward": (_I, [_I, _I, _I, _I] + [_P] * 8 + [_P] * 6 + [_P, _Z, _P]),
+    "elman_e4_forward_workspace": (_Z, [_I, _I, _I, _I, _I]),
+    "elman_e4_forward": (_I, [_I, _I, _I, _I, _I, _I] + [_P] * 7 + [_P] * 3 + [_P, _Z, _P]),
+    "elman_e4_backward_workspace": (_Z, [_I, _I, _I, _I, _I]),
+    "elman_e4_backward": (_I, [_I, _I, _I, _I, _I] + [_P] * 8 + [_P] * 6 + [_P, _Z, _P]),
     "elman_e33_forward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e33_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 5 + [_P] * 3 + [_P, _Z, _P]),
     "elman_e33_backward_workspace": (_Z, [_I, _I, _I, _I]),

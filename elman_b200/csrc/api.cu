@@ -884,6 +884,178 @@ int elman_e5_backward_carry(int dtype, int T, int B, int d, int r, const void* U
   return ELMAN_OK;
 }
 
+// ------------------------------- E4 ----------------------------------------
+// E1 whose recurrent matrix is the product U V of two rank-r factors
+// (elman/models/lowrank_elman.py:16-46, :134-160 of the reference):
+//   h_t = tanh(W_x x_t + U (V h_{t-1}) + b),  y_t = h_t * silu(z_t)
+// The recurrence is the E5 one (the single-cluster low-rank kernel) fed with the dense
+// projection of x and with z as the gate input; the time-parallel part is E1's.
+
+struct E4FwdWs {
+  void* pre; float* tmp; int* sync; long long* trace; void* UP; void* VP;
+};
+static size_t carve_e4_fwd(int dtype, int T, int B, int d, int r, void* ws, E4FwdWs* o) {
+  Carver c(ws);
+  size_t es = esize(dtype);
+  o->pre = c.take((size_t)T * B * d * es);
+  o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
+  o->sync = (int*)c.take(rec_sync_bytes());
+  o->trace = (long long*)c.take(kTraceBytes);
+  o->UP = o->VP = nullptr;
+  if (dtype == ELMAN_BF16) {
+    size_t up = 0, vp = 0;
+    lowrank_tc_pad_bytes(d, r, &up, &vp);
+    o->UP = c.take(up);
+    o->VP = c.take(vp);
+  }
+  return c.total();
+}
+
+size_t elman_e4_forward_workspace(int dtype, int T, int B, int d, int r) {
+  E4FwdWs w;
+  return carve_e4_fwd(dtype, T, B, d, r, nullptr, &w);
+}
+
+int elman_e4_forward(int dtype, int training, int T, int B, int d, int r, const void* x,
+                     const void* z, const void* h0, const void* W_x, const void* U, const void* V,
+                     const void* b, void* h, void* output, void* v, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  ELMAN_ARG_CHECK(r >= 1, "rank must be positive (got %d)", r);
+  if (B == 0 || d == 0) return ELMAN_OK;
+  REQUIRE_PTR(h0); REQUIRE_PTR(h);
+  cudaStream_t st = (cudaStream_t)stream;
+  ELMAN_RETURN_IF(copy_rows(dtype, h0, h, (long)B * d, st));
+  if (T == 0) return ELMAN_OK;
+  REQUIRE_PTR(x); REQUIRE_PTR(z); REQUIRE_PTR(W_x); REQUIRE_PTR(U); REQUIRE_PTR(V); REQUIRE_PTR(b);
+  REQUIRE_PTR(output); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(!training || v != nullptr, "v must be provided when training");
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E4FwdWs w;
+  size_t need = carve_e4_fwd(dtype, T, B, d, r, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  ELMAN_RETURN_IF(proj_nt(dtype, T * B, d, d, x, d, W_x, d, b, w.pre, d, 0, st));
+  if (use_tc(dtype) && lowrank_tc_supported(T, B, d, r, 0)) {
+    LowRankTcArgs ta{};
+    ta.T = T; ta.B = B; ta.d = d; ta.r = r; ta.bwd = 0;
+    ta.Urole = U; ta.Vrole = V;
+    ta.in0 = w.pre; ta.in1 = z;
+    ta.state = h; ta.out0 = training ? v : nullptr; ta.out1 = output;
+    ta.UP = w.UP; ta.VP = w.VP; ta.sync = w.sync; ta.trace = w.trace;
+    return lowrank_tc(ta, st);
+  }
+  LowRankFwdArgs a{T, B, d, r, U, V, w.pre, z, h, output, training ? v : nullptr, w.tmp, w.sync};
+  return lowrank_fwd_generic(dtype, a, st);
+}
+
+struct E4BwdWs {
+  void* Ut; void* Vt; void* dv; float* db; float* tmp; int* sync; long long* trace;
+  void* Vh; void* dVh; void* UP; void* VP; void* UhP; void* VhP; void* dUP; void* dVP;
+  float* splitk; size_t splitk_bytes;
+};
+static size_t carve_e4_bwd(int dtype, int T, int B, int d, int r, void* ws, E4BwdWs* o) {
+  Carver c(ws);
+  size_t es = esize(dtype);
+  const int ra = e5_rank_alloc(dtype, r);
+  size_t TBr = (size_t)T * B * ra * es, TBd = (size_t)T * B * d * es;
+  o->Ut = c.take((size_t)d * r * es);
+  o->Vt = c.take((size_t)d * r * es);
+  o->dv = c.take(TBd + (size_t)B * d * es);  // one extra time slot: the zero gradient from the future
+  o->db = (float*)c.take((size_t)d * sizeof(float));
+  o->tmp = (float*)c.take((size_t)2 * B * r * sizeof(float));
+  o->sync = (int*)c.take(rec_sync_bytes());
+  o->trace = (long long*)c.take(kTraceBytes);
+  o->splitk_bytes = splitk_scratch_bytes(dtype, d, d);
+  o->splitk = o->splitk_bytes ? (float*)c.take(o->splitk_bytes) : nullptr;
+  o->Vh = c.take(TBr);
+  o->dVh = c.take(TBr);
+  o->UP = o->VP = o->UhP = o->VhP = o->dUP = o->dVP = nullptr;
+  if (dtype == ELMAN_BF16) {
+    size_t up = 0, vp = 0;
+    lowrank_tc_pad_bytes(d, r, &up, &vp);
+    o->UP = c.take(up);
+    o->VP = c.take(vp);
+    o->UhP = c.take((size_t)d * ra * es);
+    o->VhP = c.take((size_t)d * ra * es);
+    o->dUP = c.take((size_t)d * ra * es);
+    o->dVP = c.take((size_t)d * ra * es);
+  }
+  return c.total();
+}
+
+size_t elman_e4_backward_workspace(int dtype, int T, int B, int d, int r) {
+  E4BwdWs w;
+  return carve_e4_bwd(dtype, T, B, d, r, nullptr, &w);
+}
+
+int elman_e4_backward(int dtype, int T, int B, int d, int r, const void* W_x, const void* U,
+                      const void* V, const void* x, const void* z, const void* h, const void* v,
+                      const void* d_output, void* dx, void* dz, void* dW_x, void* dU, void* dV,
+                      void* db, void* workspace, size_t workspace_bytes, void* stream) {
+  ELMAN_RETURN_IF(check_common(dtype, T, B, d));
+  ELMAN_ARG_CHECK(r >= 1, "rank must be positive (got %d)", r);
+  if (d == 0) return ELMAN_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  REQUIRE_PTR(dW_x); REQUIRE_PTR(dU); REQUIRE_PTR(dV); REQUIRE_PTR(db);
+  size_t es = esize(dtype);
+  if (T == 0 || B == 0) {
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dW_x, 0, (size_t)d * d * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dU, 0, (size_t)d * r * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(dV, 0, (size_t)d * r * es, st));
+    ELMAN_CUDA_CHECK(cudaMemsetAsync(db, 0, (size_t)d * es, st));
+    return ELMAN_OK;
+  }
+  REQUIRE_PTR(W_x); REQUIRE_PTR(U); REQUIRE_PTR(V); REQUIRE_PTR(x); REQUIRE_PTR(z); REQUIRE_PTR(h);
+  REQUIRE_PTR(v); REQUIRE_PTR(d_output); REQUIRE_PTR(dx); REQUIRE_PTR(dz); REQUIRE_PTR(workspace);
+  ELMAN_ARG_CHECK(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
+  E4BwdWs w;
+  size_t need = carve_e4_bwd(dtype, T, B, d, r, workspace, &w);
+  if (workspace_bytes < need)
+    return set_error(ELMAN_ERR_WORKSPACE, "workspace %zu < required %zu", workspace_bytes, need);
+  const int TB = T * B;
+  const int rp = e5_rank_run(dtype, r);
+  const bool padded = rp != r;
+  const void *Uh = U, *Vh = V;       // as the time-parallel GEMMs see them: U [d, rp], V [rp, d]
+  if (padded) {
+    ELMAN_RETURN_IF(resize2d(dtype, U, d, r, w.UhP, d, rp, st));
+    ELMAN_RETURN_IF(resize2d(dtype, V, r, d, w.VhP, rp, d, st));
+    Uh = w.UhP; Vh = w.VhP;
+  }
+  ELMAN_RETURN_IF(transpose2d(dtype, d, r, U, w.Ut, st));  // [r,d]
+  ELMAN_RETURN_IF(transpose2d(dtype, r, d, V, w.Vt, st));  // [d,r]
+  ELMAN_CUDA_CHECK(cudaMemsetAsync((char*)w.dv + (size_t)T * B * d * es, 0, (size_t)B * d * es, st));
+  if (use_tc(dtype) && lowrank_tc_supported(T, B, d, r, 1)) {
+    LowRankTcArgs ta{};
+    ta.T = T; ta.B = B; ta.d = d; ta.r = r; ta.bwd = 1;
+    ta.Urole = w.Vt; ta.Vrole = w.Ut;
+    ta.in0 = z; ta.in1 = d_output; ta.in2 = h; ta.in3 = v;
+    ta.state = w.dv; ta.out0 = dz; ta.out1 = nullptr; ta.db = w.db;
+    ta.UP = w.UP; ta.VP = w.VP; ta.sync = w.sync; ta.trace = w.trace;
+    ELMAN_RETURN_IF(lowrank_tc(ta, st));
+  } else {
+    LowRankBwdArgs a{T, B, d, r, w.Ut, w.Vt, h, v, z, d_output, w.dv, dz, w.db, w.tmp, w.sync};
+    ELMAN_RETURN_IF(lowrank_bwd_generic(dtype, a, st));
+  }
+  ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
+  // time-parallel part: dx = dv W_x, dW_x = dv^T x; rank activations Vh = h V^T, dVh = dv U
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, nullptr, dx, d, 0, st));
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(proj_nt(dtype, TB, rp, d, h, d, Vh, d, nullptr, w.Vh, rp, 0, st));
+  ELMAN_RETURN_IF(gemm_nn(dtype, TB, rp, d, w.dv, d, Uh, rp, nullptr, w.dVh, rp, 0, st));
+  {  // dU [d, r] = dv^T [d, TB] * Vh [TB, rp]
+    void* out = padded ? w.dUP : dU;
+    ELMAN_RETURN_IF(gemm_tn(dtype, d, rp, TB, w.dv, w.Vh, out, st, w.splitk, w.splitk_bytes));
+    if (padded) ELMAN_RETURN_IF(resize2d(dtype, out, d, rp, dU, d, r, st));
+  }
+  {  // dV [r, d] = dVh^T [rp, TB] * h[0:T] [TB, d]
+    void* out = padded ? w.dVP : dV;
+    ELMAN_RETURN_IF(gemm_tn(dtype, rp, d, TB, w.dVh, h, out, st, w.splitk, w.splitk_bytes));
+    if (padded) ELMAN_RETURN_IF(copy_rows(dtype, out, dV, (long)r * d, st));
+  }
+  return ELMAN_OK;
+}
+
 // --------------------------- projection GEMM --------------------------------
 
 int elman_projection(int dtype, int M, int N, int K, const void* A, int lda, const void* W,

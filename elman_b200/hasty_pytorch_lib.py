@@ -590,6 +590,58 @@ def mamba_gated_elman_hx_backward(W_x, W_h, W_gh, x, z_gate, h, v, d_output):
 
 # --------------------------------------------------------------------------- E33
 
+def lowrank_elman_forward(training, x, z, h0, W_x, U, V, b):
+    """E4: h_t = tanh(W_x x_t + U (V h_{t-1}) + b), y_t = h_t * silu(z_t) -> [h, output, v];
+    the reference's lowrank_elman_forward (elman/cuda/pytorch/elman_ladder.cc:2665-2726)."""
+    fn = "lowrank_elman_forward"
+    dt = _check_inputs(fn, x, x=x, z=z, h0=h0, W_x=W_x, U=U, V=V, b=b)
+    if x.dim() != 3:
+        raise RuntimeError(f"{fn}: x must be [T, B, dim]")
+    T, B, d = x.shape
+    if U.dim() != 2 or U.shape[0] != d:
+        raise RuntimeError(f"{fn}: U must be [dim, rank]")
+    r = U.shape[1]
+    _shape(fn, z, (T, B, d), "z"); _shape(fn, h0, (B, d), "h0"); _shape(fn, W_x, (d, d), "W_x")
+    _shape(fn, V, (r, d), "V"); _shape(fn, b, (d,), "b")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        h = torch.empty(T + 1, B, d, dtype=x.dtype, device=x.device)
+        out = torch.empty(T, B, d, dtype=x.dtype, device=x.device)
+        v = torch.empty((T, B, d) if training else (0,), dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e4_forward_workspace(dt, T, B, d, r), x.device)
+        rc = lib.elman_e4_forward(dt, 1 if training else 0, T, B, d, r, _ptr(x), _ptr(z), _ptr(h0),
+                                  _ptr(W_x), _ptr(U), _ptr(V), _ptr(b), _ptr(h), _ptr(out), _ptr(v),
+                                  ws.data_ptr(), ws.numel(), _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [h, out, v]
+
+
+def lowrank_elman_backward(W_x, U, V, x, z, h, v, d_output):
+    """-> [dx, dz, dW_x, dU, dV, db]; the reference's lowrank_elman_backward (:2728-2800)."""
+    fn = "lowrank_elman_backward"
+    dt = _check_inputs(fn, x, W_x=W_x, U=U, V=V, x=x, z=z, h=h, v=v, d_output=d_output)
+    T, B, d = x.shape
+    r = U.shape[1]
+    _shape(fn, V, (r, d), "V"); _shape(fn, z, (T, B, d), "z"); _shape(fn, h, (T + 1, B, d), "h")
+    _shape(fn, v, (T, B, d), "v"); _shape(fn, d_output, (T, B, d), "d_output")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        dx, dz = torch.empty_like(x), torch.empty_like(x)
+        dW_x = torch.empty(d, d, dtype=x.dtype, device=x.device)
+        dU = torch.empty(d, r, dtype=x.dtype, device=x.device)
+        dV = torch.empty(r, d, dtype=x.dtype, device=x.device)
+        db = torch.empty(d, dtype=x.dtype, device=x.device)
+        ws = _workspace(lib.elman_e4_backward_workspace(dt, T, B, d, r), x.device)
+        rc = lib.elman_e4_backward(dt, T, B, d, r, _ptr(W_x), _ptr(U), _ptr(V), _ptr(x), _ptr(z),
+                                   _ptr(h), _ptr(v), _ptr(d_output), _ptr(dx), _ptr(dz), _ptr(dW_x),
+                                   _ptr(dU), _ptr(dV), _ptr(db), ws.data_ptr(), ws.numel(),
+                                   _stream(x.device))
+        _lib.check(rc, fn)
+        ws.record_stream(torch.cuda.current_stream(x.device))
+    return [dx, dz, dW_x, dU, dV, db]
+
+
 def e33_self_gate_forward(training, x, h0, W_x, W_h, b):
     """y_t = h_t * silu(h_t) -> [h, output, v (empty if not training)]; the reference's
     e33_self_gate_forward (elman/cuda/pytorch/elman_ladder.cc:444-497)."""

@@ -16,16 +16,17 @@ import torch.nn.functional as F
 from . import fused_ops
 from .mamba_gated_elman import MambaGatedElman
 from .pure_lowrank_elman import PureLowRankElman
-from .siblings import E32NoPresilu, E33SelfGate, E57LearnedRadius
+from .siblings import E32NoPresilu, E33SelfGate, E57LearnedRadius, LowRankElman
 from .stock_elman import StockElman
 
-_LEVELS = {0: StockElman, 1: MambaGatedElman, 5: PureLowRankElman, 32: E32NoPresilu,
-           33: E33SelfGate, 57: E57LearnedRadius}
+_LEVELS = {0: StockElman, 1: MambaGatedElman, 4: LowRankElman, 5: PureLowRankElman,
+           32: E32NoPresilu, 33: E33SelfGate, 57: E57LearnedRadius}
 
 
 def get_ladder_level(level):
-    """Layer class of an ablation-ladder level (0 = E0, 1 = E1, 5 = E5, 32 / 33 / 57 = the E1
-    siblings without pre-silu, with a self gate, with a learned spectral radius)."""
+    """Layer class of an ablation-ladder level (0 = E0, 1 = E1, 4 = E1 with a low-rank recurrent
+    matrix, 5 = E5, 32 / 33 / 57 = the E1 siblings without pre-silu, with a self gate, with a
+    learned spectral radius)."""
     try:
         return _LEVELS[int(level)]
     except (KeyError, ValueError):

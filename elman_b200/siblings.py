@@ -1,5 +1,5 @@
 """Siblings of E1 that run on the same recurrence kernels — the reference's ladder levels
-32, 33 and 57.  Class names, constructor arguments, parameter names and forward contracts
+4, 32, 33 and 57.  Class names, constructor arguments, parameter names and forward contracts
 follow the reference files so that checkpoints and callers carry over:
 
   E32NoPresilu      E1 without the silu on the recurrence input
@@ -7,6 +7,8 @@ follow the reference files so that checkpoints and callers carry over:
                     functions, :30-47)
   E33SelfGate       y_t = h_t * silu(h_t), in_proj to d_inner only
                     (elman/models/e33_self_gate.py:30-50, :52-193, :196-296)
+  LowRankElman      (E4) E1 whose recurrent matrix is U V, rank r; the recurrence runs on the
+                    low-rank (E5) kernel (elman/models/lowrank_elman.py:28-46, :49-160, :163-254)
   E57LearnedRadius  E1 whose W_h is rescaled to a LEARNED spectral radius
                     sigmoid(log_radius) * max_radius (elman/models/e57_learned_radius.py:25-148,
                     :151-254; reuses the E1 autograd Function, :118-121)
@@ -228,3 +230,105 @@ class E57LearnedRadius(nn.Module):
 
     def extra_repr(self):
         return f"dim={self.dim}, d_inner={self.d_inner}, LEVEL=57_LEARNED_RADIUS"
+
+
+class LowRankElmanFunction(torch.autograd.Function):
+    """forward(x, z, h0, W_x, U, V, b, training) -> (output, h); the gradient of h is dropped
+    (elman/models/lowrank_elman.py:28-46)."""
+
+    @staticmethod
+    def forward(ctx, x, z, h0, W_x, U, V, b, training):
+        h, output, v = hasty_pytorch_lib.lowrank_elman_forward(training, x, z, h0, W_x, U, V, b)
+        ctx.save_for_backward(W_x, U, V, x, z, h, v)
+        return output, h
+
+    @staticmethod
+    def backward(ctx, grad_output, _grad_h):
+        W_x, U, V, x, z, h, v = ctx.saved_tensors
+        if v.numel() == 0:
+            raise RuntimeError("backward needs the pre-activations: run forward with training=True")
+        dx, dz, dW_x, dU, dV, db = hasty_pytorch_lib.lowrank_elman_backward(
+            W_x, U, V, x, z, h, v, grad_output.contiguous())
+        return dx, dz, None, dW_x, dU, dV, db, None
+
+
+class LowRankElmanCell(nn.Module):
+    """E4 cell: W_x [dim, dim], U [dim, rank], V [rank, dim], b; U V rescaled to the given
+    spectral radius by a three-step power iteration on the product, both factors taking the
+    square root of the scale (elman/models/lowrank_elman.py:49-108)."""
+
+    def __init__(self, dim, rank=64, spectral_radius=0.95):
+        super().__init__()
+        self.dim, self.rank, self.spectral_radius = dim, rank, spectral_radius
+        self.W_x = nn.Parameter(torch.empty(dim, dim))
+        self.U = nn.Parameter(torch.empty(dim, rank))
+        self.V = nn.Parameter(torch.empty(rank, dim))
+        self.b = nn.Parameter(torch.zeros(dim))
+        nn.init.xavier_uniform_(self.W_x)
+        nn.init.orthogonal_(self.U)
+        nn.init.orthogonal_(self.V)
+        with torch.no_grad():
+            self.U.mul_(0.3)
+            self.V.mul_(0.3)
+
+    def get_UV(self):
+        u = getattr(self, "_spectral_u", None)
+        if u is None or u.shape[0] != self.dim:
+            u = torch.randn(self.dim, device=self.U.device, dtype=self.U.dtype)
+            u = u / u.norm()
+        UV = self.U @ self.V
+        with torch.no_grad():
+            for _ in range(3):
+                v = UV.T @ u
+                v = v / (v.norm() + 1e-8)
+                u = UV @ v
+                u = u / (u.norm() + 1e-8)
+            self._spectral_u = u
+        sigma = (u @ UV @ v).abs()
+        scale = self.spectral_radius / (sigma + 1e-8)
+        return self.U * scale.sqrt(), self.V * scale.sqrt()
+
+    def forward(self, x, z, h0=None):
+        """x, z: [T, B, dim] -> (output [T, B, dim], h [T+1, B, dim])."""
+        T, B, D = x.shape
+        if not x.is_cuda:
+            raise RuntimeError("elman_b200 runs on CUDA tensors only (no CPU fallback)")
+        if h0 is None:
+            h0 = torch.zeros(B, D, device=x.device, dtype=x.dtype)
+        U, V = self.get_UV()
+        return LowRankElmanFunction.apply(x.contiguous(), z.contiguous(), h0.contiguous(),
+                                          self.W_x.contiguous(), U.contiguous(), V.contiguous(),
+                                          self.b.contiguous(), self.training)
+
+
+class LowRankElman(nn.Module):
+    """E4 layer: x, z = split(in_proj(x)); x = silu(x); cell; out_proj
+    (elman/models/lowrank_elman.py:163-254; rank defaults to dim / (2 expansion), floor 16)."""
+
+    def __init__(self, dim, expansion=1.0, rank=None, spectral_radius=0.95, dropout=0.0, **kwargs):
+        super().__init__()
+        self.dim = dim
+        self.d_inner = int(dim * expansion)
+        if rank is None:
+            rank = max(16, int(dim / (2 * expansion)))
+        self.rank = rank
+        self.in_proj = nn.Linear(dim, 2 * self.d_inner, bias=False)
+        self.cell = LowRankElmanCell(self.d_inner, rank=rank, spectral_radius=spectral_radius)
+        self.out_proj = nn.Linear(self.d_inner, dim, bias=False)
+        self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
+        nn.init.xavier_uniform_(self.in_proj.weight)
+        nn.init.xavier_uniform_(self.out_proj.weight)
+
+    def forward(self, x, h0=None, **kwargs):
+        """x: [B,T,dim] -> (output [B,T,dim], h_final [B,d_inner])."""
+        x_proj, z = self.in_proj(x).chunk(2, dim=-1)
+        x_rnn = F.silu(x_proj).permute(1, 0, 2).contiguous()
+        z_rnn = z.permute(1, 0, 2).contiguous()
+        cell_out, h_all = self.cell(x_rnn, z_rnn, h0)
+        y = self.dropout(cell_out.permute(1, 0, 2).contiguous())
+        out = fused_ops.linear(y, self.out_proj.weight) if fused_ops.library_handles(y) \
+            else self.out_proj(y)
+        return out, h_all[-1]
+
+    def extra_repr(self):
+        return f"dim={self.dim}, d_inner={self.d_inner}, rank={self.rank}, LEVEL=4"

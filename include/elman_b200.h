@@ -279,6 +279,26 @@ int elman_e1_hx_backward(int dtype, int T, int B, int d, const void* W_x, const 
                          size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * E4 — E1 with a low-rank recurrent matrix:
+ *   h_t = tanh(W_x x_t + U (V h_{t-1}) + b),  y_t = h_t * silu(z_t),  U [d, r], V [r, d].
+ * Replaces lowrank_elman_forward / lowrank_elman_backward
+ * (elman/cuda/pytorch/elman_ladder.cc:2665-2726, :2728-2800; module
+ * elman/models/lowrank_elman.py:28-46, :134-160).  The recurrence runs on the E5 kernels
+ * (rank-r intermediate on chip) with the dense projection of x as its input and z as
+ * the gate input; backward returns dx, dz, dW_x, dU, dV, db.
+ * ------------------------------------------------------------------------- */
+size_t elman_e4_forward_workspace(int dtype, int T, int B, int d, int r);
+int elman_e4_forward(int dtype, int training, int T, int B, int d, int r, const void* x,
+                     const void* z, const void* h0, const void* W_x, const void* U, const void* V,
+                     const void* b, void* h, void* output, void* v, void* workspace,
+                     size_t workspace_bytes, void* stream);
+size_t elman_e4_backward_workspace(int dtype, int T, int B, int d, int r);
+int elman_e4_backward(int dtype, int T, int B, int d, int r, const void* W_x, const void* U,
+                      const void* V, const void* x, const void* z, const void* h, const void* v,
+                      const void* d_output, void* dx, void* dz, void* dW_x, void* dU, void* dV,
+                      void* db, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
  * E33 — E1 with a self gate:  h_t as E1,  y_t = h_t * silu(h_t)  (no gate input).
  * Replaces e33_self_gate_forward / e33_self_gate_backward
  * (elman/cuda/pytorch/elman_ladder.cc:444-497, :499-557; module

@@ -254,6 +254,47 @@ def e33_backward(W_x: Tensor, W_h: Tensor, x: Tensor, h: Tensor, v: Tensor,
 
 
 # ----------------------------------------------------------------------------
+# E4: E1 with a low-rank recurrent matrix W_h = U V
+# (elman/models/lowrank_elman.py:134-160 of the reference, the Python time loop; the
+#  backward is the BPTT its CUDA pair lowrank_elman_forward/backward implements,
+#  elman_ladder.cc:2665-2800)
+# ----------------------------------------------------------------------------
+
+def e4_forward(x: Tensor, z: Tensor, h0: Tensor, W_x: Tensor, U: Tensor, V: Tensor,
+               b: Tensor) -> Dict[str, Tensor]:
+    T = x.shape[0]
+    h = [h0]
+    ys, vs = [], []
+    for t in range(T):
+        raw = x[t] @ W_x.T + (h[-1] @ V.T) @ U.T + b
+        hn = torch.tanh(raw)
+        h.append(hn)
+        vs.append(raw)
+        ys.append(hn * silu(z[t]))
+    return {"h": torch.stack(h), "output": torch.stack(ys), "v": torch.stack(vs)}
+
+
+def e4_backward(W_x: Tensor, U: Tensor, V: Tensor, x: Tensor, z: Tensor, h: Tensor, v: Tensor,
+                d_output: Tensor) -> Dict[str, Tensor]:
+    T, B, d = x.shape
+    dv_all = torch.zeros_like(x)
+    dz = torch.zeros_like(x)
+    dh_rec = torch.zeros(B, d, dtype=x.dtype)
+    for t in range(T - 1, -1, -1):
+        h_t = h[t + 1]
+        dz[t] = d_output[t] * h_t * dsilu(z[t])
+        dh = d_output[t] * silu(z[t]) + dh_rec
+        th = torch.tanh(v[t])
+        dv = dh * (1.0 - th * th)
+        dv_all[t] = dv
+        dh_rec = (dv @ U) @ V
+    dv2 = dv_all.reshape(T * B, d)
+    hp = h[:T].reshape(T * B, d)
+    return {"dx": (dv2 @ W_x).reshape(T, B, d), "dz": dz, "dW_x": dv2.T @ x.reshape(T * B, d),
+            "dU": dv2.T @ (hp @ V.T), "dV": (dv2 @ U).T @ hp, "db": dv2.sum(0)}
+
+
+# ----------------------------------------------------------------------------
 # E1 with the README's gate  y_t = h_t · silu(W_g [h_t ; x_t] + b_g)
 # (README.md:25-29 of the reference; no class in the reference implements it,
 #  so this one function is "parity unpinned" by reference code.)

@@ -186,6 +186,9 @@ def main():
             mod = load_ref(args.reference, name)
             inp, res = run_sibling_layer(mod, cls, 2, 8, 64, seed, **kw)
             save(name.split("_")[0] + "_layer", True, inp, res, [2, 8, 64, seed])
+        mod = load_ref(args.reference, "lowrank_elman")       # E4: rank 24 of 64
+        inp, res = run_sibling_layer(mod, "LowRankElman", 2, 8, 64, 64, rank=24)
+        save("e4_layer", True, inp, res, [2, 8, 64, 64])
         return
     if args.only_lm:
         inp, res = run_ladder_lm(args.reference, seed=51)
@@ -233,6 +236,9 @@ def main():
         mod = load_ref(args.reference, name)
         inp, res = run_sibling_layer(mod, cls, 2, 8, 64, seed, **kw)
         save(name.split("_")[0] + "_layer", True, inp, res, [2, 8, 64, seed])
+    mod = load_ref(args.reference, "lowrank_elman")
+    inp, res = run_sibling_layer(mod, "LowRankElman", 2, 8, 64, 64, rank=24)
+    save("e4_layer", True, inp, res, [2, 8, 64, 64])
 
 
 if __name__ == "__main__":

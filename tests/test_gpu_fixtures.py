@@ -152,7 +152,7 @@ def test_ladder_lm_on_gpu_matches_reference_fixture(golden_dir, chunks):
     torch.cuda.synchronize()
     assert _lib.launch_count() > before, "the CUDA library did not run"
     assert _lib.device_status()[0] == 0
-    assert abs(float(loss) - float(fix["out_loss"][0])) < 1e-4 * abs(float(fix["out_loss"][0]))
+    assert abs(loss.item() - float(fix["out_loss"][0])) < 1e-4 * abs(float(fix["out_loss"][0]))
     for k, p in model.named_parameters():
         want = torch.from_numpy(fix["out_g_" + k])
         assert orc.rel_err(p.grad.float().cpu(), want) < TOL, k
@@ -188,9 +188,10 @@ def test_ladder_lm_bf16_gradients_match_the_fp32_model(chunks):
 
 @pytest.mark.parametrize("name,cls,kw", [("e32_layer", "E32NoPresilu", {}),
                                          ("e33_layer", "E33SelfGate", {"r_h_mode": "spectral_norm"}),
-                                         ("e57_layer", "E57LearnedRadius", {"expansion": 1.0})])
+                                         ("e57_layer", "E57LearnedRadius", {"expansion": 1.0}),
+                                         ("e4_layer", "LowRankElman", {"rank": 24})])
 def test_sibling_layers_on_gpu_match_reference_fixtures(golden_dir, name, cls, kw):
-    """E32 / E33 / E57 on the GPU (fp32) against the fixtures of the reference's own files."""
+    """E4 / E32 / E33 / E57 on the GPU (fp32) against the fixtures of the reference's own files."""
     from elman_b200 import siblings
     inp, want = load(golden_dir, name)
     layer = getattr(siblings, cls)(inp["x"].shape[-1], **kw)
@@ -225,3 +226,34 @@ def test_e33_self_gate_bf16_tensor_core_path_matches_oracle(T, B, d):
     got = {"h": h, "output": out, "v": v, "dx": dx, "dW_x": dWx, "dW_h": dWh, "db": db}
     for k, w in {**f, **g}.items():
         assert orc.rel_err(got[k].float().cpu(), w) < 2e-2, k
+
+
+@pytest.mark.parametrize("T,B,d,r", [(12, 16, 256, 64), (20, 32, 512, 100), (64, 32, 1536, 270)])
+def test_e4_lowrank_bf16_tensor_core_path_matches_oracle(T, B, d, r):
+    """E4 (dense W_x, low-rank recurrent matrix, z as gate input) on the single-cluster low-rank
+    kernel, every output and gradient against the fp32 oracle; rank 100 and 270 are zero-padded."""
+    from elman_b200 import hasty_pytorch_lib as H
+    inp = orc.make_e1_inputs(T, B, d, seed=444 + d)
+    g = torch.Generator().manual_seed(d + r)
+    s = 0.8 * (d * r) ** -0.25
+    inp["U"], inp["V"] = s * torch.randn(d, r, generator=g), s * torch.randn(r, d, generator=g)
+    dev = {k: v.to(torch.bfloat16).cuda().contiguous() for k, v in inp.items()}
+    ref = {k: v.to(torch.bfloat16).float() for k, v in inp.items()}
+    before = _lib.tc_launch_count()
+    h, out, v = H.lowrank_elman_forward(True, dev["x"], dev["z"], dev["h0"], dev["W_x"], dev["U"],
+                                        dev["V"], dev["b"])
+    dx, dz, dWx, dU, dV, db = H.lowrank_elman_backward(dev["W_x"], dev["U"], dev["V"], dev["x"],
+                                                       dev["z"], h, v, dev["d_output"])
+    torch.cuda.synchronize()
+    assert _lib.tc_launch_count() >= before + 2 and _lib.device_status()[0] == 0
+    f = orc.e4_forward(ref["x"], ref["z"], ref["h0"], ref["W_x"], ref["U"], ref["V"], ref["b"])
+    gr = orc.e4_backward(ref["W_x"], ref["U"], ref["V"], ref["x"], ref["z"], f["h"], f["v"],
+                         ref["d_output"])
+    got = {"h": h, "output": out, "v": v, "dx": dx, "dz": dz, "dW_x": dWx, "dU": dU, "dV": dV, "db": db}
+    want = {**f, **gr}
+    for k, t in got.items():
+        assert orc.rel_err(t.float().cpu(), want[k]) < 2e-2, k   # bf16 tolerance, norm-wise
+    # inference mode: no pre-activations stored, same states and outputs
+    h2, out2, v2 = H.lowrank_elman_forward(False, dev["x"], dev["z"], dev["h0"], dev["W_x"],
+                                           dev["U"], dev["V"], dev["b"])
+    assert v2.numel() == 0 and torch.equal(h2, h) and torch.equal(out2, out)

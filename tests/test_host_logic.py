@@ -101,6 +101,16 @@ class OracleBackend:
         return [g["dx"], g["dW_x"], g["dW_h"], g["db"]]
 
     @staticmethod
+    def lowrank_elman_forward(training, x, z, h0, W_x, U, V, b):
+        o = orc.e4_forward(x, z, h0, W_x, U, V, b)
+        return [o["h"], o["output"], o["v"] if training else x.new_empty(0)]
+
+    @staticmethod
+    def lowrank_elman_backward(W_x, U, V, x, z, h, v, d_output):
+        g = orc.e4_backward(W_x, U, V, x, z, h, v, d_output)
+        return [g[k] for k in ("dx", "dz", "dW_x", "dU", "dV", "db")]
+
+    @staticmethod
     def stock_elman_forward(training, x, h0, W_x, W_h, W_gate, b, b_gate):
         o = orc.e0_forward(x, h0, W_x, W_h, W_gate, b, b_gate)
         e = x.new_empty(0)
@@ -394,9 +404,10 @@ def test_graphed_step_raises_when_the_status_word_reports_a_timeout(monkeypatch)
 
 @pytest.mark.parametrize("name,cls,kw", [("e32_layer", "E32NoPresilu", {}),
                                          ("e33_layer", "E33SelfGate", {"r_h_mode": "spectral_norm"}),
-                                         ("e57_layer", "E57LearnedRadius", {"expansion": 1.0})])
+                                         ("e57_layer", "E57LearnedRadius", {"expansion": 1.0}),
+                                         ("e4_layer", "LowRankElman", {"rank": 24})])
 def test_sibling_layers_against_reference_fixtures(golden_dir, oracle_backend, name, cls, kw):
-    """E32 / E33 / E57 (the reference's ladder levels that run on the E1 recurrence) against
+    """E4 / E32 / E33 / E57 (the reference's ladder levels that run on the E1 and E5 recurrences) against
     what the reference's own files computed: outputs, state, every parameter gradient."""
     from elman_b200 import siblings
     inp, want = load(golden_dir, name)
@@ -413,6 +424,19 @@ def test_sibling_layers_against_reference_fixtures(golden_dir, oracle_backend, n
     assert orc.rel_err(x.grad, want["dx"]) < 2e-5
     for k, p in layer.named_parameters():
         assert orc.rel_err(p.grad, want["g_" + k]) < 5e-5, k
+
+
+def test_oracle_e4_explicit_backward_equals_autograd():
+    inp = orc.make_e1_inputs(7, 3, 24, seed=5)
+    g0 = torch.Generator().manual_seed(6)
+    U, V = 0.3 * torch.randn(24, 5, generator=g0), 0.3 * torch.randn(5, 24, generator=g0)
+    f = orc.e4_forward(inp["x"], inp["z"], inp["h0"], inp["W_x"], U, V, inp["b"])
+    g = orc.e4_backward(inp["W_x"], U, V, inp["x"], inp["z"], f["h"], f["v"], inp["d_output"])
+    leaves = [t.clone().requires_grad_(True) for t in (inp["x"], inp["z"], inp["W_x"], U, V, inp["b"])]
+    o = orc.e4_forward(leaves[0], leaves[1], inp["h0"], *leaves[2:])
+    (o["output"] * inp["d_output"]).sum().backward()
+    for k, t in zip(("dx", "dz", "dW_x", "dU", "dV", "db"), leaves):
+        assert orc.rel_err(g[k], t.grad) < 1e-5, k
 
 
 def test_oracle_e33_explicit_backward_equals_autograd():

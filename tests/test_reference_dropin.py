@@ -68,6 +68,7 @@ def test_reference_model_files_find_the_extension_unchanged():
     # siblings that run on the same functions (E32, E57: the E1 pair; E33: its own pair)
     assert _load_reference("e32_no_presilu").MAMBA_CUDA_AVAILABLE is True
     assert _load_reference("e33_self_gate").E33_CUDA_AVAILABLE is True
+    assert _load_reference("lowrank_elman").HASTY_AVAILABLE is True       # E4
 
 
 @needs_reference
@@ -87,6 +88,14 @@ def test_reference_cells_on_cuda_match_their_own_cpu_fallback(dtype, tol):
     cases.append((m0.StockElmanCell(d, w_h_mode="free"), lambda cell, x: cell(x)))
     m5 = _load_reference("pure_lowrank_elman")
     cases.append((m5.PureLowRankElmanCell(d, rank=r), lambda cell, x: cell(x)))
+    m4 = _load_reference("lowrank_elman")
+    u0 = torch.randn(d)
+    u0 = u0 / u0.norm()
+
+    def call_e4(cell, x):    # its power iteration starts from a stored vector: pin it per pass
+        cell._spectral_u = u0.to(x.device, x.dtype)
+        return cell(x, x.flip(0) * 0.5)
+    cases.append((m4.LowRankElmanCell(d, rank=r), call_e4))
     for cell, call in cases:
         cell = cell.to(dtype)
         x_cpu = torch.randn(T, B, d).to(dtype)
