@@ -642,6 +642,66 @@ def lowrank_elman_backward(W_x, U, V, x, z, h, v, d_output):
     return [dx, dz, dW_x, dU, dV, db]
 
 
+def _e1h_dense_weight(W_h):
+    """[H, N, N] per-head weights, used as h_prev @ W_h[k] by the reference's einsum
+    'bhi,hij->bhj', as ONE block-diagonal [H N, H N] matrix in the W h convention of the dense
+    recurrence (block k = W_h[k] transposed)."""
+    return torch.block_diag(*W_h.transpose(1, 2).unbind(0)).contiguous()
+
+
+def e1h_forward(training, pre_x, z, h0, W_h, b_h):
+    """E1H, H independent heads of size N: h_t = tanh(pre_x_t + h_{t-1} W_h + b) per head,
+    y_t = h_t * silu(z_t).  pre_x, z: [T, B, H, N]; h0: [B, H, N]; W_h: [H, N, N]; b_h: [H, N]
+    -> [h_final [B,H,N], output [T,B,H,N], saved state for e1h_backward]; the reference's
+    e1h_forward (elman/cuda/pytorch/elman_ladder.cc:14610-14666; its kernel,
+    elman/cuda/lib/e1h_multihead_gpu.cu.cc, keeps every 16th state and recomputes).
+
+    Here the heads run as one dense recurrence with a block-diagonal weight on the tensor-core
+    recurrence kernel — the step is bound by its dependency chain, not by the multiplications, so
+    the zero blocks cost nothing that matters; the third return value holds all states and
+    pre-activations ([2T+1, B, H, N]) instead of checkpoints and is opaque to the caller, as
+    it is in the reference."""
+    fn = "e1h_forward"
+    _check_inputs(fn, pre_x, pre_x=pre_x, z=z, h0=h0, W_h=W_h, b_h=b_h)
+    if pre_x.dim() != 4:
+        raise RuntimeError(f"{fn}: pre_x must be [T, B, H, N]")
+    T, B, Hh, N = pre_x.shape
+    d = Hh * N
+    _shape(fn, z, (T, B, Hh, N), "z"); _shape(fn, h0, (B, Hh, N), "h0")
+    _shape(fn, W_h, (Hh, N, N), "W_h"); _shape(fn, b_h, (Hh, N), "b_h")
+    pre = (pre_x.reshape(T, B, d) + b_h.reshape(d)).contiguous()
+    h, out, v = e1_recurrence_forward(training, pre, z.reshape(T, B, d), h0.reshape(B, d),
+                                      _e1h_dense_weight(W_h))
+    saved = torch.cat([h, v]).reshape(2 * T + 1, B, Hh, N) if training else pre_x.new_empty(0)
+    return [h[T].reshape(B, Hh, N).clone(), out.reshape(T, B, Hh, N), saved]
+
+
+def e1h_backward(pre_x, z, W_h, b_h, saved, d_output):
+    """-> [d_pre_x [T,B,H,N], d_z [T,B,H,N], d_W_h [B,H,N,N] fp32, d_b [B,H,N] fp32]; the
+    reference's e1h_backward (:14668-14730).  The reference returns per-batch-row partial
+    weight gradients that its caller sums over the first axis; here the sums are formed on the
+    device by one GEMM and returned in row 0, the other rows are zero."""
+    fn = "e1h_backward"
+    _check_inputs(fn, pre_x, pre_x=pre_x, z=z, W_h=W_h, b_h=b_h, saved=saved, d_output=d_output)
+    T, B, Hh, N = pre_x.shape
+    d = Hh * N
+    _shape(fn, saved, (2 * T + 1, B, Hh, N), "saved"); _shape(fn, d_output, (T, B, Hh, N), "d_output")
+    flat = saved.reshape(2 * T + 1, B, d)
+    h, v = flat[:T + 1], flat[T + 1:]
+    dv, dz, db = e1_recurrence_backward(_e1h_dense_weight(W_h), z.reshape(T, B, d), h, v,
+                                        d_output.reshape(T, B, d).contiguous())
+    dvf = dv[:T].reshape(T * B, d)
+    dWd = gemm(GEMM_TN, dvf, h[:T].reshape(T * B, d))        # [d, d]: sum_t dv_t h_{t-1}^T
+    blocks = dWd.reshape(Hh, N, Hh, N)
+    idx = torch.arange(Hh, device=dWd.device)
+    dW = blocks[idx, :, idx, :].transpose(1, 2).float()       # per head, back to h_prev @ W form
+    dW_rows = torch.zeros(B, Hh, N, N, dtype=torch.float32, device=dWd.device)
+    db_rows = torch.zeros(B, Hh, N, dtype=torch.float32, device=dWd.device)
+    dW_rows[0] = dW
+    db_rows[0] = db.float().reshape(Hh, N)
+    return [dv[:T].reshape(T, B, Hh, N), dz.reshape(T, B, Hh, N), dW_rows, db_rows]
+
+
 def e33_self_gate_forward(training, x, h0, W_x, W_h, b):
     """y_t = h_t * silu(h_t) -> [h, output, v (empty if not training)]; the reference's
     e33_self_gate_forward (elman/cuda/pytorch/elman_ladder.cc:444-497)."""

@@ -1,5 +1,5 @@
 """Siblings of E1 that run on the same recurrence kernels — the reference's ladder levels
-4, 32, 33 and 57.  Class names, constructor arguments, parameter names and forward contracts
+4, 32, 33, 57 and the multi-head E1H.  Class names, constructor arguments, parameter names and forward contracts
 follow the reference files so that checkpoints and callers carry over:
 
   E32NoPresilu      E1 without the silu on the recurrence input
@@ -9,6 +9,8 @@ follow the reference files so that checkpoints and callers carry over:
                     (elman/models/e33_self_gate.py:30-50, :52-193, :196-296)
   LowRankElman      (E4) E1 whose recurrent matrix is U V, rank r; the recurrence runs on the
                     low-rank (E5) kernel (elman/models/lowrank_elman.py:28-46, :49-160, :163-254)
+  E1MultiHead       (E1H) H independent heads of size n_state, run as one block-diagonal
+                    recurrence (elman/models/e1_multihead.py:43-115, :118-283)
   E57LearnedRadius  E1 whose W_h is rescaled to a LEARNED spectral radius
                     sigmoid(log_radius) * max_radius (elman/models/e57_learned_radius.py:25-148,
                     :151-254; reuses the E1 autograd Function, :118-121)
@@ -332,3 +334,82 @@ class LowRankElman(nn.Module):
 
     def extra_repr(self):
         return f"dim={self.dim}, d_inner={self.d_inner}, rank={self.rank}, LEVEL=4"
+
+
+class E1HFunction(torch.autograd.Function):
+    """forward(training, pre_x [B,T,H,N], z, h0 [B,H,N], W_h [H,N,N], b_h [H,N]) -> (output
+    [B,T,H,N], h_final); the gradients of h0 and h_final are dropped
+    (elman/models/e1_multihead.py:43-115)."""
+
+    @staticmethod
+    def forward(ctx, training, pre_x, z, h0, W_h, b_h):
+        pre_x_t = pre_x.permute(1, 0, 2, 3).contiguous()
+        z_t = z.permute(1, 0, 2, 3).contiguous()
+        h_final, output_t, saved = hasty_pytorch_lib.e1h_forward(training, pre_x_t, z_t, h0, W_h, b_h)
+        ctx.save_for_backward(pre_x_t, z_t, W_h, b_h, saved)
+        return output_t.permute(1, 0, 2, 3).contiguous(), h_final
+
+    @staticmethod
+    def backward(ctx, d_output, _d_h_final):
+        pre_x_t, z_t, W_h, b_h, saved = ctx.saved_tensors
+        if saved.numel() == 0:
+            raise RuntimeError("backward needs the saved states: run forward with training=True")
+        d_pre, d_z, dW_rows, db_rows = hasty_pytorch_lib.e1h_backward(
+            pre_x_t, z_t, W_h, b_h, saved, d_output.permute(1, 0, 2, 3).contiguous())
+        return (None, d_pre.permute(1, 0, 2, 3).contiguous(), d_z.permute(1, 0, 2, 3).contiguous(),
+                None, dW_rows.sum(dim=0).to(W_h.dtype), db_rows.sum(dim=0).to(b_h.dtype))
+
+
+class E1MultiHead(nn.Module):
+    """E1H layer: x, z = split(in_proj(x)); x = silu(x); per-head W_x; H independent Elman
+    recurrences of size n_state with per-head W_h and b; gate silu(z); out_proj
+    (elman/models/e1_multihead.py:118-283).  Unlike the reference's kernel (bf16, training mode
+    only) the recurrence here runs for fp32 and bf16, training or not."""
+
+    def __init__(self, dim, n_heads=16, n_state=32, expansion=1.0, dropout=0.0, mamba2_init=False,
+                 **kwargs):
+        super().__init__()
+        self.dim, self.n_heads, self.n_state = dim, n_heads, n_state
+        self.d_inner = n_heads * n_state
+        self.in_proj = nn.Linear(dim, 2 * self.d_inner, bias=False)
+        self.W_x = nn.Parameter(torch.empty(n_heads, n_state, n_state))
+        self.W_h = nn.Parameter(torch.empty(n_heads, n_state, n_state))
+        self.b = nn.Parameter(torch.zeros(n_heads, n_state))
+        self.out_proj = nn.Linear(self.d_inner, dim, bias=False)
+        self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
+        if mamba2_init:
+            nn.init.normal_(self.in_proj.weight, std=0.02)
+            nn.init.normal_(self.out_proj.weight, std=0.02)
+            nn.init.normal_(self.W_x, std=0.02)
+        else:
+            nn.init.xavier_uniform_(self.in_proj.weight)
+            nn.init.xavier_uniform_(self.out_proj.weight)
+        with torch.no_grad():
+            for k in range(n_heads):
+                w = torch.empty(n_state, n_state, dtype=torch.float32)
+                nn.init.orthogonal_(w)
+                self.W_h.data[k].copy_(w * (0.999 if mamba2_init else 0.9))
+                if not mamba2_init:
+                    nn.init.xavier_uniform_(self.W_x.data[k])
+
+    def forward(self, x, h0=None, **kwargs):
+        """x: [B,T,dim] -> (output [B,T,dim], h_final [B,H,n_state])."""
+        B, T, D = x.shape
+        Hh, N = self.n_heads, self.n_state
+        if not x.is_cuda:
+            raise RuntimeError("elman_b200 runs on CUDA tensors only (no CPU fallback)")
+        x_proj, z = self.in_proj(x).chunk(2, dim=-1)
+        x_proj = F.silu(x_proj).view(B, T, Hh, N)
+        pre_x = torch.einsum("bthi,hij->bthj", x_proj, self.W_x)
+        if h0 is None:
+            h0 = torch.zeros(B, Hh, N, device=x.device, dtype=x.dtype)
+        out, h_final = E1HFunction.apply(self.training, pre_x, z.reshape(B, T, Hh, N).contiguous(),
+                                         h0.contiguous(), self.W_h, self.b)
+        y = self.dropout(out.reshape(B, T, self.d_inner))
+        proj = fused_ops.linear(y, self.out_proj.weight) if fused_ops.library_handles(y) \
+            else self.out_proj(y)
+        return proj, h_final
+
+    def extra_repr(self):
+        return (f"dim={self.dim}, n_heads={self.n_heads}, n_state={self.n_state}, "
+                f"d_inner={self.d_inner}, LEVEL=E1H_MULTIHEAD")

@@ -295,6 +295,44 @@ def e4_backward(W_x: Tensor, U: Tensor, V: Tensor, x: Tensor, z: Tensor, h: Tens
 
 
 # ----------------------------------------------------------------------------
+# E1H: H independent heads of size N (elman/models/e1_multihead.py:204-211 of the reference,
+# the Python time loop: wh = einsum('bhi,hij->bhj', h_prev, W_h); the backward is the BPTT of
+# its CUDA pair e1h_forward/backward, elman_ladder.cc:14610-14730)
+# ----------------------------------------------------------------------------
+
+def e1h_forward(pre_x: Tensor, z: Tensor, h0: Tensor, W_h: Tensor, b: Tensor) -> Dict[str, Tensor]:
+    """pre_x, z: [T,B,H,N]; h0: [B,H,N]; W_h: [H,N,N]; b: [H,N]."""
+    T = pre_x.shape[0]
+    h = [h0]
+    ys, vs = [], []
+    for t in range(T):
+        raw = pre_x[t] + torch.einsum("bhi,hij->bhj", h[-1], W_h) + b
+        hn = torch.tanh(raw)
+        h.append(hn)
+        vs.append(raw)
+        ys.append(hn * silu(z[t]))
+    return {"h": torch.stack(h), "output": torch.stack(ys), "v": torch.stack(vs)}
+
+
+def e1h_backward(z: Tensor, W_h: Tensor, h: Tensor, v: Tensor, d_output: Tensor) -> Dict[str, Tensor]:
+    T = z.shape[0]
+    d_pre = torch.zeros_like(z)
+    dz = torch.zeros_like(z)
+    dh_rec = torch.zeros_like(h[0])
+    dW = torch.zeros_like(W_h)
+    for t in range(T - 1, -1, -1):
+        h_t = h[t + 1]
+        dz[t] = d_output[t] * h_t * dsilu(z[t])
+        dh = d_output[t] * silu(z[t]) + dh_rec
+        th = torch.tanh(v[t])
+        dv = dh * (1.0 - th * th)
+        d_pre[t] = dv
+        dW += torch.einsum("bhi,bhj->hij", h[t], dv)
+        dh_rec = torch.einsum("bhj,hij->bhi", dv, W_h)
+    return {"d_pre_x": d_pre, "dz": dz, "dW_h": dW, "db": d_pre.sum((0, 1))}
+
+
+# ----------------------------------------------------------------------------
 # E1 with the README's gate  y_t = h_t · silu(W_g [h_t ; x_t] + b_g)
 # (README.md:25-29 of the reference; no class in the reference implements it,
 #  so this one function is "parity unpinned" by reference code.)

@@ -148,6 +148,24 @@ def run_sibling_layer(mod, cls_name, B, T, dim, seed, **kw):
     return inp, res
 
 
+def run_e1h_layer(mod, B, T, dim, seed, **kw):
+    """The reference's multi-head E1 layer (elman/models/e1_multihead.py) through its own
+    PyTorch loop (`_forward_pytorch`, the path it takes off CUDA), default init."""
+    torch.manual_seed(seed)
+    layer = mod.E1MultiHead(dim, **kw)
+    g = torch.Generator().manual_seed(seed + 1)
+    x = torch.randn(B, T, dim, generator=g)
+    r = torch.randn(B, T, dim, generator=g)
+    inp = {"x": x, "d_output": r}
+    inp.update({"p_" + k: v.detach().clone() for k, v in layer.state_dict().items()})
+    xin = x.clone().requires_grad_(True)
+    out, h_final = layer(xin)
+    (out * r).sum().backward()
+    res = {"output": out, "h_final": h_final, "dx": xin.grad}
+    res.update({"g_" + k: p.grad for k, p in layer.named_parameters()})
+    return inp, res
+
+
 def run_ladder_lm(reference_root, seed):
     """The reference's LadderLM (level 1, spectral-norm W_h as it defaults to) on seeded
     token ids: loss and every parameter gradient.  Importing it pulls in the whole
@@ -189,6 +207,9 @@ def main():
         mod = load_ref(args.reference, "lowrank_elman")       # E4: rank 24 of 64
         inp, res = run_sibling_layer(mod, "LowRankElman", 2, 8, 64, 64, rank=24)
         save("e4_layer", True, inp, res, [2, 8, 64, 64])
+        mod = load_ref(args.reference, "e1_multihead")        # E1H: 4 heads of 16
+        inp, res = run_e1h_layer(mod, 2, 8, 64, 65, n_heads=4, n_state=16)
+        save("e1h_layer", True, inp, res, [2, 8, 64, 65])
         return
     if args.only_lm:
         inp, res = run_ladder_lm(args.reference, seed=51)
@@ -239,6 +260,9 @@ def main():
     mod = load_ref(args.reference, "lowrank_elman")
     inp, res = run_sibling_layer(mod, "LowRankElman", 2, 8, 64, 64, rank=24)
     save("e4_layer", True, inp, res, [2, 8, 64, 64])
+    mod = load_ref(args.reference, "e1_multihead")
+    inp, res = run_e1h_layer(mod, 2, 8, 64, 65, n_heads=4, n_state=16)
+    save("e1h_layer", True, inp, res, [2, 8, 64, 65])
 
 
 if __name__ == "__main__":

@@ -257,3 +257,46 @@ def test_e4_lowrank_bf16_tensor_core_path_matches_oracle(T, B, d, r):
     h2, out2, v2 = H.lowrank_elman_forward(False, dev["x"], dev["z"], dev["h0"], dev["W_x"],
                                            dev["U"], dev["V"], dev["b"])
     assert v2.numel() == 0 and torch.equal(h2, h) and torch.equal(out2, out)
+
+
+def test_e1h_layer_on_gpu_matches_reference_fixture(golden_dir):
+    """The multi-head E1 layer on the GPU (fp32) against the fixture of the reference's own file."""
+    from elman_b200 import siblings
+    inp, want = load(golden_dir, "e1h_layer")
+    layer = siblings.E1MultiHead(64, n_heads=4, n_state=16)
+    layer.load_state_dict({k[2:]: v for k, v in inp.items() if k.startswith("p_")})
+    layer = layer.cuda()
+    x = inp["x"].cuda().requires_grad_(True)
+    before = _lib.launch_count()
+    out, h_final = layer(x)
+    (out * inp["d_output"].cuda()).sum().backward()
+    torch.cuda.synchronize()
+    assert _lib.launch_count() > before
+    got = {"output": out, "h_final": h_final, "dx": x.grad}
+    for k, p in layer.named_parameters():
+        got["g_" + k] = p.grad
+    check(got, want, "e1h_layer")
+
+
+@pytest.mark.parametrize("T,B,Hh,N", [(16, 32, 16, 32), (12, 8, 8, 64), (40, 32, 40, 32)])
+def test_e1h_bf16_tensor_core_path_matches_oracle(T, B, Hh, N):
+    """H independent heads as one block-diagonal recurrence on the tcgen05 kernel (d = H N = 512,
+    512, 1280), forward and backward against the per-head fp32 oracle."""
+    from elman_b200 import hasty_pytorch_lib as H
+    g = torch.Generator().manual_seed(Hh * N + T)
+    mk = lambda *shape, s=1.0: (s * torch.randn(*shape, generator=g)).to(torch.bfloat16)
+    px, z, dy = mk(T, B, Hh, N, s=0.7), mk(T, B, Hh, N), mk(T, B, Hh, N)
+    h0, W, b = mk(B, Hh, N, s=0.1), mk(Hh, N, N, s=0.9 * N ** -0.5), mk(Hh, N, s=0.1)
+    dev = [t.cuda() for t in (px, z, h0, W, b, dy)]
+    before = _lib.tc_launch_count()
+    h_final, out, saved = H.e1h_forward(True, dev[0], dev[1], dev[2], dev[3], dev[4])
+    d_pre, dz, dW_rows, db_rows = H.e1h_backward(dev[0], dev[1], dev[3], dev[4], saved, dev[5])
+    torch.cuda.synchronize()
+    assert _lib.tc_launch_count() >= before + 2 and _lib.device_status()[0] == 0
+    f = orc.e1h_forward(px.float(), z.float(), h0.float(), W.float(), b.float())
+    gr = orc.e1h_backward(z.float(), W.float(), f["h"], f["v"], dy.float())
+    got = {"h_final": h_final, "output": out, "d_pre_x": d_pre, "dz": dz,
+           "dW_h": dW_rows.sum(0), "db": db_rows.sum(0)}
+    want = {"h_final": f["h"][T], "output": f["output"], **gr}
+    for k, t in got.items():
+        assert orc.rel_err(t.float().cpu(), want[k]) < 2e-2, k   # bf16 tolerance, norm-wise

@@ -101,6 +101,21 @@ class OracleBackend:
         return [g["dx"], g["dW_x"], g["dW_h"], g["db"]]
 
     @staticmethod
+    def e1h_forward(training, pre_x, z, h0, W_h, b_h):
+        o = orc.e1h_forward(pre_x, z, h0, W_h, b_h)
+        T = pre_x.shape[0]
+        saved = torch.cat([o["h"], o["v"]]) if training else pre_x.new_empty(0)
+        return [o["h"][T].clone(), o["output"], saved]
+
+    @staticmethod
+    def e1h_backward(pre_x, z, W_h, b_h, saved, d_output):
+        T, B = pre_x.shape[:2]
+        g = orc.e1h_backward(z, W_h, saved[:T + 1], saved[T + 1:], d_output)
+        dW = torch.zeros((B,) + tuple(W_h.shape)); db = torch.zeros((B,) + tuple(b_h.shape))
+        dW[0], db[0] = g["dW_h"], g["db"]
+        return [g["d_pre_x"], g["dz"], dW, db]
+
+    @staticmethod
     def lowrank_elman_forward(training, x, z, h0, W_x, U, V, b):
         o = orc.e4_forward(x, z, h0, W_x, U, V, b)
         return [o["h"], o["output"], o["v"] if training else x.new_empty(0)]
@@ -424,6 +439,40 @@ def test_sibling_layers_against_reference_fixtures(golden_dir, oracle_backend, n
     assert orc.rel_err(x.grad, want["dx"]) < 2e-5
     for k, p in layer.named_parameters():
         assert orc.rel_err(p.grad, want["g_" + k]) < 5e-5, k
+
+
+def test_e1h_layer_against_reference_fixture(golden_dir, oracle_backend):
+    """The multi-head E1 layer against what the reference's own file computed (its PyTorch
+    loop): output, final state, every parameter gradient; same parameter names."""
+    from elman_b200 import siblings
+    inp, want = load(golden_dir, "e1h_layer")
+    layer = siblings.E1MultiHead(64, n_heads=4, n_state=16)
+    sd = {k[2:]: v for k, v in inp.items() if k.startswith("p_")}
+    assert set(sd) == set(layer.state_dict()), "parameter names differ from the reference's"
+    layer.load_state_dict(sd)
+    x = as_fake_cuda(inp["x"].clone()).requires_grad_(True)
+    out, h_final = layer(x)
+    (out * inp["d_output"]).sum().backward()
+    assert orc.rel_err(out, want["output"]) < 2e-5
+    assert orc.rel_err(h_final, want["h_final"]) < 2e-5
+    assert orc.rel_err(x.grad, want["dx"]) < 2e-5
+    for k, p in layer.named_parameters():
+        assert orc.rel_err(p.grad, want["g_" + k]) < 5e-5, k
+
+
+def test_oracle_e1h_explicit_backward_equals_autograd():
+    g0 = torch.Generator().manual_seed(8)
+    T, B, Hh, N = 6, 3, 4, 8
+    px, z, dy = (torch.randn(T, B, Hh, N, generator=g0) for _ in range(3))
+    h0 = 0.1 * torch.randn(B, Hh, N, generator=g0)
+    W, b = 0.3 * torch.randn(Hh, N, N, generator=g0), 0.1 * torch.randn(Hh, N, generator=g0)
+    f = orc.e1h_forward(px, z, h0, W, b)
+    g = orc.e1h_backward(z, W, f["h"], f["v"], dy)
+    leaves = [t.clone().requires_grad_(True) for t in (px, z, W, b)]
+    o = orc.e1h_forward(leaves[0], leaves[1], h0, leaves[2], leaves[3])
+    (o["output"] * dy).sum().backward()
+    for k, t in zip(("d_pre_x", "dz", "dW_h", "db"), leaves):
+        assert orc.rel_err(g[k], t.grad) < 1e-5, k
 
 
 def test_oracle_e4_explicit_backward_equals_autograd():

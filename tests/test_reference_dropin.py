@@ -69,6 +69,7 @@ def test_reference_model_files_find_the_extension_unchanged():
     assert _load_reference("e32_no_presilu").MAMBA_CUDA_AVAILABLE is True
     assert _load_reference("e33_self_gate").E33_CUDA_AVAILABLE is True
     assert _load_reference("lowrank_elman").HASTY_AVAILABLE is True       # E4
+    assert _load_reference("e1_multihead").HAS_CUDA is True               # E1H
 
 
 @needs_reference
