@@ -23,6 +23,7 @@ _P = _c.c_void_p
 _I = _c.c_int
 _Z = _c.c_size_t
 _L = _c.c_long
+_F = _c.c_float
 
 # name -> (restype, argtypes); must list every function the header declares
 SIGNATURES = {
@@ -71,6 +72,8 @@ SIGNATURES = {
     "elman_e1_hx_forward": (_I, [_I, _I, _I, _I, _I] + [_P] * 7 + [_P] * 4 + [_P, _Z, _P]),
     "elman_e1_hx_backward_workspace": (_Z, [_I, _I, _I, _I]),
     "elman_e1_hx_backward": (_I, [_I, _I, _I, _I] + [_P] * 8 + [_P] * 6 + [_P, _Z, _P]),
+    "elman_spectral_norm_forward": (_I, [_I, _I, _P, _P, _P, _P, _P, _F, _F, _I, _P]),
+    "elman_spectral_norm_backward": (_I, [_I, _I, _P, _P, _P, _P, _P, _P, _I, _F, _F, _P]),
     "elman_e4_forward_workspace": (_Z, [_I, _I, _I, _I, _I]),
     "elman_e4_forward": (_I, [_I, _I, _I, _I, _I, _I] + [_P] * 7 + [_P] * 3 + [_P, _Z, _P]),
     "elman_e4_backward_workspace": (_Z, [_I, _I, _I, _I, _I]),

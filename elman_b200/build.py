@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libelman_b200.so")
-SOURCES = ["api.cu", "gemm_simt.cu", "gemm_tc.cu", "rec_simt.cu", "rec_tc.cu", "lowrank_tc.cu", "extras.cu", "layer_ops.cu", "train_ops.cu"]
+SOURCES = ["api.cu", "gemm_simt.cu", "gemm_tc.cu", "rec_simt.cu", "rec_tc.cu", "lowrank_tc.cu", "extras.cu", "layer_ops.cu", "train_ops.cu", "spectral.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

@@ -1393,6 +1393,31 @@ size_t elman_add_rmsnorm_backward_workspace(int D) {
   return add_rmsnorm_bwd_scratch_bytes(D < 0 ? 0 : D);
 }
 
+int elman_spectral_norm_forward(int dtype, int d, const void* W, void* u, float* v, float* sigma,
+                                void* W_eff, float target_radius, float eps, int iterations,
+                                void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(d >= 0 && iterations >= 1, "bad size or iteration count");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (d == 0) return ELMAN_OK;
+  REQUIRE_PTR(W); REQUIRE_PTR(u); REQUIRE_PTR(v); REQUIRE_PTR(sigma); REQUIRE_PTR(W_eff);
+  return spectral_norm_fwd(dtype, d, W, u, v, sigma, W_eff, target_radius, eps, iterations,
+                           (cudaStream_t)stream);
+}
+
+int elman_spectral_norm_backward(int dtype, int d, const void* W, const void* u, const float* v,
+                                 const float* sigma, const void* dW_eff, void* dW, int accumulate,
+                                 float target_radius, float eps, void* stream) {
+  ELMAN_ARG_CHECK(dtype == ELMAN_F32 || dtype == ELMAN_BF16, "unknown dtype %d", dtype);
+  ELMAN_ARG_CHECK(d >= 0, "negative size");
+  ELMAN_RETURN_IF(check_status_on_entry());
+  if (d == 0) return ELMAN_OK;
+  REQUIRE_PTR(W); REQUIRE_PTR(u); REQUIRE_PTR(v); REQUIRE_PTR(sigma); REQUIRE_PTR(dW_eff);
+  REQUIRE_PTR(dW);
+  return spectral_norm_bwd(dtype, d, W, u, v, sigma, dW_eff, dW, accumulate, target_radius, eps,
+                           (cudaStream_t)stream);
+}
+
 int elman_add_rmsnorm_forward(int dtype, long M, int D, const void* x, const float* residual_in,
                               const void* weight, float eps, float* residual_out, void* y,
                               float* rstd, void* stream) {

@@ -275,4 +275,12 @@ int lowrank_tc_blocks(int T, int B, int d, int r);   // resident blocks (one clu
 void lowrank_tc_pad_bytes(int d, int r, size_t* up_bytes, size_t* vp_bytes);
 int lowrank_tc(const LowRankTcArgs& a, cudaStream_t stream);
 
+// Spectral normalisation of a [d, d] matrix (csrc/spectral.cu): three power-iteration steps
+// from u (advanced in place), v and sigma saved for the backward pass.
+int spectral_norm_fwd(int dtype, int d, const void* W, void* u, float* v, float* sigma, void* W_eff,
+                      float target, float eps, int iters, cudaStream_t st);
+int spectral_norm_bwd(int dtype, int d, const void* W, const void* u, const float* v,
+                      const float* sigma, const void* G, void* dW, int accumulate, float target,
+                      float eps, cudaStream_t st);
+
 }  // namespace elman

@@ -447,6 +447,51 @@ def projection(A, W, bias=None, out=None, accumulate=False):
 
 # ------------------------------ layer ops around the cell (extensions of the C ABI)
 
+def spectral_norm_forward(W, u, target_radius, eps, iterations):
+    """Power iteration from u (advanced in place) and rescaling of W in one kernel
+    -> (W_eff like W, v fp32 [d], sigma fp32 [1]) through elman_spectral_norm_forward."""
+    fn = "spectral_norm_forward"
+    dt = _check_inputs(fn, W, W=W, u=u)
+    if W.dim() != 2 or W.shape[0] != W.shape[1]:
+        raise RuntimeError(f"{fn}: W must be square")
+    d = W.shape[0]
+    _shape(fn, u, (d,), "u")
+    with torch.cuda.device(W.device):
+        W_eff = torch.empty_like(W)
+        v = torch.empty(d, dtype=torch.float32, device=W.device)
+        sigma = torch.empty(1, dtype=torch.float32, device=W.device)
+        rc = _lib.load().elman_spectral_norm_forward(dt, d, _ptr(W), _ptr(u), _ptr(v), _ptr(sigma),
+                                                     _ptr(W_eff), float(target_radius), float(eps),
+                                                     int(iterations), _stream(W.device))
+        _lib.check(rc, fn)
+    return W_eff, v, sigma
+
+
+def spectral_norm_backward(W, u, v, sigma, dW_eff, target_radius, eps, out=None):
+    """Gradient of W from the gradient of W_eff (u, v constant) -> dW like W; with `out` the
+    result is ADDED into it."""
+    fn = "spectral_norm_backward"
+    dt = _check_inputs(fn, W, W=W, u=u, dW_eff=dW_eff)
+    d = W.shape[0]
+    _shape(fn, dW_eff, (d, d), "dW_eff"); _shape(fn, u, (d,), "u")
+    for name, t, n in (("v", v, d), ("sigma", sigma, 1)):
+        if t.dtype != torch.float32 or t.numel() != n or t.device != W.device or not t.is_contiguous():
+            raise RuntimeError(f"{fn}: {name} must be a contiguous float32 tensor of {n} elements")
+    with torch.cuda.device(W.device):
+        accumulate = out is not None
+        if out is None:
+            out = torch.empty_like(W)
+        else:
+            _check_inputs(fn, W, out=out)
+            _shape(fn, out, (d, d), "out")
+        rc = _lib.load().elman_spectral_norm_backward(dt, d, _ptr(W), _ptr(u), _ptr(v), _ptr(sigma),
+                                                      _ptr(dW_eff), _ptr(out), 1 if accumulate else 0,
+                                                      float(target_radius), float(eps),
+                                                      _stream(W.device))
+        _lib.check(rc, fn)
+    return out
+
+
 def add_rmsnorm_forward(x, residual_in, weight, eps):
     """x [..., D] (+ residual_in fp32, or None) -> (y like x, residual_out fp32, rstd fp32 [rows])
     through elman_add_rmsnorm_forward."""

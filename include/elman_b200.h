@@ -446,6 +446,24 @@ int elman_e1_recurrence_backward(int dtype, int flags, int T, int B, int d,
                                  void* dv, void* dz, void* db,
                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Spectral normalisation of a recurrent matrix, one kernel per direction (replaces the
+ * reference cells' get_W_h, elman/models/mamba_gated_elman.py:123-146 and
+ * elman/models/stock_elman.py:104-125, a dozen framework ops per layer and step):
+ * `iterations` power-iteration steps from u [d] (same dtype as W, advanced in place),
+ *   v = W^T u / (|W^T u| + eps),  u = W v / (|W v| + eps),
+ * sigma = |u^T W v|, W_eff = W * target_radius / (sigma + eps).  v [d] and sigma [1] (fp32) are
+ * kept for the backward pass:  dW (+)= s dW_eff - <dW_eff, W> target_radius / (sigma + eps)^2 u v^T
+ * with s = target_radius / (sigma + eps)  (u and v held constant, as in the reference, which
+ * runs the iteration under no_grad).  One thread-block cluster per matrix; fp32 arithmetic.
+ */
+int elman_spectral_norm_forward(int dtype, int d, const void* W, void* u, float* v, float* sigma,
+                                void* W_eff, float target_radius, float eps, int iterations,
+                                void* stream);
+int elman_spectral_norm_backward(int dtype, int d, const void* W, const void* u, const float* v,
+                                 const float* sigma, const void* dW_eff, void* dW, int accumulate,
+                                 float target_radius, float eps, void* stream);
+
 /* ---------------------------------------------------------------------------
  * The time-parallel ops of the layer and the model around the cell (the callers of the
  * hot path), one kernel per pass.

@@ -124,3 +124,43 @@ def test_silu_backward_concat_matches_pytorch(dtype, M, d):
     s = torch.sigmoid(xr.float())
     want = torch.cat([da.float() * s * (1 + xr.float() * (1 - s)), dz.float()], dim=1)
     assert rel(got, want) < (1e-6 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("d", [7, 32, 50, 72, 256, 1280])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 1.5e-2)])
+def test_spectral_norm_kernel_matches_the_framework_ops(d, dtype, tol):
+    """elman_spectral_norm_forward/backward (one cluster kernel per direction) against the same
+    steps as framework ops in fp32: the rescaled matrix, the advanced vector u, and the
+    gradient of W through sigma = |u^T W v| with u, v constant."""
+    from elman_b200 import _spectral
+    from oracle.elman_oracle import rel_err
+    g = torch.Generator().manual_seed(d)
+    W = (torch.randn(d, d, generator=g) * d ** -0.5).to(dtype)
+    u0 = torch.randn(d, generator=g)
+    u0 = (u0 / u0.norm()).to(dtype)
+    G = torch.randn(d, d, generator=g).to(dtype)
+
+    class Holder:
+        pass
+    ref, got = Holder(), Holder()
+    ref._spectral_u = u0.float().clone()
+    Wr = W.float().clone().requires_grad_(True)
+    old = _spectral.FUSED
+    _spectral.FUSED = False
+    try:
+        We_ref = _spectral.spectrally_normalised(ref, Wr)
+    finally:
+        _spectral.FUSED = old
+    (We_ref * G.float()).sum().backward()
+
+    got._spectral_u = u0.clone().cuda()
+    Wg = W.clone().cuda().requires_grad_(True)
+    before = _lib.launch_count()
+    We = _spectral.spectrally_normalised(got, Wg)
+    (We.float() * G.cuda().float()).sum().backward()
+    torch.cuda.synchronize()
+    assert _lib.launch_count() - before == 2, "one kernel forward, one backward"
+    assert _lib.device_status()[0] == 0
+    assert rel_err(We.float().cpu(), We_ref.detach()) < tol
+    assert rel_err(got._spectral_u.float().cpu(), ref._spectral_u) < tol
+    assert rel_err(Wg.grad.float().cpu(), Wr.grad) < tol
