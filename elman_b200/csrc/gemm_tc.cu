@@ -66,6 +66,8 @@ struct GemmParams {
   const void* aux = nullptr;
   int stall_step = -1;        // test hook: block 0 arms a stage at this K iteration but loads nothing
   int ksplit = 1;             // persistent kernel: K range cut into this many work items per tile
+  int c_tma = 0;              // pair kernel: plain bf16 output leaves through shared memory and
+                              // bulk tensor stores (a third tensor map describes C)
   float* partial = nullptr;   // [ksplit][M][N] fp32 partial sums when ksplit > 1
 };
 
@@ -207,7 +209,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int gm, int gn0
 
 __global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               GemmParams p) {
+               const __grid_constant__ CUtensorMap tmC, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -323,9 +325,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t r[32];
       ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c * 32), r);
       ptx::tmem_ld_wait();
-      store_chunk(p, gm, n0 + c * 32, r, vec_ok,
-                  p.bias != nullptr ? p.bias + n0 + c * 32 : nullptr);
+      if (p.c_tma) {
+        // plain bf16 output: through shared memory (the operand ring is idle now that every MMA
+        // has retired: one 4 KB box per warp and column pair of chunks) and bulk tensor stores
+        uint8_t* buf = smem + (warp * 2 + (c >> 1)) * 4096;
+        const uint32_t row_a = ptx::smem_u32(buf) + (uint32_t)(lane * 128);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float f[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[8 * j + q]);
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int n = n0 + c * 32 + 8 * j + q;
+              if (n < p.N) f[q] += __bfloat162float(p.bias[n]);
+            }
+          }
+          const uint32_t piece = (uint32_t)((c & 1) * 4 + j) ^ (uint32_t)(lane & 7);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_a + (piece << 4)),
+                       "r"(pack_bf16(f[0], f[1])), "r"(pack_bf16(f[2], f[3])),
+                       "r"(pack_bf16(f[4], f[5])), "r"(pack_bf16(f[6], f[7]))
+                       : "memory");
+        }
+        if (c & 1) {
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tch::tma_store_2d(&tmC, buf, n0 + (c - 1) * 32, m0 + warp * 32);
+            tch::bulk_commit();
+          }
+        }
+      } else {
+        store_chunk(p, gm, n0 + c * 32, r, vec_ok,
+                    p.bias != nullptr ? p.bias + n0 + c * 32 : nullptr);
+      }
     }
+    if (p.c_tma && lane == 0) tch::bulk_wait_read_all();   // before the shared memory goes away
   } else {
     // Give copies that may still be in flight time to land before the CTA's
     // shared memory and tensor memory are released.
@@ -573,12 +609,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 constexpr int Q_BM = 256, Q_BN = 256;             // tile of the pair
 constexpr int Q_A_BYTES = 128 * BK * 2, Q_B_BYTES = 128 * BK * 2;   // per CTA and stage
 constexpr int Q_STAGE_BYTES = Q_A_BYTES + Q_B_BYTES;
-template <int STAGES> constexpr int pair_smem_bytes() { return STAGES * Q_STAGE_BYTES + 1024; }
+constexpr int Q_STORE_BYTES = 32 * 128;           // per epilogue warp: 32 rows x 64 bf16, swizzled
+template <int STAGES> constexpr int pair_smem_bytes() {
+  return STAGES * Q_STAGE_BYTES + P_EPI_WARPS * Q_STORE_BYTES + 1024;
+}
 
 template <int STAGES, int ACC_BUFS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
-                    const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];    // used in the even CTA only
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -594,6 +634,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * Q_A_BYTES;
+  uint8_t* sStore = smem + STAGES * Q_STAGE_BYTES;   // one staging buffer per epilogue warp
   const int nk = (p.K + BK - 1) / BK;
   const int tiles_n = (p.N + Q_BN - 1) / Q_BN;
   const int tiles = ((p.M + Q_BM - 1) / Q_BM) * tiles_n;
@@ -762,7 +803,46 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         ptx::tmem_ld_wait();
         if (c + 1 < CH) ptx::tmem_ld32(tsrc + (uint32_t)((c + 1) * 32), r[(c + 1) & 1]);
         const int col = half * (Q_BN / 2) + c * 32;
-        if (p.ksplit == 1) {
+        if (p.c_tma) {
+          // bias, rounding, then this thread's 64 bytes of the row into the warp's staging
+          // buffer in the 128-byte-swizzled layout of a [32 rows x 64 columns] box; every second
+          // chunk completes a box, which one lane hands to a bulk tensor store (clipped at the
+          // edges of C by the hardware).  The global writes are whole 128-byte rows this way.
+          uint8_t* buf = sStore + (warp - 2) * Q_STORE_BYTES;
+          if ((c & 1) == 0) {   // the previous box must have been read out of the buffer
+            if (lane == 0) tch::bulk_wait_read_all();
+            __syncwarp();
+          }
+          const uint32_t row_a = ptx::smem_u32(buf) + (uint32_t)(lane * 128);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float f[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[c & 1][8 * j + q]);
+            if (p.bias != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 8; q += 2) {
+                const float2 b2 = __bfloat1622float2(
+                    *reinterpret_cast<const __nv_bfloat162*>(&s_bias[b][col + 8 * j + q]));
+                f[q] += b2.x;
+                f[q + 1] += b2.y;
+              }
+            }
+            const uint32_t piece = (uint32_t)((c & 1) * 4 + j) ^ (uint32_t)(lane & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_a + (piece << 4)),
+                         "r"(pack_bf16(f[0], f[1])), "r"(pack_bf16(f[2], f[3])),
+                         "r"(pack_bf16(f[4], f[5])), "r"(pack_bf16(f[6], f[7]))
+                         : "memory");
+          }
+          if (c & 1) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tch::tma_store_2d(&tmC, buf, n0 + col - 32, m0 + quarter * 32);
+              tch::bulk_commit();
+            }
+          }
+        } else if (p.ksplit == 1) {
           store_chunk(p, gm, n0 + col, r[c & 1], vec_ok,
                       p.bias != nullptr ? &s_bias[b][col] : nullptr);
         } else if (gm < p.M) {
@@ -787,6 +867,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   if (abort_flag != 0) {
     for (int i = 0; i < 2000; ++i) __nanosleep(100);
   }
+  if (p.c_tma && warp >= 2 && lane == 0) tch::bulk_wait_read_all();   // my last box has left
   ptx::tc_fence_before();
   __syncthreads();
   // neither CTA may leave while the other can still read its shared memory (the MMAs read
@@ -975,8 +1056,13 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
     p.split = split->split; p.C_act = split->C_act; p.C_hi = split->C_hi;
     p.split_mode = split->mode; p.aux = split->aux;
   }
+  CUtensorMap tmC = tmA;
+  p.c_tma = (!c_is_f32 && !accumulate && split == nullptr && (ldc & 7) == 0 &&
+             ((uintptr_t)C & 15) == 0) ? 1 : 0;
+  if (p.c_tma)
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmC, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 32));
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, p);
+  gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, tmC, p);
   count_launch(true);
   ELMAN_CUDA_CHECK(cudaGetLastError());
   return ELMAN_OK;
@@ -1056,10 +1142,17 @@ int gemm_tc_pair(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf
   else
     ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128));
   const int items = tiles * ksplit;
+  // plain bf16 output (no accumulate, no K split, no multi-output epilogue) leaves by bulk
+  // tensor stores; everything else by the epilogue threads' own stores
+  CUtensorMap tmC = tmA;
+  p.c_tma = (!p.c_is_f32 && !p.accumulate && ksplit == 1 && p.split == 0 && (p.ldc & 7) == 0 &&
+             ((uintptr_t)p.C & 15) == 0) ? 1 : 0;
+  if (p.c_tma)
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmC, p.C, (uint64_t)M, (uint64_t)N, (uint64_t)p.ldc, 32));
   auto kern = gemm_tc_pair_kernel<PAIR_STAGES, 2>;
   ELMAN_RETURN_IF(ensure_dynamic_smem(kern, pair_smem_bytes<PAIR_STAGES>(), attr_set));
   const int grid = 2 * (items < pairs ? items : pairs);
-  kern<<<grid, P_THREADS, pair_smem_bytes<PAIR_STAGES>(), stream>>>(tmA, tmB, p);
+  kern<<<grid, P_THREADS, pair_smem_bytes<PAIR_STAGES>(), stream>>>(tmA, tmB, tmC, p);
   count_launch(true);
   ELMAN_CUDA_CHECK(cudaGetLastError());
   if (ksplit > 1) {
