@@ -829,6 +829,16 @@ def main():
                           "projection_fwd": proj_ms, "gemms_bwd": bgemm_ms,
                           "recurrence_fwd_us_per_step": rec_fwd_ms * 1e3 / T,
                           "recurrence_bwd_us_per_step": rec_bwd_ms * 1e3 / T},
+            # tensor-core view of the time-parallel phases and of the whole call (algorithmic
+            # flops: one 2*T*B*d^2 GEMM forward, three backward, 12*T*B*d^2 per call)
+            "tensor_view": {
+                "projection_fwd_tflops": rec_flops / (proj_ms / 1e3) / 1e12 if proj_ms > 0 else None,
+                "gemms_bwd_tflops": 3 * rec_flops / (bgemm_ms / 1e3) / 1e12 if bgemm_ms > 0 else None,
+                "whole_call_tflops": 6 * rec_flops / (total_ms / args.steps / 1e3) / 1e12,
+                "projection_fwd_frac": rec_flops / (proj_ms / 1e3) / 1e12 / peak_tf if proj_ms > 0 else None,
+                "gemms_bwd_frac": 3 * rec_flops / (bgemm_ms / 1e3) / 1e12 / peak_tf if bgemm_ms > 0 else None,
+                "whole_call_frac": 6 * rec_flops / (total_ms / args.steps / 1e3) / 1e12 / peak_tf,
+                "peak_tflops": peak_tf},
             "wall_s_timed_region": wall,
         }
         line.update(sub)

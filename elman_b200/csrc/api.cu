@@ -145,12 +145,27 @@ static int gemm_nn(int dtype, int M, int N, int K, const void* A, int lda, const
 // C[M,N] = Am^T Bm where the inputs are stored as Am[K,M] and Bm[K,N] (sum over the
 // leading "row" index, K = T*B): both operands are MN-major for the tensor core and are
 // read in place.  `splitk` is optional scratch for fp32 partial sums over K ranges.
+// The two weight gradients that share dv: dW_a = dv^T a, dW_b = dv^T b, [d, d] each.
+static int gemm_tn(int dtype, int M, int N, long K, const void* Am, const void* Bm, void* C,
+                   cudaStream_t st, float* splitk = nullptr, size_t splitk_bytes = 0,
+                   int accumulate = 0);
+static int weight_grads_pair(int dtype, int d, long TB, const void* dv, const void* a, void* dW_a,
+                             const void* b, void* dW_b, cudaStream_t st, float* splitk,
+                             size_t splitk_bytes) {
+  if (use_tc(dtype) && TB < (1L << 31)) {
+    const int rc = gemm_tc_dual_tn(d, d, (int)TB, (const bf16*)dv, (const bf16*)a, (const bf16*)b,
+                                   dW_a, dW_b, st);
+    if (rc != ELMAN_ERR_UNSUPPORTED) return rc;
+  }
+  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, dv, a, dW_a, st, splitk, splitk_bytes, 0));
+  return gemm_tn(dtype, d, d, TB, dv, b, dW_b, st, splitk, splitk_bytes, 0);
+}
+
 static size_t splitk_scratch_bytes(int dtype, int M, int N) {
   return dtype == ELMAN_BF16 ? (size_t)GEMM_MAX_KSPLIT * M * N * sizeof(float) : 0;
 }
 static int gemm_tn(int dtype, int M, int N, long K, const void* Am, const void* Bm, void* C,
-                   cudaStream_t st, float* splitk = nullptr, size_t splitk_bytes = 0,
-                   int accumulate = 0) {
+                   cudaStream_t st, float* splitk, size_t splitk_bytes, int accumulate) {
   if (M == 0 || N == 0) return ELMAN_OK;
   if (use_tc(dtype) && K < (1L << 31) && (M & 7) == 0 && (N & 7) == 0 && (K & 7) == 0 &&
       gemm_tc_supported(M, N, (int)K, Am, M, Bm, N, C, N, 0)) {
@@ -449,8 +464,7 @@ int elman_e1_backward_carry(int dtype, int flags, int T, int B, int d, const voi
   // dx = dv W_x ; dW_x = dv^T x ; dW_h = dv^T h[0:T]
   PhaseTimer timer(3, st);
   ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, w.WxT, dx, d, 0, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, dW_h, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(weight_grads_pair(dtype, d, TB, w.dv, x, dW_x, h, dW_h, st, w.splitk, w.splitk_bytes));
   return ELMAN_OK;
 }
 
@@ -616,9 +630,8 @@ int elman_e0_backward(int dtype, int T, int B, int d, const void* W_x, const voi
   ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, w.WT2, dx, d, 0, st));
   ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dg, d, W_gate, d, w.WT2, dx, d, 1, st));
   // dW_x = dv^T x ; dW_h = dv^T h[0:T] ; dW_gate = dg^T x
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(weight_grads_pair(dtype, d, TB, w.dv, x, dW_x, h, dW_h, st, w.splitk, w.splitk_bytes));
   ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dg, x, dW_gate, st, w.splitk, w.splitk_bytes));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, dW_h, st, w.splitk, w.splitk_bytes));
   return ELMAN_OK;
 }
 
@@ -1314,8 +1327,7 @@ int elman_e1_hx_backward(int dtype, int T, int B, int d, const void* W_x, const 
                               nullptr, st));
   ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
   ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, nullptr, dx, d, 0, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, dW_h, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(weight_grads_pair(dtype, d, TB, w.dv, x, dW_x, h, dW_h, st, w.splitk, w.splitk_bytes));
   ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, dz, h1, dW_gh, st, w.splitk, w.splitk_bytes));
   return ELMAN_OK;
 }
@@ -1382,8 +1394,7 @@ int elman_e33_backward(int dtype, int T, int B, int d, const void* W_x, const vo
                               w.sync, nullptr, st));
   ELMAN_RETURN_IF(float_to_dtype(dtype, w.db, db, d, st));
   ELMAN_RETURN_IF(gemm_nn(dtype, TB, d, d, w.dv, d, W_x, d, w.WxT, dx, d, 0, st));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, x, dW_x, st, w.splitk, w.splitk_bytes));
-  ELMAN_RETURN_IF(gemm_tn(dtype, d, d, TB, w.dv, h, dW_h, st, w.splitk, w.splitk_bytes));
+  ELMAN_RETURN_IF(weight_grads_pair(dtype, d, TB, w.dv, x, dW_x, h, dW_h, st, w.splitk, w.splitk_bytes));
   return ELMAN_OK;
 }
 

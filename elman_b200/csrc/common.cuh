@@ -275,6 +275,11 @@ int lowrank_tc_blocks(int T, int B, int d, int r);   // resident blocks (one clu
 void lowrank_tc_pad_bytes(int d, int r, size_t* up_bytes, size_t* vp_bytes);
 int lowrank_tc(const LowRankTcArgs& a, cudaStream_t stream);
 
+// C1 = A^T B1 and C2 = A^T B2 in one launch (csrc/gemm_tc.cu); ELMAN_ERR_UNSUPPORTED (without a
+// recorded error message) when the shapes do not allow it.
+int gemm_tc_dual_tn(int M, int N, int K, const bf16* A, const bf16* B1, const bf16* B2, void* C1,
+                    void* C2, cudaStream_t stream);
+
 // Spectral normalisation of a [d, d] matrix (csrc/spectral.cu): three power-iteration steps
 // from u (advanced in place), v and sigma saved for the backward pass.
 int spectral_norm_fwd(int dtype, int d, const void* W, void* u, float* v, float* sigma, void* W_eff,

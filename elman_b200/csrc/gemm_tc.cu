@@ -68,6 +68,8 @@ struct GemmParams {
   int ksplit = 1;             // persistent kernel: K range cut into this many work items per tile
   int c_tma = 0;              // pair kernel: plain bf16 output leaves through shared memory and
                               // bulk tensor stores (a third tensor map describes C)
+  int dual = 0;               // pair kernel: two products that share A in one launch (second W and
+                              // C in the tensor maps tmB2 / tmC2); c_tma only, no K split
   float* partial = nullptr;   // [ksplit][M][N] fp32 partial sums when ksplit > 1
 };
 
@@ -618,7 +620,9 @@ template <int STAGES, int ACC_BUFS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmC,
+                    const __grid_constant__ CUtensorMap tmB2,
+                    const __grid_constant__ CUtensorMap tmC2, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];    // used in the even CTA only
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -638,7 +642,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   const int nk = (p.K + BK - 1) / BK;
   const int tiles_n = (p.N + Q_BN - 1) / Q_BN;
   const int tiles = ((p.M + Q_BM - 1) / Q_BM) * tiles_n;
-  const int items = tiles * p.ksplit;
+  const int items = tiles * p.ksplit * (p.dual ? 2 : 1);   // dual: the second product's tiles follow
   constexpr uint32_t TCOLS = ACC_BUFS * Q_BN;
 
   if (tid == 0) {
@@ -675,10 +679,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 
   if (warp == 0) {
     if (lane == 0) {
-      struct Cursor { int w, i, k_hi, m0, n0; };
+      struct Cursor { int w, i, k_hi, m0, n0, second; };
       auto open_item = [&](Cursor& cu) {
         if (cu.w >= items) return;
-        const int t = cu.w / p.ksplit, sp = cu.w - t * p.ksplit;
+        cu.second = (p.dual && cu.w >= tiles) ? 1 : 0;
+        const int w1 = cu.w - cu.second * tiles;
+        const int t = w1 / p.ksplit, sp = w1 - t * p.ksplit;
         cu.m0 = (t / tiles_n) * Q_BM + 128 * (int)rank;
         cu.n0 = (t % tiles_n) * Q_BN + 128 * (int)rank;
         cu.i = (int)((long)sp * nk / p.ksplit);
@@ -687,7 +693,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       auto advance = [&](Cursor& cu) {
         if (++cu.i >= cu.k_hi) { cu.w += npairs; open_item(cu); }
       };
-      Cursor ld{pair, 0, 0, 0, 0};
+      Cursor ld{pair, 0, 0, 0, 0, 0};
       open_item(ld);
       for (int it = 0; ld.w < items; ++it) {
         const int s = it % STAGES;
@@ -700,6 +706,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
         if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[s], 2 * Q_STAGE_BYTES);
         if (!(it == p.stall_step && blockIdx.x == 0)) {
           const int i = ld.i, m0 = ld.m0, n0 = ld.n0;
+          const CUtensorMap* tmW = ld.second ? &tmB2 : &tmB;
           if (p.a_mn) {
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk)
@@ -711,10 +718,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
           if (p.b_mn) {
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk)
-              ptx::tma_load_2d_pair(sB + s * Q_B_BYTES + blk * P_BLOCK_BYTES, &tmB, n0 + 64 * blk,
+              ptx::tma_load_2d_pair(sB + s * Q_B_BYTES + blk * P_BLOCK_BYTES, tmW, n0 + 64 * blk,
                                     i * BK, bar);
           } else {
-            ptx::tma_load_2d_pair(sB + s * Q_B_BYTES, &tmB, i * BK, n0, bar);
+            ptx::tma_load_2d_pair(sB + s * Q_B_BYTES, tmW, i * BK, n0, bar);
           }
         }
         advance(ld);
@@ -772,7 +779,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const bool vec_ok = ((p.ldc & 7) == 0) && (((uintptr_t)p.C & 15) == 0);
     int lt = 0;
     for (int w = pair; w < items; w += npairs, ++lt) {
-      const int t = w / p.ksplit, sp = w - t * p.ksplit;
+      const int second = (p.dual && w >= tiles) ? 1 : 0;
+      const int w1 = w - second * tiles;
+      const int t = w1 / p.ksplit, sp = w1 - t * p.ksplit;
       const int b = lt % ACC_BUFS;
       const uint32_t use = (uint32_t)(lt / ACC_BUFS);
       const int m0 = (t / tiles_n) * Q_BM + 128 * (int)rank, n0 = (t % tiles_n) * Q_BN;
@@ -838,7 +847,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA,
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tch::tma_store_2d(&tmC, buf, n0 + col - 32, m0 + quarter * 32);
+              tch::tma_store_2d(second ? &tmC2 : &tmC, buf, n0 + col - 32, m0 + quarter * 32);
               tch::bulk_commit();
             }
           }
@@ -961,7 +970,8 @@ int gemm_tc_nt(int M, int N, int K, const bf16* A, int lda, const bf16* W, int l
 int gemm_tc_persistent(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
                        int b_mn, const GemmParams& p, cudaStream_t stream);
 int gemm_tc_pair(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
-                 int b_mn, GemmParams p, float* splitk, size_t splitk_bytes, cudaStream_t stream);
+                 int b_mn, GemmParams p, float* splitk, size_t splitk_bytes, cudaStream_t stream,
+                 const bf16* W2 = nullptr, void* C2 = nullptr);
 namespace { int sm_count(); }
 
 int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
@@ -1117,13 +1127,14 @@ int gemm_tc_persistent(int M, int N, int K, const bf16* A, int lda, int a_mn, co
 
 // The CTA-pair kernel; K is cut into ranges when the tiles alone would leave SM pairs idle.
 int gemm_tc_pair(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W, int ldw,
-                 int b_mn, GemmParams p, float* splitk, size_t splitk_bytes, cudaStream_t stream) {
+                 int b_mn, GemmParams p, float* splitk, size_t splitk_bytes, cudaStream_t stream,
+                 const bf16* W2, void* C2) {
   constexpr int PAIR_STAGES = 6;
   static bool attr_set[kMaxDev] = {false};
   const int pairs = sm_count() / 2;
   const int tiles = ((M + Q_BM - 1) / Q_BM) * ((N + Q_BN - 1) / Q_BN);
   int ksplit = 1;
-  if (splitk != nullptr && tiles * 2 <= pairs) {
+  if (W2 == nullptr && splitk != nullptr && tiles * 2 <= pairs) {
     const int nk = (K + BK - 1) / BK;
     ksplit = pairs / tiles;
     if (ksplit > GEMM_MAX_KSPLIT) ksplit = GEMM_MAX_KSPLIT;
@@ -1141,7 +1152,7 @@ int gemm_tc_pair(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf
     ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, BK));
   else
     ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128));
-  const int items = tiles * ksplit;
+  const int items = tiles * ksplit * (W2 != nullptr ? 2 : 1);
   // plain bf16 output (no accumulate, no K split, no multi-output epilogue) leaves by bulk
   // tensor stores; everything else by the epilogue threads' own stores
   CUtensorMap tmC = tmA;
@@ -1149,10 +1160,21 @@ int gemm_tc_pair(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf
              ((uintptr_t)p.C & 15) == 0) ? 1 : 0;
   if (p.c_tma)
     ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmC, p.C, (uint64_t)M, (uint64_t)N, (uint64_t)p.ldc, 32));
+  CUtensorMap tmB2 = tmB, tmC2 = tmC;
+  if (W2 != nullptr) {   // second product sharing A: same shapes and layouts, own W and C
+    if (!p.c_tma || C2 == nullptr || ((uintptr_t)C2 & 15) != 0 || ((uintptr_t)W2 & 15) != 0)
+      return set_error(ELMAN_ERR_UNSUPPORTED, "dual GEMM: output form or alignment not supported");
+    if (b_mn)
+      ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB2, W2, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, BK));
+    else
+      ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmB2, W2, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128));
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmC2, C2, (uint64_t)M, (uint64_t)N, (uint64_t)p.ldc, 32));
+    p.dual = 1;
+  }
   auto kern = gemm_tc_pair_kernel<PAIR_STAGES, 2>;
   ELMAN_RETURN_IF(ensure_dynamic_smem(kern, pair_smem_bytes<PAIR_STAGES>(), attr_set));
   const int grid = 2 * (items < pairs ? items : pairs);
-  kern<<<grid, P_THREADS, pair_smem_bytes<PAIR_STAGES>(), stream>>>(tmA, tmB, tmC, p);
+  kern<<<grid, P_THREADS, pair_smem_bytes<PAIR_STAGES>(), stream>>>(tmA, tmB, tmC, tmB2, tmC2, p);
   count_launch(true);
   ELMAN_CUDA_CHECK(cudaGetLastError());
   if (ksplit > 1) {
@@ -1163,6 +1185,27 @@ int gemm_tc_pair(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf
     ELMAN_CUDA_CHECK(cudaGetLastError());
   }
   return ELMAN_OK;
+}
+
+// Two products that share their first operand, C1 = A^T B1 and C2 = A^T B2 (A [K, M], B [K, N],
+// all MN-major, bf16 out): the two weight gradients of a cell, dv^T x and dv^T h, in ONE launch
+// of the CTA-pair kernel.  Each has too few output tiles to fill the device and would otherwise
+// be cut along K with fp32 partial sums and a reduce pass; together their tiles occupy most of
+// the SM pairs without a K split.  Returns ELMAN_ERR_UNSUPPORTED when the shapes do not allow it
+// (the caller then runs them one by one).
+int gemm_tc_dual_tn(int M, int N, int K, const bf16* A, const bf16* B1, const bf16* B2, void* C1,
+                    void* C2, cudaStream_t stream) {
+  if (options().gemm_pair == 1 || M < Q_BM || N < Q_BN || (M & 7) != 0 || (N & 7) != 0 ||
+      (K & 7) != 0 || !gemm_tc_supported(M, N, K, A, M, B1, N, C1, N, 0))
+    return ELMAN_ERR_UNSUPPORTED;
+  GemmParams q;
+  q.M = M; q.N = N; q.K = K;
+  q.bias = nullptr; q.C = C1; q.ldc = N; q.c_is_f32 = 0; q.accumulate = 0;
+  q.spin_limit = options().spin_limit;
+  q.stall_step = (int)options().test_stall_step;
+  q.status = device_status_ptr();
+  q.a_mn = 1; q.b_mn = 1;
+  return gemm_tc_pair(M, N, K, A, M, 1, B1, N, 1, q, nullptr, 0, stream, B2, C2);
 }
 
 }  // namespace elman

@@ -237,19 +237,25 @@ def test_host_pipeline_delivers_the_device_results():
         pipe.submit(calls[0]["x"].cuda(), calls[0]["z"], calls[0]["d_output"])
 
 
-def test_weight_gradients_with_split_k_match_oracle():
-    """T*B large against d: the dW GEMMs have few output tiles and a long K, which the
-    persistent kernel cuts into K ranges with fp32 partial sums (deterministic reduce)."""
+def test_weight_gradients_dual_launch_and_split_k_match_oracle():
+    """T*B large against d: the dW GEMMs have few output tiles and a long K.  By default dW_x and
+    dW_h (same first operand dv) run as ONE launch of the CTA-pair kernel; with the pair kernel
+    off each is cut into K ranges with fp32 partial sums (deterministic reduce); with the
+    persistent kernel off as well, one tile per block over the whole K."""
     inp = orc.make_e1_inputs(80, 32, 256, seed=77)
     got, ref = run_e1(inp, torch.bfloat16)
-    assert_close(errors(got, oracle_e1(ref)), TOL[torch.bfloat16], "split-K dW vs oracle")
+    assert_close(errors(got, oracle_e1(ref)), TOL[torch.bfloat16], "dual dW launch vs oracle")
     again, _ = run_e1(inp, torch.bfloat16)
     for k in ("dW_x", "dW_h", "dx"):
         assert torch.equal(got[k], again[k]), k
-    with option("gemm_persistent", 1):      # the 128x128 kernel, no K split
-        plain, _ = run_e1(inp, torch.bfloat16)
+    with option("gemm_pair", 1):            # split-K through the persistent 128x256 kernel
+        split, _ = run_e1(inp, torch.bfloat16)
+        assert_close(errors(split, oracle_e1(ref)), TOL[torch.bfloat16], "split-K dW vs oracle")
+        with option("gemm_persistent", 1):  # the 128x128 kernel, no K split
+            plain, _ = run_e1(inp, torch.bfloat16)
     for k in ("dW_x", "dW_h"):
         assert orc.rel_err(got[k].float().cpu(), plain[k].float().cpu()) < 5e-3, k
+        assert orc.rel_err(split[k].float().cpu(), plain[k].float().cpu()) < 5e-3, k
 
 
 @pytest.mark.parametrize("T,B,d", [(6, 48, 256), (5, 64, 256), (4, 96, 384), (5, 128, 512),

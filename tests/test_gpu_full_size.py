@@ -49,7 +49,8 @@ def test_e1_config1_full_size_outputs_and_gradients():
     inp = orc.make_e1_inputs(T, B, d, seed=1235)
     before = _lib.tc_launch_count()
     got, ref = run_e1(inp, BF16)
-    assert _lib.tc_launch_count() >= before + 6, "recurrences and GEMMs must take the tcgen05 kernels"
+    # two recurrences, the projection, dx, and the two weight gradients in one dual launch
+    assert _lib.tc_launch_count() >= before + 5, "recurrences and GEMMs must take the tcgen05 kernels"
     assert _lib.device_status()[0] == 0
     truth = oracle_e1(ref)                       # one fp32 CPU pass, a few seconds
     keys = ("h", "output", "v", "dx", "dz", "dW_x", "dW_h", "db")
