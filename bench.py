@@ -63,7 +63,7 @@ def parse_args():
     ap.add_argument("--workload", default="cell", choices=["cell", "lm", "e5", "c4"],
                     help="cell = configs[1] (the headline line); lm = configs[2] training step; "
                          "e5 = configs[3] low-rank cell")
-    ap.add_argument("--pipeline-chunks", type=int, default=8,
+    ap.add_argument("--pipeline-chunks", type=int, default=10,
                     help="lm workload, our arm: time chunks of the (layer, time chunk) pipeline "
                          "over CUDA streams; 0 or 1 = layers one after another as the reference")
     ap.add_argument("--pipeline-streams", type=int, default=0, help="0 = from the SM count")

@@ -211,7 +211,8 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int gm, int gn0
 
 __global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, GemmParams p) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAct,
+               const __grid_constant__ CUtensorMap tmHi, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -330,8 +331,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (p.c_tma) {
         // plain bf16 output: through shared memory (the operand ring is idle now that every MMA
         // has retired: one 4 KB box per warp and column pair of chunks) and bulk tensor stores
+        // (the input projection's three-output form, c_tma == 2: a tile left of `split` stores
+        // the raw values and, through a second box, their silu; a tile right of it stores the
+        // gate input; all three outputs are dense [M, split], split a multiple of the tile width)
         uint8_t* buf = smem + (warp * 2 + (c >> 1)) * 4096;
+        uint8_t* buf_act = buf + 32768;
         const uint32_t row_a = ptx::smem_u32(buf) + (uint32_t)(lane * 128);
+        const bool split_lo = p.c_tma == 2 && n0 < p.split;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float f[8];
@@ -345,16 +351,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           }
           const uint32_t piece = (uint32_t)((c & 1) * 4 + j) ^ (uint32_t)(lane & 7);
+          uint32_t w[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) w[q] = pack_bf16(f[2 * q], f[2 * q + 1]);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_a + (piece << 4)),
-                       "r"(pack_bf16(f[0], f[1])), "r"(pack_bf16(f[2], f[3])),
-                       "r"(pack_bf16(f[4], f[5])), "r"(pack_bf16(f[6], f[7]))
+                       "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
                        : "memory");
+          if (split_lo) {   // silu of the value as stored (rounded to bf16)
+            uint32_t a[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 rf = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[q]));
+              a[q] = pack_bf16(siluf_(rf.x), siluf_(rf.y));
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_a + 32768u + (piece << 4)),
+                         "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3])
+                         : "memory");
+          }
         }
         if (c & 1) {
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tch::tma_store_2d(&tmC, buf, n0 + (c - 1) * 32, m0 + warp * 32);
+            const int col = n0 + (c - 1) * 32, row = m0 + warp * 32;
+            if (p.c_tma == 1) {
+              tch::tma_store_2d(&tmC, buf, col, row);
+            } else if (split_lo) {
+              tch::tma_store_2d(&tmC, buf, col, row);
+              tch::tma_store_2d(&tmAct, buf_act, col, row);
+            } else {
+              tch::tma_store_2d(&tmHi, buf, col - p.split, row);
+            }
             tch::bulk_commit();
           }
         }
@@ -1066,13 +1093,21 @@ int gemm_tc(int M, int N, int K, const bf16* A, int lda, int a_mn, const bf16* W
     p.split = split->split; p.C_act = split->C_act; p.C_hi = split->C_hi;
     p.split_mode = split->mode; p.aux = split->aux;
   }
-  CUtensorMap tmC = tmA;
+  CUtensorMap tmC = tmA, tmAct = tmA, tmHi = tmA;
   p.c_tma = (!c_is_f32 && !accumulate && split == nullptr && (ldc & 7) == 0 &&
              ((uintptr_t)C & 15) == 0) ? 1 : 0;
   if (p.c_tma)
     ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmC, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 32));
+  if (split != nullptr && split->mode == 0 && split->split % BN == 0) {
+    // three dense [M, split] outputs, each through its own tensor map
+    const uint64_t sp = (uint64_t)split->split;
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmC, C, (uint64_t)M, sp, sp, 32));
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmAct, split->C_act, (uint64_t)M, sp, sp, 32));
+    ELMAN_RETURN_IF(make_tmap_bf16_sw128(&tmHi, split->C_hi, (uint64_t)M, sp, sp, 32));
+    p.c_tma = 2;
+  }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, tmC, p);
+  gemm_tc_kernel<<<grid, 128, GEMM_SMEM, stream>>>(tmA, tmB, tmC, tmAct, tmHi, p);
   count_launch(true);
   ELMAN_CUDA_CHECK(cudaGetLastError());
   return ELMAN_OK;
