@@ -2,7 +2,7 @@
 
 `E1HostPipeline.submit()` takes pinned host tensors (x, z, d_output), runs the cell on
 the GPU and leaves output, dx, dz, dW_x, dW_h, db in pinned host buffers.  Uploads,
-kernels and downloads run on three CUDA streams over `depth` device slots, so the
+kernels and downloads run on three CUDA streams over `depth` device slots (default 3), so the
 upload of call i+1 and the download of call i-1 overlap the kernels of call i: with
 PCIe moving about as many bytes per call as the kernels take time for, a stream of
 calls runs at the speed of the slowest of the three instead of their sum.  The
@@ -20,7 +20,7 @@ class _Slot:
 
 
 class E1HostPipeline:
-    def __init__(self, T, B, d, W_x, W_h, b, h0=None, dtype=torch.bfloat16, device=None, depth=2):
+    def __init__(self, T, B, d, W_x, W_h, b, h0=None, dtype=torch.bfloat16, device=None, depth=3):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
             else torch.device(device)
         self.T, self.B, self.d, self.dtype = T, B, d, dtype
