@@ -420,6 +420,12 @@ def lowrank_blocks(dtype, T, B, d, r):
 # names run the same (already fused) path.
 pure_lowrank_elman_forward_fused = pure_lowrank_elman_forward
 pure_lowrank_elman_backward_fused = pure_lowrank_elman_backward
+# The reference's back-to-back-GEMM variant of E5 (V_h h and U_h (.) fused with the rank-r
+# intermediate kept on chip; elman/cuda/pytorch/elman_ladder.cc:3111-3178, :3180-3250, whose
+# kernel is a stub restricted to rank 64/128/256) has the same signature; here every E5 call is
+# that fusion (the single-cluster low-rank kernel), for any rank.
+b2b_lowrank_elman_forward = pure_lowrank_elman_forward
+b2b_lowrank_elman_backward = pure_lowrank_elman_backward
 
 
 # ------------------------------------------------------------------ projection

@@ -14,7 +14,8 @@ there is no fallback inside this package.
 from elman_b200 import _lib as _elman_lib
 from elman_b200.hasty_pytorch_lib import *  # noqa: F401,F403
 from elman_b200.hasty_pytorch_lib import (  # noqa: F401  (names without __all__)
-    e1h_backward, e1h_forward, e33_self_gate_backward, e33_self_gate_forward, lowrank_elman_backward,
+    b2b_lowrank_elman_backward, b2b_lowrank_elman_forward, e1h_backward, e1h_forward,
+    e33_self_gate_backward, e33_self_gate_forward, lowrank_elman_backward,
     lowrank_elman_forward,
     mamba_gated_elman_backward, mamba_gated_elman_forward, pure_lowrank_elman_backward,
     pure_lowrank_elman_backward_fused, pure_lowrank_elman_forward,

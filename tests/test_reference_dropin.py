@@ -28,7 +28,10 @@ REFERENCE_FUNCTIONS = {
     "mamba_gated_elman_forward": (7, 3), "mamba_gated_elman_backward": (7, 5),
     "pure_lowrank_elman_forward": (10, 3), "pure_lowrank_elman_backward": (10, 8),
     "pure_lowrank_elman_forward_fused": (10, 3), "pure_lowrank_elman_backward_fused": (10, 8),
+    "b2b_lowrank_elman_forward": (10, 3), "b2b_lowrank_elman_backward": (10, 8),
     "e33_self_gate_forward": (6, 3), "e33_self_gate_backward": (6, 4),
+    "lowrank_elman_forward": (8, 3), "lowrank_elman_backward": (8, 6),
+    "e1h_forward": (6, 3), "e1h_backward": (6, 4),
 }
 
 
