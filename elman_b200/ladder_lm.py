@@ -84,7 +84,29 @@ class LadderLM(nn.Module):
         sink = fused_ops.get_grad_sink()
         if sink is not None and torch.is_grad_enabled():
             sink.begin_pass()
+        if return_loss and actual_length is not None:
+            positions = torch.arange(target.size(1), device=target.device).unsqueeze(0)
+            target = target.clone()
+            target[~(positions < (actual_length.unsqueeze(1) - 1))] = -100
         time_major = False
+        if self._can_pipeline(inp) and return_loss and self.loss_chunk_size == 0:
+            # Pipeline with the loss: final norm, head and cross-entropy run per time chunk as
+            # soon as the last layer has produced it — beside the rest of the wavefront instead
+            # of after it on the whole sequence, and in the backward pass the last chunk's head
+            # gradient is all the first recurrence waits for.  The mean over tokens is the sum
+            # of the chunks' sums over the number of counted targets.
+            target_tm = target.t().contiguous()          # [T,B]: the small integer side transposed
+
+            def chunk_loss(c, hc, rc, t0, t1):
+                hn, _ = self._add_norm(self.norm, hc, rc, last=True)
+                return F.cross_entropy(self._head(hn).view(-1, self.vocab_size),
+                                       target_tm[t0:t1].reshape(-1), ignore_index=-100,
+                                       reduction="sum")
+            h = self.embedding(inp.t())
+            sums, _, new_hiddens = self._pipelined_layers(h, prev_hiddens, per_chunk=chunk_loss)
+            count = target.numel() if actual_length is None else (target != -100).sum().clamp(min=1)
+            loss = torch.stack(sums).sum() / count
+            return (loss, (new_hiddens, None)) if return_prev_hiddens else loss
         if self._can_pipeline(inp):
             # the pipeline is time-major throughout: gather the embedding rows in that order
             h = self.embedding(inp.t())
@@ -105,10 +127,6 @@ class LadderLM(nn.Module):
         if not return_loss:
             logits = self._head(h)
             return (logits, (new_hiddens, None)) if return_prev_hiddens else logits
-        if actual_length is not None:
-            positions = torch.arange(target.size(1), device=h.device).unsqueeze(0)
-            target = target.clone()
-            target[~(positions < (actual_length.unsqueeze(1) - 1))] = -100
         if time_major:
             # the mean over tokens does not care about their order: transpose the small
             # integer targets instead of the activations
@@ -207,7 +225,11 @@ class LadderLM(nn.Module):
         C = self.pipeline_chunks
         return [(T * c) // C for c in range(C + 1)]
 
-    def _pipelined_layers(self, h, prev_hiddens):
+    def _pipelined_layers(self, h, prev_hiddens, per_chunk=None):
+        """h: [T,B,D] time-major -> (h, residual, final states), both outputs [T,B,D]; with
+        `per_chunk(c, h_c, residual_c, t0, t1)` the last layer's chunks are handed to it one by
+        one on the caller's stream as they become ready, and its results are returned as a
+        list in place of h (residual None)."""
         from .mamba_gated_elman import ChunkLink
         T, B, _ = h.shape          # time-major [T,B,D]
         edges = self._chunk_edges(T)
@@ -287,14 +309,19 @@ class LadderLM(nn.Module):
                     post_done[i][c] = record(sq)
                 h_chunks[c], res_chunks[c] = out, residual
             states.append(state)
+        results = []
         for c in range(C):
             main.wait_event(post_done[-1][c])
             h_chunks[c].record_stream(main)
             res_chunks[c].record_stream(main)
+            if per_chunk is not None:
+                results.append(per_chunk(c, h_chunks[c], res_chunks[c], edges[c], edges[c + 1]))
         for st in states:
             st.record_stream(main)
         for s in pre_streams + rec_streams + post_streams:
             main.wait_event(record(s))   # every stream rejoins (required under graph capture)
+        if per_chunk is not None:
+            return results, None, [st.detach() for st in states]
         # both still time-major [T,B,D]
         return torch.cat(h_chunks, dim=0), torch.cat(res_chunks, dim=0), [st.detach() for st in states]
 
