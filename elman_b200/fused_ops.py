@@ -210,6 +210,42 @@ class InProjSplitSiluFunction(torch.autograd.Function):
         return du.view(*ctx.lead, u2.shape[-1]), dW
 
 
+EMBEDDING_ONE_HOT_MAX_VOCAB = 4096
+
+
+class EmbeddingRowsFunction(torch.autograd.Function):
+    """forward(tokens [...], weight [V, D]) -> weight[tokens].  The backward pass forms the
+    weight gradient as a GEMM, onehot(tokens)^T · d_rows, through `weight_grad_tn`: dense and
+    deterministic, and with a gradient sink it accumulates beside the data path instead of
+    running ATen's sort-and-segment kernels at the very end of the backward pass.  Meant for
+    byte-level vocabularies (`embedding_rows` falls back to nn.functional.embedding above
+    EMBEDDING_ONE_HOT_MAX_VOCAB rows)."""
+
+    @staticmethod
+    def forward(ctx, tokens, weight):
+        ctx.save_for_backward(tokens, weight)
+        return torch.nn.functional.embedding(tokens, weight)
+
+    @staticmethod
+    def backward(ctx, d_rows):
+        tokens, weight = ctx.saved_tensors
+        n = tokens.numel()
+        onehot = torch.zeros(n, weight.size(0), dtype=weight.dtype, device=weight.device)
+        onehot.scatter_(1, tokens.reshape(n, 1), 1.0)
+        d2 = d_rows.contiguous().view(n, weight.size(1))
+        if d2.dtype != weight.dtype:
+            d2 = d2.to(weight.dtype)
+        return None, weight_grad_tn(weight, onehot, d2)
+
+
+def embedding_rows(tokens, weight):
+    """weight[tokens], with the one-hot GEMM backward where the library handles the weight."""
+    if library_handles(weight) and weight.size(0) <= EMBEDDING_ONE_HOT_MAX_VOCAB \
+            and torch.is_grad_enabled() and weight.requires_grad:
+        return EmbeddingRowsFunction.apply(tokens, weight)
+    return torch.nn.functional.embedding(tokens, weight)
+
+
 def linear(x, weight, bias=None):
     """y = x W^T (+ b) over the last dimension through the library's GEMMs."""
     from .mamba_gated_elman import LinearFunction

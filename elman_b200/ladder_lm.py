@@ -102,15 +102,13 @@ class LadderLM(nn.Module):
                 return F.cross_entropy(self._head(hn).view(-1, self.vocab_size),
                                        target_tm[t0:t1].reshape(-1), ignore_index=-100,
                                        reduction="sum")
-            h = self.embedding(inp.t())
-            sums, _, new_hiddens = self._pipelined_layers(h, prev_hiddens, per_chunk=chunk_loss)
+            sums, _, new_hiddens = self._pipelined_layers(self._embed_chunks(inp), prev_hiddens,
+                                                          per_chunk=chunk_loss)
             count = target.numel() if actual_length is None else (target != -100).sum().clamp(min=1)
             loss = torch.stack(sums).sum() / count
             return (loss, (new_hiddens, None)) if return_prev_hiddens else loss
         if self._can_pipeline(inp):
-            # the pipeline is time-major throughout: gather the embedding rows in that order
-            h = self.embedding(inp.t())
-            h, residual, new_hiddens = self._pipelined_layers(h, prev_hiddens)
+            h, residual, new_hiddens = self._pipelined_layers(self._embed_chunks(inp), prev_hiddens)
             time_major = True
         else:
             h = self.embedding(inp)
@@ -225,13 +223,31 @@ class LadderLM(nn.Module):
         C = self.pipeline_chunks
         return [(T * c) // C for c in range(C + 1)]
 
+    def _embed_chunks(self, inp):
+        """Embedding rows of inp [B,T] for the pipeline, which is time-major throughout: one
+        [T,B,D] tensor — or, with the fused ops, one tensor per time chunk, so that a chunk's
+        share of the embedding gradient is formed (as a one-hot GEMM) as soon as the backward
+        wavefront has left layer 0's unit of that chunk rather than after the whole pass."""
+        tokens = inp.t()
+        if self.fused_ops and fused_ops.library_handles(self.embedding.weight):
+            tokens = tokens.contiguous()
+            edges = self._chunk_edges(tokens.size(0))
+            return [fused_ops.embedding_rows(tokens[edges[c]:edges[c + 1]], self.embedding.weight)
+                    for c in range(len(edges) - 1)]
+        return self.embedding(tokens)
+
     def _pipelined_layers(self, h, prev_hiddens, per_chunk=None):
-        """h: [T,B,D] time-major -> (h, residual, final states), both outputs [T,B,D]; with
+        """h: [T,B,D] time-major (or its time chunks as a list, cut at `_chunk_edges`)
+        -> (h, residual, final states), both outputs [T,B,D]; with
         `per_chunk(c, h_c, residual_c, t0, t1)` the last layer's chunks are handed to it one by
         one on the caller's stream as they become ready, and its results are returned as a
         list in place of h (residual None)."""
         from .mamba_gated_elman import ChunkLink
-        T, B, _ = h.shape          # time-major [T,B,D]
+        given = list(h) if isinstance(h, (list, tuple)) else None
+        if given is not None:
+            h = given[0]
+        T = h.size(0) if given is None else sum(x.size(0) for x in given)
+        B = h.size(1)              # time-major [T,B,D]
         edges = self._chunk_edges(T)
         C = len(edges) - 1
         main = torch.cuda.current_stream(h.device)
@@ -240,7 +256,7 @@ class LadderLM(nn.Module):
         shared, shared_t = [None] * self.depth, [None] * self.depth
         # time-major chunks [Tc,B,D]: the cell's own layout, so no layer transposes anything;
         # slices along the leading dimension are contiguous views, nothing is copied
-        h_chunks = [h[edges[c]:edges[c + 1]] for c in range(C)]
+        h_chunks = given if given is not None else [h[edges[c]:edges[c + 1]] for c in range(C)]
         start = torch.cuda.Event()   # everything the side streams read is enqueued before this
         start.record(main)
         for s in pre_streams + rec_streams + post_streams:

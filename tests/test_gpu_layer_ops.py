@@ -164,3 +164,28 @@ def test_spectral_norm_kernel_matches_the_framework_ops(d, dtype, tol):
     assert rel_err(We.float().cpu(), We_ref.detach()) < tol
     assert rel_err(got._spectral_u.float().cpu(), ref._spectral_u) < tol
     assert rel_err(Wg.grad.float().cpu(), Wr.grad) < tol
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_embedding_rows_gradient_matches_the_framework_embedding(dtype, tol):
+    """The one-hot GEMM backward of `embedding_rows` gives nn.functional.embedding's weight
+    gradient (tokens repeat many times: vocabulary 256, 51 x 32 tokens)."""
+    torch.manual_seed(5)
+    V, D, Tc, B = 256, 320, 51, 32
+    tokens = torch.randint(0, V, (Tc, B), device="cuda")
+    tokens[0, :8] = 7                       # a row hit many times, and rows never hit
+    w_ref = (torch.randn(V, D, device="cuda") * 0.1).to(dtype).requires_grad_(True)
+    w_lib = w_ref.detach().clone().requires_grad_(True)
+    dy = torch.randn(Tc, B, D, device="cuda").to(dtype)
+    y_ref = F.embedding(tokens, w_ref)
+    y_lib = fused_ops.embedding_rows(tokens, w_lib)
+    assert y_lib.grad_fn is not None and "EmbeddingRows" in type(y_lib.grad_fn).__name__
+    assert torch.equal(y_ref, y_lib)
+    y_ref.backward(dy)
+    y_lib.backward(dy)
+    ref = w_ref.grad.float()
+    err = (w_lib.grad.float() - ref).norm() / ref.norm()
+    assert err < tol, err
+    never = torch.ones(V, dtype=torch.bool, device="cuda")
+    never[tokens.unique()] = False
+    assert torch.count_nonzero(w_lib.grad[never]) == 0
