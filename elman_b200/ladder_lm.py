@@ -192,7 +192,12 @@ class LadderLM(nn.Module):
         `n_rec` streams for the recurrences themselves, dealt to the layers round-robin."""
         key = (device, n_rec)
         if key not in self._streams:
-            mk = lambda n: [torch.cuda.Stream(device=device) for _ in range(n)]
+            # From the pool of high-priority streams: the framework hands out streams from a
+            # fixed pool per priority and starts over when it is used up, and the gradient
+            # sink, the host pipeline, graph capture and the communication stream draw from the
+            # default pool — two logical streams on one CUDA stream would serialise units
+            # that are meant to overlap.  (The priority itself changes nothing measurable.)
+            mk = lambda n: [torch.cuda.Stream(device=device, priority=-1) for _ in range(n)]
             self._streams[key] = (mk(self.depth), mk(n_rec), mk(self.depth))
         return self._streams[key]
 
